@@ -1,0 +1,290 @@
+// Block-cooperative extension of the fragment API for B200 (sm_100a).
+//
+// The per-warp API (rocwmma.hpp) keeps accumulators in registers.  Blackwell's
+// 5th-generation tensor cores are instead driven per thread block: one thread
+// issues tcgen05.mma on operand tiles that the Tensor Memory Accelerator (TMA)
+// staged in shared memory, and the accumulator lives in tensor memory (TMEM).
+// This header holds the device-side building blocks for kernels of that kind:
+// mbarrier pipeline primitives with BOUNDED waits, TMA tile loads, TMEM
+// allocation, tcgen05.mma / commit / ld wrappers, and the shared-memory and
+// instruction descriptors they take.
+//
+// It plays the role of the reference's cooperative global->LDS staging
+// (rocwmma_coop.hpp, samples/perf_hgemm.cpp:592-685), redone for the hardware.
+// No function here uses cluster multicast.
+//
+// Every wait gives up after a time limit, raises a block-wide abort flag and
+// returns false; callers leave their loops, release what they hold and return,
+// so that a protocol error surfaces as a status code instead of a hung GPU.
+#ifndef ROCWMMA_B200_BLOCK_API_HPP
+#define ROCWMMA_B200_BLOCK_API_HPP
+
+#include "internal/config.hpp"
+#include "internal/types.hpp"
+
+namespace rocwmma
+{
+    namespace block
+    {
+        // ---- addresses ------------------------------------------------------------
+        ROCWMMA_DEVICE inline uint32_t smem_addr(void const* p)
+        {
+            return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+        }
+
+        ROCWMMA_DEVICE inline bool elect_one()
+        {
+            uint32_t pred = 0;
+            asm volatile("{\n\t"
+                         ".reg .pred P;\n\t"
+                         "elect.sync _|P, 0xffffffff;\n\t"
+                         "selp.u32 %0, 1, 0, P;\n\t"
+                         "}"
+                         : "=r"(pred));
+            return pred != 0;
+        }
+
+        // ---- mbarrier -------------------------------------------------------------
+        ROCWMMA_DEVICE inline void mbar_init(uint64_t* bar, uint32_t count)
+        {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)),
+                         "r"(count)
+                         : "memory");
+        }
+        // Makes freshly initialised barriers visible to the async (TMA / tensor
+        // core) proxy.
+        ROCWMMA_DEVICE inline void mbar_init_fence()
+        {
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        ROCWMMA_DEVICE inline void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+        {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                             smem_addr(bar)),
+                         "r"(bytes)
+                         : "memory");
+        }
+        ROCWMMA_DEVICE inline void mbar_arrive(uint64_t* bar)
+        {
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar))
+                         : "memory");
+        }
+        ROCWMMA_DEVICE inline bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+        {
+            uint32_t done;
+            asm volatile("{\n\t"
+                         ".reg .pred P;\n\t"
+                         "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+                         "selp.u32 %0, 1, 0, P;\n\t"
+                         "}"
+                         : "=r"(done)
+                         : "r"(smem_addr(bar)), "r"(parity)
+                         : "memory");
+            return done != 0;
+        }
+
+        // Codes recorded next to the abort flag: which kind of wait ran out.
+        enum WaitCode : uint32_t
+        {
+            WAIT_STAGE_EMPTY = 1, // loader waiting for the MMA to release a ring slot
+            WAIT_STAGE_FULL  = 2, // MMA issuer waiting for TMA data
+            WAIT_ACC_EMPTY   = 3, // MMA issuer waiting for the epilogue to drain TMEM
+            WAIT_ACC_FULL    = 4, // epilogue waiting for the MMAs of a tile
+            WAIT_DRAIN       = 5, // leaving: waiting for own TMA copies still in flight
+            WAIT_PEER        = 6  // CTA-pair handshake
+        };
+
+        // Block-wide abort state in shared memory.
+        struct AbortState
+        {
+            volatile uint32_t flag;
+            volatile uint32_t code;
+        };
+
+        // ~2 s at B200 clocks; a healthy pipeline wait lasts microseconds.
+        constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;
+
+        // Waits until the phase with the given parity of `bar` has completed.
+        // Returns false if the block is aborting or the time limit passed (in which
+        // case it raises the abort flag itself).
+        ROCWMMA_DEVICE inline bool
+            mbar_wait(uint64_t* bar, uint32_t parity, AbortState* abort, uint32_t code,
+                      long long limit = WAIT_LIMIT_CYCLES)
+        {
+            if(mbar_try_wait(bar, parity))
+                return true;
+            const long long start = clock64();
+            uint32_t        spins = 0;
+            while(true)
+            {
+                if(mbar_try_wait(bar, parity))
+                    return true;
+                if((++spins & 63u) == 0u)
+                {
+                    if(abort->flag != 0u)
+                        return false;
+                    if(clock64() - start > limit)
+                    {
+                        abort->code = code;
+                        abort->flag = 1u;
+                        __threadfence_block();
+                        return false;
+                    }
+                }
+            }
+        }
+
+        // ---- TMA (cp.async.bulk.tensor), no multicast --------------------------------
+        ROCWMMA_DEVICE inline void tma_prefetch_descriptor(void const* tensorMap)
+        {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensorMap))
+                         : "memory");
+        }
+        // Loads the box of `tensorMap` whose innermost coordinate is x (elements;
+        // x * element size must be a multiple of 16 bytes) and outer coordinate y
+        // into shared memory at dst, signalling `bar` with the byte count.
+        ROCWMMA_DEVICE inline void tma_load_2d(void* dst, void const* tensorMap, uint64_t* bar,
+                                               int32_t x, int32_t y)
+        {
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                         " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_addr(dst)),
+                         "l"(reinterpret_cast<uint64_t>(tensorMap)), "r"(smem_addr(bar)), "r"(x),
+                         "r"(y)
+                         : "memory");
+        }
+
+        // ---- tensor memory ----------------------------------------------------------
+        // One full warp allocates `columns` (power of two, 32..512) TMEM columns; the
+        // base address is written to *slot in shared memory.
+        ROCWMMA_DEVICE inline void tmem_alloc(uint32_t* slot, uint32_t columns)
+        {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_addr(slot)),
+                         "r"(columns)
+                         : "memory");
+        }
+        ROCWMMA_DEVICE inline void tmem_relinquish_alloc_permit()
+        {
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        ROCWMMA_DEVICE inline void tmem_dealloc(uint32_t base, uint32_t columns)
+        {
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base),
+                         "r"(columns)
+                         : "memory");
+        }
+        ROCWMMA_DEVICE inline void tc_fence_before_sync()
+        {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        }
+        ROCWMMA_DEVICE inline void tc_fence_after_sync()
+        {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+
+        // ---- descriptors -------------------------------------------------------------
+        // Shared-memory matrix descriptor for a K-major operand tile written by TMA
+        // with the 128-byte swizzle: rows are 128 bytes wide, groups of 8 rows are
+        // 1024 bytes apart.  `addr` is the shared-memory byte address of the tile (or
+        // of a 32-byte K step inside its first row); the tile base must be
+        // 1024-byte aligned.
+        ROCWMMA_DEVICE inline uint64_t smem_desc_kmajor_sw128(uint32_t addr)
+        {
+            uint64_t d = 0;
+            d |= uint64_t((addr & 0x3ffffu) >> 4); // start address, 16-byte units
+            d |= uint64_t(1) << 16; // leading-dimension byte offset (unused with swizzle)
+            d |= uint64_t(1024u >> 4) << 32; // stride between 8-row groups
+            d |= uint64_t(1) << 46; // descriptor version for sm_100
+            d |= uint64_t(2) << 61; // layout: 128-byte swizzle
+            return d;
+        }
+
+        enum class MmaKind : uint32_t
+        {
+            F16, // fp16 or bf16 inputs, fp32 accumulate
+            TF32,
+            I8,
+            F8F6F4
+        };
+        // Operand format codes of the instruction descriptor.
+        constexpr uint32_t FMT_F16 = 0, FMT_BF16 = 1, FMT_TF32 = 2;
+        constexpr uint32_t FMT_E4M3 = 0, FMT_E5M2 = 1;
+        constexpr uint32_t FMT_U8 = 0, FMT_S8 = 1;
+        constexpr uint32_t ACC_F16 = 0, ACC_F32 = 1, ACC_S32 = 2;
+
+        // 32-bit instruction descriptor: accumulator format, A/B formats, both
+        // operands K-major, tile M x N.
+        ROCWMMA_HOST_DEVICE constexpr uint32_t
+            make_instr_desc(uint32_t accFmt, uint32_t aFmt, uint32_t bFmt, uint32_t m, uint32_t n)
+        {
+            return (accFmt << 4) | (aFmt << 7) | (bFmt << 10) | (0u << 15) | (0u << 16)
+                   | ((n >> 3) << 17) | ((m >> 4) << 24);
+        }
+
+        // D[tmem] (+)= A[smem] * B[smem].  Issued by ONE thread.
+        template <MmaKind Kind>
+        ROCWMMA_DEVICE inline void mma_ss(uint32_t dTmem, uint64_t descA, uint64_t descB,
+                                          uint32_t idesc, uint32_t accumulate)
+        {
+            if constexpr(Kind == MmaKind::F16)
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+                                 dTmem),
+                             "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+                             : "memory");
+            else if constexpr(Kind == MmaKind::TF32)
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+                                 dTmem),
+                             "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+                             : "memory");
+            else if constexpr(Kind == MmaKind::I8)
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+                                 dTmem),
+                             "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+                             : "memory");
+            else
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+                                 dTmem),
+                             "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+                             : "memory");
+        }
+
+        // Makes `bar` complete one arrival when all tcgen05.mma issued so far by this
+        // thread have finished (implies tcgen05.fence::before_thread_sync).
+        ROCWMMA_DEVICE inline void mma_commit(uint64_t* bar)
+        {
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::
+                             "r"(smem_addr(bar))
+                         : "memory");
+        }
+
+        // Reads 32 consecutive 32-bit columns of this thread's TMEM lane
+        // (lane = 32 * (warp % 4) + laneid).  Warp-wide.
+        ROCWMMA_DEVICE inline void tmem_load_32x32b_x32(uint32_t taddr, uint32_t (&r)[32])
+        {
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
+                "[%32];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+                  "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                  "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+                  "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+                  "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr)
+                : "memory");
+        }
+        ROCWMMA_DEVICE inline void tmem_load_wait()
+        {
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        }
+    } // namespace block
+} // namespace rocwmma
+
+#endif // ROCWMMA_B200_BLOCK_API_HPP

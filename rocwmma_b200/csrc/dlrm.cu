@@ -1,0 +1,548 @@
+// Fused DLRM dot-interaction forward and backward for B200.
+//
+// Reference (paths in the rocWMMA tree): forward samples/simple_dlrm.cpp:184-284,
+// backward :290-441, host routines test/reference_impl.hpp:83-179.  The reference
+// runs one 16x16 tile per warp with grid.z = batch, writes the m x m product to a
+// global scratch array, gathers the triangle from it, and for the backward pass
+// launches a separate kernel (plus a host synchronisation) to rebuild the symmetric
+// gradient matrix.  Both passes move ~8 bytes per flop-pair of useful work and are
+// bound by HBM bandwidth, so here each pass is ONE kernel that touches every input
+// and output byte exactly once:
+//
+//   * a warp owns whole samples; eight consecutive samples form a group so that the
+//     packed [k + m(m-1)/2]-wide rows, which are only 2-byte aligned one by one, start
+//     on a 16-byte boundary as a group and move with 128-bit accesses;
+//   * samples stream through a per-warp cp.async ring (padded rows, conflict-free
+//     ldmatrix); the m x m (forward) and m x k (backward) products run on warp-level
+//     tensor-core instructions (mma.sync m16n8k16, fp32 accumulate) with m padded to
+//     32 by a shared row of zeros; nothing is written to global scratch;
+//   * forward: X X^T needs only A fragments -- the B operand of block (i, j) is a
+//     re-labelling of the A registers of block j; only blocks on or below the diagonal
+//     are computed;
+//   * backward: the symmetric matrix G is rebuilt in shared memory (stored in fp16 as
+//     the host routine does), G X overwrites the sample's own ring slot column block
+//     by column block and leaves with 128-bit row stores.
+//
+// Limits: fp16, m <= 32, k a multiple of 16 and <= 256, pointers 16-byte aligned.
+#include "common.cuh"
+#include <cuda_fp16.h>
+
+namespace
+{
+    constexpr uint32_t GROUP   = 8; // samples per aligned group
+    constexpr uint32_t MAX_K   = 256;
+    constexpr uint32_t G_LD    = 40; // halves per row of the 32x32 G tile (80 bytes)
+    constexpr uint32_t ZERO_BYTES = MAX_K * 2 + 16;
+
+    __device__ inline uint32_t smemAddr(void const* p)
+    {
+        return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    }
+    __device__ inline void cpAsync16(uint32_t dst, void const* src)
+    {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+    __device__ inline void cpAsyncCommit()
+    {
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    template <int N>
+    __device__ inline void cpAsyncWait()
+    {
+        asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+    }
+    __device__ inline void ldmatrixX4(uint32_t (&r)[4], uint32_t addr)
+    {
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                     : "r"(addr));
+    }
+    __device__ inline void ldmatrixX4Trans(uint32_t (&r)[4], uint32_t addr)
+    {
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                     : "r"(addr));
+    }
+    __device__ inline void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                    uint32_t a3, uint32_t b0, uint32_t b1)
+    {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+                     "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+
+    struct Shape
+    {
+        uint32_t m, k, batch;
+        uint32_t outLen; // k + m(m-1)/2
+        uint32_t rowStride; // bytes per staged sample row: 2k + 16
+        uint32_t stageBytes; // m * rowStride
+        uint32_t numGroups; // ceil(batch / 8)
+    };
+
+    // Sample `q` of this warp's sequence: groups are dealt round-robin to warps.
+    __device__ inline uint32_t sampleOf(uint32_t q, uint32_t warpGlobal, uint32_t totalWarps)
+    {
+        return (warpGlobal + (q / GROUP) * totalWarps) * GROUP + (q % GROUP);
+    }
+
+    // Copies one sample (m rows of k halves, contiguous in global memory) into a ring slot.
+    __device__ inline void issueSample(uint32_t slotAddr, __half const* sample, Shape const& sh,
+                                       uint32_t lane)
+    {
+        const uint32_t chunksPerRow = sh.k / 8;
+        const uint32_t total        = sh.m * chunksPerRow;
+        for(uint32_t c = lane; c < total; c += 32)
+        {
+            const uint32_t row = c / chunksPerRow, cc = c % chunksPerRow;
+            cpAsync16(slotAddr + row * sh.rowStride + cc * 16,
+                      reinterpret_cast<uint8_t const*>(sample) + size_t(c) * 16);
+        }
+    }
+
+    // =====================================================================================
+    // forward
+    // =====================================================================================
+    template <uint32_t NWARPS, uint32_t NSTAGES>
+    __global__ void __launch_bounds__(NWARPS * 32, 1)
+        dlrmFwdKernel(__half const* __restrict__ input, __half* __restrict__ output, Shape sh)
+    {
+        extern __shared__ __align__(16) uint8_t smem[];
+        const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+        const uint32_t g = lane >> 2, t = lane & 3;
+
+        // layout: [zero row][warp 0: ring slots, out staging][warp 1: ...]
+        const uint32_t outStageBytes = GROUP * sh.outLen * 2; // multiple of 16
+        const uint32_t perWarp       = NSTAGES * sh.stageBytes + outStageBytes;
+        uint8_t*       zeroRow       = smem;
+        uint8_t*       mine          = smem + ZERO_BYTES + warp * perWarp;
+        __half*        outStage      = reinterpret_cast<__half*>(mine + NSTAGES * sh.stageBytes);
+        const uint32_t ringAddr      = smemAddr(mine);
+        const uint32_t zeroAddr      = smemAddr(zeroRow);
+
+        for(uint32_t i = threadIdx.x; i < ZERO_BYTES / 4; i += blockDim.x)
+            reinterpret_cast<uint32_t*>(zeroRow)[i] = 0u;
+        __syncthreads();
+
+        const uint32_t totalWarps = gridDim.x * NWARPS;
+        const uint32_t warpGlobal = blockIdx.x * NWARPS + warp;
+        const uint32_t myGroups
+            = warpGlobal < sh.numGroups ? (sh.numGroups - warpGlobal + totalWarps - 1) / totalWarps
+                                        : 0;
+        const uint32_t numQ = myGroups * GROUP;
+        const bool     twoM = sh.m > 16;
+
+        // prologue
+#pragma unroll
+        for(uint32_t q = 0; q < NSTAGES - 1; ++q)
+        {
+            if(q < numQ)
+            {
+                const uint32_t s = sampleOf(q, warpGlobal, totalWarps);
+                if(s < sh.batch)
+                    issueSample(ringAddr + q * sh.stageBytes, input + size_t(s) * sh.m * sh.k, sh,
+                                lane);
+            }
+            cpAsyncCommit();
+        }
+
+        // ldmatrix row addresses of this lane inside a slot: matrix (lane / 8) of the x4 group
+        // is rows (lane/8 & 1) * 8 ..., column block (lane / 16) * 8; rows >= m read zeros.
+        const uint32_t lmRow = ((lane >> 3) & 1u) * 8u + (lane & 7u);
+        const uint32_t lmCol = (lane >> 4) * 8u;
+
+        for(uint32_t q = 0; q < numQ; ++q)
+        {
+            cpAsyncWait<NSTAGES - 2>();
+            __syncwarp();
+            {
+                const uint32_t qn = q + NSTAGES - 1;
+                if(qn < numQ)
+                {
+                    const uint32_t s = sampleOf(qn, warpGlobal, totalWarps);
+                    if(s < sh.batch)
+                        issueSample(ringAddr + (qn % NSTAGES) * sh.stageBytes,
+                                    input + size_t(s) * sh.m * sh.k, sh, lane);
+                }
+                cpAsyncCommit();
+            }
+
+            const uint32_t sample = sampleOf(q, warpGlobal, totalWarps);
+            const uint32_t slot   = q % GROUP;
+            if(sample < sh.batch)
+            {
+                const uint32_t slotAddr = ringAddr + (q % NSTAGES) * sh.stageBytes;
+                float          acc[6][4];
+#pragma unroll
+                for(uint32_t i = 0; i < 6; ++i)
+#pragma unroll
+                    for(uint32_t e = 0; e < 4; ++e)
+                        acc[i][e] = 0.0f;
+
+                const uint32_t row0 = lmRow, row1 = 16u + lmRow;
+                const uint32_t base0 = row0 < sh.m ? slotAddr + row0 * sh.rowStride : zeroAddr;
+                const uint32_t base1 = row1 < sh.m ? slotAddr + row1 * sh.rowStride : zeroAddr;
+                for(uint32_t kk = 0; kk < sh.k; kk += 16)
+                {
+                    uint32_t a[4], b[4];
+                    ldmatrixX4(a, base0 + (kk + lmCol) * 2);
+                    // blocks (0,0) and (0,1): B operands are A's own registers
+                    mma16816(acc[0], a[0], a[1], a[2], a[3], a[0], a[2]);
+                    mma16816(acc[1], a[0], a[1], a[2], a[3], a[1], a[3]);
+                    if(twoM)
+                    {
+                        ldmatrixX4(b, base1 + (kk + lmCol) * 2);
+                        mma16816(acc[2], b[0], b[1], b[2], b[3], a[0], a[2]);
+                        mma16816(acc[3], b[0], b[1], b[2], b[3], a[1], a[3]);
+                        mma16816(acc[4], b[0], b[1], b[2], b[3], b[0], b[2]);
+                        mma16816(acc[5], b[0], b[1], b[2], b[3], b[1], b[3]);
+                    }
+                }
+
+                // row 0 of the sample, then the strict lower triangle
+                __half*       dst  = outStage + slot * sh.outLen;
+                __half const* row0p = reinterpret_cast<__half const*>(
+                    mine + (q % NSTAGES) * sh.stageBytes);
+                for(uint32_t j = lane; j < sh.k; j += 32)
+                    dst[j] = row0p[j];
+#pragma unroll
+                for(uint32_t i = 0; i < 6; ++i)
+                {
+                    const uint32_t mt = i < 2 ? 0u : 1u;
+                    const uint32_t nt = i < 2 ? i : i - 2u;
+#pragma unroll
+                    for(uint32_t e = 0; e < 4; ++e)
+                    {
+                        const uint32_t r = mt * 16u + g + 8u * (e >> 1);
+                        const uint32_t c = nt * 8u + 2u * t + (e & 1u);
+                        if(c < r && r < sh.m)
+                            dst[sh.k + r * (r - 1u) / 2u + c] = __float2half_rn(acc[i][e]);
+                    }
+                }
+            }
+
+            // end of a group: flush its packed rows with 128-bit stores
+            if(slot == GROUP - 1)
+            {
+                __syncwarp();
+                const uint32_t first = sampleOf(q - (GROUP - 1), warpGlobal, totalWarps);
+                const uint32_t cnt   = min(GROUP, sh.batch - first);
+                __half*        gout  = output + size_t(first) * sh.outLen;
+                if(cnt == GROUP)
+                {
+                    for(uint32_t i = lane; i < sh.outLen; i += 32)
+                        reinterpret_cast<uint4*>(gout)[i]
+                            = reinterpret_cast<uint4 const*>(outStage)[i];
+                }
+                else
+                {
+                    for(uint32_t i = lane; i < cnt * sh.outLen; i += 32)
+                        gout[i] = outStage[i];
+                }
+                __syncwarp();
+            }
+        }
+        cpAsyncWait<0>();
+    }
+
+    // =====================================================================================
+    // backward
+    // =====================================================================================
+    template <uint32_t NWARPS, uint32_t NSTAGES>
+    __global__ void __launch_bounds__(NWARPS * 32, 1)
+        dlrmBwdKernel(__half const* __restrict__ input, __half const* __restrict__ upstream,
+                      __half* __restrict__ grad, __half* __restrict__ mlpGrad, Shape sh)
+    {
+        extern __shared__ __align__(16) uint8_t smem[];
+        const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+        const uint32_t g = lane >> 2, t = lane & 3;
+
+        // layout: [zero row][triangle index table][warp 0: ring, 2 x upstream group, G][...]
+        const uint32_t triCount   = sh.m * (sh.m - 1) / 2;
+        const uint32_t triBytes   = (triCount * 2 + 15) / 16 * 16;
+        const uint32_t upBytes    = GROUP * sh.outLen * 2;
+        const uint32_t gBytes     = 32 * G_LD * 2;
+        const uint32_t perWarp    = NSTAGES * sh.stageBytes + 2 * upBytes + gBytes;
+        uint8_t*       zeroRow    = smem;
+        uint16_t*      tri        = reinterpret_cast<uint16_t*>(smem + ZERO_BYTES);
+        uint8_t*       mine       = smem + ZERO_BYTES + triBytes + warp * perWarp;
+        uint8_t*       upStage    = mine + NSTAGES * sh.stageBytes;
+        __half*        gTile      = reinterpret_cast<__half*>(upStage + 2 * upBytes);
+        const uint32_t ringAddr   = smemAddr(mine);
+        const uint32_t zeroAddr   = smemAddr(zeroRow);
+        const uint32_t gAddr      = smemAddr(gTile);
+
+        for(uint32_t i = threadIdx.x; i < ZERO_BYTES / 4; i += blockDim.x)
+            reinterpret_cast<uint32_t*>(zeroRow)[i] = 0u;
+        // (r, c) of packed triangle entry idx, row-major over r, c < r
+        for(uint32_t r = threadIdx.x; r < sh.m; r += blockDim.x)
+            for(uint32_t c = 0; c < r; ++c)
+                tri[r * (r - 1) / 2 + c] = uint16_t((r << 8) | c);
+        for(uint32_t i = lane; i < 32 * G_LD / 2; i += 32)
+            reinterpret_cast<uint32_t*>(gTile)[i] = 0u; // diagonal and padding stay zero
+        __syncthreads();
+
+        const uint32_t totalWarps = gridDim.x * NWARPS;
+        const uint32_t warpGlobal = blockIdx.x * NWARPS + warp;
+        const uint32_t myGroups
+            = warpGlobal < sh.numGroups ? (sh.numGroups - warpGlobal + totalWarps - 1) / totalWarps
+                                        : 0;
+        const uint32_t numQ = myGroups * GROUP;
+        const bool     twoM = sh.m > 16;
+
+        // Issues sample q; with the first sample of a group also the group's upstream rows.
+        auto issue = [&](uint32_t q) {
+            const uint32_t s = sampleOf(q, warpGlobal, totalWarps);
+            if(s >= sh.batch)
+                return;
+            issueSample(ringAddr + (q % NSTAGES) * sh.stageBytes, input + size_t(s) * sh.m * sh.k,
+                        sh, lane);
+            if(q % GROUP == 0)
+            {
+                uint8_t*       dst = upStage + ((q / GROUP) & 1u) * upBytes;
+                const uint32_t cnt = min(GROUP, sh.batch - s);
+                __half const*  src = upstream + size_t(s) * sh.outLen;
+                if(cnt == GROUP)
+                {
+                    for(uint32_t i = lane; i < sh.outLen; i += 32)
+                        cpAsync16(smemAddr(dst) + i * 16,
+                                  reinterpret_cast<uint8_t const*>(src) + size_t(i) * 16);
+                }
+                else
+                {
+                    for(uint32_t i = lane; i < cnt * sh.outLen; i += 32)
+                        reinterpret_cast<__half*>(dst)[i] = src[i];
+                }
+            }
+        };
+
+#pragma unroll
+        for(uint32_t q = 0; q < NSTAGES - 1; ++q)
+        {
+            if(q < numQ)
+                issue(q);
+            cpAsyncCommit();
+        }
+
+        const uint32_t lmRow = ((lane >> 3) & 1u) * 8u + (lane & 7u);
+        const uint32_t lmCol = (lane >> 4) * 8u;
+
+        for(uint32_t q = 0; q < numQ; ++q)
+        {
+            cpAsyncWait<NSTAGES - 2>();
+            __syncwarp();
+            if(q + NSTAGES - 1 < numQ)
+                issue(q + NSTAGES - 1);
+            cpAsyncCommit();
+
+            const uint32_t sample = sampleOf(q, warpGlobal, totalWarps);
+            if(sample >= sh.batch)
+                continue;
+            const uint32_t slot     = q % GROUP;
+            uint8_t*       slotPtr  = mine + (q % NSTAGES) * sh.stageBytes;
+            const uint32_t slotAddr = ringAddr + (q % NSTAGES) * sh.stageBytes;
+            __half const*  up = reinterpret_cast<__half const*>(upStage + ((q / GROUP) & 1u) * upBytes)
+                               + slot * sh.outLen;
+
+            // bottom-MLP gradient: the first k upstream values
+            for(uint32_t c = lane; c < sh.k / 8; c += 32)
+            {
+                alignas(16) __half v[8];
+#pragma unroll
+                for(uint32_t e = 0; e < 8; ++e)
+                    v[e] = up[c * 8 + e];
+                reinterpret_cast<uint4*>(mlpGrad + size_t(sample) * sh.k)[c]
+                    = *reinterpret_cast<uint4 const*>(v);
+            }
+
+            // symmetric G (fp16, zero diagonal) from the packed triangle
+            for(uint32_t i = lane; i < triCount; i += 32)
+            {
+                const uint32_t rc = tri[i], r = rc >> 8, c = rc & 0xffu;
+                const __half   v  = up[sh.k + i];
+                gTile[r * G_LD + c] = v;
+                gTile[c * G_LD + r] = v;
+            }
+            __syncwarp();
+
+            // A fragments of G: [mt][kt]
+            uint32_t ga[2][2][4];
+            ldmatrixX4(ga[0][0], gAddr + (lmRow * G_LD + lmCol) * 2);
+            if(twoM)
+            {
+                ldmatrixX4(ga[0][1], gAddr + (lmRow * G_LD + 16 + lmCol) * 2);
+                ldmatrixX4(ga[1][0], gAddr + ((16 + lmRow) * G_LD + lmCol) * 2);
+                ldmatrixX4(ga[1][1], gAddr + ((16 + lmRow) * G_LD + 16 + lmCol) * 2);
+            }
+
+            // B = X read k-row by k-row (transposing ldmatrix); rows >= m are zeros
+            const uint32_t kr0 = lmRow, kr1 = 16u + lmRow;
+            const uint32_t xb0 = kr0 < sh.m ? slotAddr + kr0 * sh.rowStride : zeroAddr;
+            const uint32_t xb1 = kr1 < sh.m ? slotAddr + kr1 * sh.rowStride : zeroAddr;
+
+            for(uint32_t n0 = 0; n0 < sh.k; n0 += 64)
+            {
+                const uint32_t pairs = min(4u, (sh.k - n0) / 16u); // 16 columns per ldmatrix.x4
+                float          acc[2][8][4];
+#pragma unroll
+                for(uint32_t a = 0; a < 2; ++a)
+#pragma unroll
+                    for(uint32_t b = 0; b < 8; ++b)
+#pragma unroll
+                        for(uint32_t e = 0; e < 4; ++e)
+                            acc[a][b][e] = 0.0f;
+#pragma unroll
+                for(uint32_t p = 0; p < 4; ++p)
+                {
+                    if(p < pairs)
+                    {
+                        uint32_t       xb[4];
+                        const uint32_t col = (n0 + p * 16u + lmCol) * 2u;
+                        ldmatrixX4Trans(xb, xb0 + col); // k rows 0..15
+                        mma16816(acc[0][2 * p], ga[0][0][0], ga[0][0][1], ga[0][0][2], ga[0][0][3],
+                                 xb[0], xb[1]);
+                        mma16816(acc[0][2 * p + 1], ga[0][0][0], ga[0][0][1], ga[0][0][2],
+                                 ga[0][0][3], xb[2], xb[3]);
+                        if(twoM)
+                        {
+                            mma16816(acc[1][2 * p], ga[1][0][0], ga[1][0][1], ga[1][0][2],
+                                     ga[1][0][3], xb[0], xb[1]);
+                            mma16816(acc[1][2 * p + 1], ga[1][0][0], ga[1][0][1], ga[1][0][2],
+                                     ga[1][0][3], xb[2], xb[3]);
+                            ldmatrixX4Trans(xb, xb1 + col); // k rows 16..31
+                            mma16816(acc[0][2 * p], ga[0][1][0], ga[0][1][1], ga[0][1][2],
+                                     ga[0][1][3], xb[0], xb[1]);
+                            mma16816(acc[0][2 * p + 1], ga[0][1][0], ga[0][1][1], ga[0][1][2],
+                                     ga[0][1][3], xb[2], xb[3]);
+                            mma16816(acc[1][2 * p], ga[1][1][0], ga[1][1][1], ga[1][1][2],
+                                     ga[1][1][3], xb[0], xb[1]);
+                            mma16816(acc[1][2 * p + 1], ga[1][1][0], ga[1][1][1], ga[1][1][2],
+                                     ga[1][1][3], xb[2], xb[3]);
+                        }
+                    }
+                }
+                // This column block of X is not needed any more: overwrite it with the result.
+                __syncwarp();
+#pragma unroll
+                for(uint32_t mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for(uint32_t nb = 0; nb < 8; ++nb)
+                    {
+                        if(nb < 2 * pairs && (mt == 0 || twoM))
+                        {
+#pragma unroll
+                            for(uint32_t h = 0; h < 2; ++h)
+                            {
+                                const uint32_t r = mt * 16u + g + 8u * h;
+                                const uint32_t c = n0 + nb * 8u + 2u * t;
+                                if(r < sh.m)
+                                    *reinterpret_cast<__half2*>(slotPtr + r * sh.rowStride + c * 2)
+                                        = __floats2half2_rn(acc[mt][nb][2 * h],
+                                                            acc[mt][nb][2 * h + 1]);
+                            }
+                        }
+                    }
+            }
+            __syncwarp();
+
+            // rows of the result leave with 128-bit stores (the sample is contiguous in grad)
+            {
+                const uint32_t chunksPerRow = sh.k / 8, total = sh.m * chunksPerRow;
+                uint4*         gdst = reinterpret_cast<uint4*>(grad + size_t(sample) * sh.m * sh.k);
+                for(uint32_t c = lane; c < total; c += 32)
+                {
+                    const uint32_t row = c / chunksPerRow, cc = c % chunksPerRow;
+                    gdst[c] = *reinterpret_cast<uint4 const*>(slotPtr + row * sh.rowStride + cc * 16);
+                }
+            }
+            __syncwarp();
+        }
+        cpAsyncWait<0>();
+    }
+
+    int checkShape(int dtype, void const* p0, void const* p1, uint32_t m, uint32_t k,
+                   uint32_t batch, Shape* sh)
+    {
+        if(!p0 || !p1 || m == 0 || k == 0 || batch == 0)
+            return B200WMMA_ERR_INVALID_ARG;
+        if(dtype != B200WMMA_F16)
+            return B200WMMA_ERR_UNSUPPORTED;
+        if(m > 32 || m < 2 || k % 16 != 0 || k > MAX_K)
+            return B200WMMA_ERR_UNSUPPORTED;
+        sh->m          = m;
+        sh->k          = k;
+        sh->batch      = batch;
+        sh->outLen     = k + m * (m - 1) / 2;
+        sh->rowStride  = 2 * k + 16;
+        sh->stageBytes = m * sh->rowStride;
+        sh->numGroups  = (batch + GROUP - 1) / GROUP;
+        return B200WMMA_OK;
+    }
+
+    inline bool aligned16(void const* p)
+    {
+        return reinterpret_cast<uintptr_t>(p) % 16 == 0;
+    }
+
+    constexpr uint32_t FWD_WARPS = 6, FWD_STAGES = 3;
+    constexpr uint32_t BWD_WARPS = 5, BWD_STAGES = 3;
+    constexpr uint32_t SMEM_LIMIT = 227 * 1024;
+} // namespace
+
+extern "C" int b200wmma_dlrm_fwd(int dtype, const void* input, void* output, uint32_t m, uint32_t k,
+                                 uint32_t batch, void* stream)
+{
+    Shape sh;
+    int   rc = checkShape(dtype, input, output, m, k, batch, &sh);
+    if(rc != B200WMMA_OK)
+        return rc;
+    if(!aligned16(input) || !aligned16(output))
+        return B200WMMA_ERR_ALIGNMENT;
+    const uint32_t perWarp = FWD_STAGES * sh.stageBytes + GROUP * sh.outLen * 2;
+    const uint32_t smemBytes = ZERO_BYTES + FWD_WARPS * perWarp;
+    if(smemBytes > SMEM_LIMIT)
+        return B200WMMA_ERR_UNSUPPORTED;
+    auto        kernel = dlrmFwdKernel<FWD_WARPS, FWD_STAGES>;
+    B200WMMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           int(smemBytes)));
+    const int sms = b200wmma::smCount();
+    if(sms <= 0)
+        return B200WMMA_ERR_CUDA;
+    const uint32_t wanted = (sh.numGroups + FWD_WARPS - 1) / FWD_WARPS;
+    const uint32_t grid   = wanted < uint32_t(sms) ? wanted : uint32_t(sms);
+    kernel<<<grid, FWD_WARPS * 32, smemBytes, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__half const*>(input), static_cast<__half*>(output), sh);
+    return b200wmma::cudaToStatus(cudaGetLastError());
+}
+
+extern "C" int b200wmma_dlrm_bwd(int dtype, const void* input, const void* upstream, void* grad,
+                                 void* mlp_grad, uint32_t m, uint32_t k, uint32_t batch,
+                                 void* stream)
+{
+    Shape sh;
+    int   rc = checkShape(dtype, input, upstream, m, k, batch, &sh);
+    if(rc != B200WMMA_OK)
+        return rc;
+    if(!grad || !mlp_grad)
+        return B200WMMA_ERR_INVALID_ARG;
+    if(!aligned16(input) || !aligned16(upstream) || !aligned16(grad) || !aligned16(mlp_grad))
+        return B200WMMA_ERR_ALIGNMENT;
+    const uint32_t triBytes = (m * (m - 1) / 2 * 2 + 15) / 16 * 16;
+    const uint32_t perWarp  = BWD_STAGES * sh.stageBytes + 2 * GROUP * sh.outLen * 2 + 32 * G_LD * 2;
+    const uint32_t smemBytes = ZERO_BYTES + triBytes + BWD_WARPS * perWarp;
+    if(smemBytes > SMEM_LIMIT)
+        return B200WMMA_ERR_UNSUPPORTED;
+    auto kernel = dlrmBwdKernel<BWD_WARPS, BWD_STAGES>;
+    B200WMMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           int(smemBytes)));
+    const int sms = b200wmma::smCount();
+    if(sms <= 0)
+        return B200WMMA_ERR_CUDA;
+    const uint32_t wanted = (sh.numGroups + BWD_WARPS - 1) / BWD_WARPS;
+    const uint32_t grid   = wanted < uint32_t(sms) ? wanted : uint32_t(sms);
+    kernel<<<grid, BWD_WARPS * 32, smemBytes, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__half const*>(input), static_cast<__half const*>(upstream),
+        static_cast<__half*>(grad), static_cast<__half*>(mlp_grad), sh);
+    return b200wmma::cudaToStatus(cudaGetLastError());
+}

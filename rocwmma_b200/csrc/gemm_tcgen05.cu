@@ -1,0 +1,637 @@
+// Block-cooperative GEMM for B200: D = alpha * A * B + beta * C.
+//
+// Rebuilds the reference's macro-tile GEMM (samples/perf_hgemm.cpp:518-714: 128x128
+// macro tile, cooperative global->LDS staging, two LDS buffers, one barrier per
+// 16-deep K step) as a persistent, warp-specialised sm_100a kernel:
+//
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A (128 x BK) and
+//               B (256 x BK) tiles into a 4-slot shared-memory ring (128-byte
+//               swizzle), one mbarrier pair (full/empty) per slot.  No multicast.
+//   warp 1      one elected thread issues tcgen05.mma (M=128, N=256) per 32-byte K
+//               step; accumulators live in tensor memory, two buffers of 256
+//               columns so the epilogue of tile i overlaps the MMAs of tile i+1.
+//   warps 2-5   epilogue: tcgen05.ld of the accumulator (one TMEM lane = one output
+//               row per thread), alpha/beta in the compute type, conversion, and
+//               128-bit stores along the row.
+//
+// A must be row-major and B column-major (both "K-major", what BASELINE's perf
+// configuration uses); other layouts are transposed into scratch first by
+// transposeInto().  Tiles at the M/N/K edges rely on TMA zero fill for loads and
+// on masks for stores.
+//
+// Every mbarrier wait is bounded; when one runs out the block raises an abort
+// flag, all roles leave their loops, tensor memory is released, and the kernel
+// records the event in the library's device status word.
+#include "common.cuh"
+#include "runtime.cuh"
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <mutex>
+#include <rocwmma/rocwmma_block.hpp>
+
+using namespace rocwmma;
+using namespace rocwmma::block;
+
+namespace
+{
+    constexpr uint32_t BM          = 128;
+    constexpr uint32_t BN          = 256;
+    constexpr uint32_t ROW_BYTES   = 128; // one swizzle row: BK * sizeof(InT)
+    constexpr uint32_t STAGES      = 4;
+    constexpr uint32_t A_BYTES     = BM * ROW_BYTES; // 16 KiB
+    constexpr uint32_t B_BYTES     = BN * ROW_BYTES; // 32 KiB
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t ACC_BUFS    = 2;
+    constexpr uint32_t TMEM_COLS   = ACC_BUFS * BN; // 512
+    constexpr uint32_t NUM_THREADS = 192;
+    constexpr uint32_t EPI_THREADS = 128;
+    constexpr uint32_t GROUP_M     = 16; // tile rows that share a band of B in L2
+
+    struct SharedControl
+    {
+        uint64_t   full[STAGES];
+        uint64_t   empty[STAGES];
+        uint64_t   accFull[ACC_BUFS];
+        uint64_t   accEmpty[ACC_BUFS];
+        uint32_t   tmemBase;
+        AbortState abort;
+    };
+    constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/
+                                    + sizeof(SharedControl) + 64;
+
+    struct GemmParams
+    {
+        uint32_t    m, n, k;
+        void const* c;
+        void*       d;
+        uint32_t    ldc, ldd;
+        double      alpha, beta;
+        uint32_t*   status;
+    };
+
+    template <typename T>
+    struct KindOf;
+    template <>
+    struct KindOf<__half>
+    {
+        static constexpr MmaKind  kind = MmaKind::F16;
+        static constexpr uint32_t fmt = FMT_F16, acc = ACC_F32;
+    };
+    template <>
+    struct KindOf<__nv_bfloat16>
+    {
+        static constexpr MmaKind  kind = MmaKind::F16;
+        static constexpr uint32_t fmt = FMT_BF16, acc = ACC_F32;
+    };
+    template <>
+    struct KindOf<float> // xfloat32_t storage
+    {
+        static constexpr MmaKind  kind = MmaKind::TF32;
+        static constexpr uint32_t fmt = FMT_TF32, acc = ACC_F32;
+    };
+    template <>
+    struct KindOf<int8_t>
+    {
+        static constexpr MmaKind  kind = MmaKind::I8;
+        static constexpr uint32_t fmt = FMT_S8, acc = ACC_S32;
+    };
+    template <>
+    struct KindOf<__nv_fp8_e4m3>
+    {
+        static constexpr MmaKind  kind = MmaKind::F8F6F4;
+        static constexpr uint32_t fmt = FMT_E4M3, acc = ACC_F32;
+    };
+
+    __device__ inline void tileCoord(uint32_t t, uint32_t tilesM, uint32_t tilesN, uint32_t& tm,
+                                     uint32_t& tn)
+    {
+        const uint32_t perGroup = GROUP_M * tilesN;
+        const uint32_t group    = t / perGroup;
+        const uint32_t firstM   = group * GROUP_M;
+        const uint32_t rows     = min(tilesM - firstM, GROUP_M);
+        const uint32_t r        = t % perGroup;
+        tm                      = firstM + r % rows;
+        tn                      = r / rows;
+    }
+
+    // alpha * acc + beta * c in the compute type, unfused like the host reference.
+    __device__ inline float scaleAdd(float alpha, float acc, float beta, float c)
+    {
+        return __fadd_rn(__fmul_rn(alpha, acc), __fmul_rn(beta, c));
+    }
+    __device__ inline int32_t scaleAdd(int32_t alpha, int32_t acc, int32_t beta, int32_t c)
+    {
+        return alpha * acc + beta * c;
+    }
+
+    template <typename OutT>
+    __device__ inline float toCompute(OutT v)
+    {
+        return float(v);
+    }
+    __device__ inline int32_t toCompute(int32_t v)
+    {
+        return v;
+    }
+    template <typename OutT, typename CompT>
+    __device__ inline OutT fromCompute(CompT v)
+    {
+        return OutT(v); // __half(float), __nv_bfloat16(float): round to nearest even
+    }
+
+    // Stores (and optionally reads C for) 32 consecutive columns of one output row.
+    template <typename OutT, typename CompT>
+    __device__ inline void epilogueRow(uint32_t const (&raw)[32], GemmParams const& p, CompT alpha,
+                                       CompT beta, bool useC, uint32_t row, uint32_t col0)
+    {
+        constexpr uint32_t VEC = 16 / sizeof(OutT); // elements per 128-bit access
+        OutT const*        cRow = static_cast<OutT const*>(p.c) + size_t(row) * p.ldc;
+        OutT*              dRow = static_cast<OutT*>(p.d) + size_t(row) * p.ldd;
+#pragma unroll
+        for(uint32_t v = 0; v < 32 / VEC; ++v)
+        {
+            const uint32_t col = col0 + v * VEC;
+            if(col >= p.n)
+                break;
+            alignas(16) OutT out[VEC];
+            alignas(16) OutT cin[VEC];
+            const bool       whole = (col + VEC <= p.n);
+            if(useC)
+            {
+                if(whole)
+                    *reinterpret_cast<uint4*>(cin) = *reinterpret_cast<uint4 const*>(cRow + col);
+                else
+                    for(uint32_t e = 0; e < VEC; ++e)
+                        cin[e] = (col + e < p.n) ? cRow[col + e] : OutT(0);
+            }
+#pragma unroll
+            for(uint32_t e = 0; e < VEC; ++e)
+            {
+                CompT acc;
+                if constexpr(std::is_same<CompT, float>::value)
+                    acc = __uint_as_float(raw[v * VEC + e]);
+                else
+                    acc = int32_t(raw[v * VEC + e]);
+                CompT r = useC ? scaleAdd(alpha, acc, beta, CompT(toCompute(cin[e])))
+                               : (std::is_same<CompT, float>::value
+                                      ? CompT(__fmul_rn(float(alpha), float(acc)))
+                                      : CompT(alpha * acc));
+                out[e]  = fromCompute<OutT, CompT>(r);
+            }
+            if(whole)
+                *reinterpret_cast<uint4*>(dRow + col) = *reinterpret_cast<uint4 const*>(out);
+            else
+                for(uint32_t e = 0; e < VEC; ++e)
+                    if(col + e < p.n)
+                        dRow[col + e] = out[e];
+        }
+    }
+
+    template <typename InT, typename OutT, typename CompT>
+    __global__ void __launch_bounds__(NUM_THREADS, 1)
+        gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmapA,
+                            const __grid_constant__ CUtensorMap tmapB,
+                            const GemmParams                    p)
+    {
+        constexpr uint32_t BK     = ROW_BYTES / sizeof(InT); // K elements per ring slot
+        constexpr uint32_t UMMA_K = 32 / sizeof(InT); // K elements per tcgen05.mma
+        constexpr uint32_t IDESC
+            = make_instr_desc(KindOf<InT>::acc, KindOf<InT>::fmt, KindOf<InT>::fmt, BM, BN);
+
+        extern __shared__ uint8_t smemRaw[];
+        const uint32_t            rawAddr = smem_addr(smemRaw);
+        uint8_t*       tiles = smemRaw + ((1024u - (rawAddr & 1023u)) & 1023u); // 1024-aligned
+        SharedControl* ctl   = reinterpret_cast<SharedControl*>(tiles + STAGES * STAGE_BYTES);
+
+        const uint32_t warp = threadIdx.x / 32;
+        const uint32_t lane = threadIdx.x % 32;
+
+        const uint32_t tilesM   = (p.m + BM - 1) / BM;
+        const uint32_t tilesN   = (p.n + BN - 1) / BN;
+        const uint32_t numTiles = tilesM * tilesN;
+        const uint32_t numKB    = (p.k + BK - 1) / BK;
+
+        if(threadIdx.x == 0)
+        {
+            for(uint32_t s = 0; s < STAGES; ++s)
+            {
+                mbar_init(&ctl->full[s], 1);
+                mbar_init(&ctl->empty[s], 1);
+            }
+            for(uint32_t b = 0; b < ACC_BUFS; ++b)
+            {
+                mbar_init(&ctl->accFull[b], 1);
+                mbar_init(&ctl->accEmpty[b], EPI_THREADS);
+            }
+            ctl->abort.flag = 0;
+            ctl->abort.code = 0;
+            mbar_init_fence();
+            tma_prefetch_descriptor(&tmapA);
+            tma_prefetch_descriptor(&tmapB);
+        }
+        if(warp == 1)
+        {
+            tmem_alloc(&ctl->tmemBase, TMEM_COLS);
+            tmem_relinquish_alloc_permit();
+        }
+        tc_fence_before_sync();
+        __syncthreads();
+        tc_fence_after_sync();
+        const uint32_t tmemBase = ctl->tmemBase;
+
+        if(warp == 0)
+        {
+            // ---------------- TMA producer ----------------
+            if(elect_one())
+            {
+                uint32_t it = 0;
+                bool     ok = true;
+                for(uint32_t t = blockIdx.x; ok && t < numTiles; t += gridDim.x)
+                {
+                    uint32_t tm, tn;
+                    tileCoord(t, tilesM, tilesN, tm, tn);
+                    for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
+                    {
+                        const uint32_t s  = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1u;
+                        if(!mbar_wait(&ctl->empty[s], ph ^ 1u, &ctl->abort, WAIT_STAGE_EMPTY))
+                        {
+                            ok = false;
+                            break;
+                        }
+                        uint8_t* slot = tiles + s * STAGE_BYTES;
+                        mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
+                        tma_load_2d(slot, &tmapA, &ctl->full[s], int32_t(kb * BK),
+                                    int32_t(tm * BM));
+                        tma_load_2d(slot + A_BYTES, &tmapB, &ctl->full[s], int32_t(kb * BK),
+                                    int32_t(tn * BN));
+                    }
+                }
+                if(!ok)
+                {
+                    // Leaving early: give copies already issued a bounded time to land
+                    // before the block's shared memory is released.
+                    const uint32_t pending = it < STAGES ? it : STAGES;
+                    for(uint32_t j = 0; j < pending; ++j)
+                    {
+                        const uint32_t prev = it - 1 - j;
+                        const uint32_t s    = prev % STAGES;
+                        const uint32_t ph   = (prev / STAGES) & 1u;
+                        const long long start = clock64();
+                        while(!mbar_try_wait(&ctl->full[s], ph) && clock64() - start < 2000000ll)
+                        {
+                        }
+                    }
+                }
+            }
+        }
+        else if(warp == 1)
+        {
+            // ---------------- MMA issuer ----------------
+            if(elect_one())
+            {
+                uint32_t it = 0, tileIter = 0;
+                bool     ok = true;
+                for(uint32_t t = blockIdx.x; ok && t < numTiles; t += gridDim.x, ++tileIter)
+                {
+                    const uint32_t buf   = tileIter & 1u;
+                    const uint32_t accPh = (tileIter >> 1) & 1u;
+                    if(!mbar_wait(&ctl->accEmpty[buf], accPh ^ 1u, &ctl->abort, WAIT_ACC_EMPTY))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t dTmem = tmemBase + buf * BN;
+                    for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
+                    {
+                        const uint32_t s  = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1u;
+                        if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
+                        {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t aAddr = smem_addr(tiles + s * STAGE_BYTES);
+                        const uint32_t bAddr = aAddr + A_BYTES;
+#pragma unroll
+                        for(uint32_t ks = 0; ks < BK / UMMA_K; ++ks)
+                        {
+                            const uint64_t da = smem_desc_kmajor_sw128(aAddr + ks * 32u);
+                            const uint64_t db = smem_desc_kmajor_sw128(bAddr + ks * 32u);
+                            mma_ss<KindOf<InT>::kind>(dTmem, da, db, IDESC, (kb | ks) != 0u);
+                        }
+                        mma_commit(&ctl->empty[s]); // slot reusable once these MMAs are done
+                    }
+                    if(ok)
+                        mma_commit(&ctl->accFull[buf]); // accumulator complete
+                }
+            }
+        }
+        else
+        {
+            // ---------------- epilogue ----------------
+            const uint32_t quad  = warp % 4; // TMEM lanes [32*quad, 32*quad+32)
+            const CompT    alpha = CompT(p.alpha);
+            const CompT    beta  = CompT(p.beta);
+            const bool     useC  = (p.beta != 0.0) && (p.c != nullptr);
+            uint32_t       tileIter = 0;
+            for(uint32_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileIter)
+            {
+                uint32_t tm, tn;
+                tileCoord(t, tilesM, tilesN, tm, tn);
+                const uint32_t buf   = tileIter & 1u;
+                const uint32_t accPh = (tileIter >> 1) & 1u;
+                if(!mbar_wait(&ctl->accFull[buf], accPh, &ctl->abort, WAIT_ACC_FULL))
+                    break;
+                tc_fence_after_sync();
+                const uint32_t row = tm * BM + quad * 32 + lane;
+#pragma unroll 1
+                for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+                {
+                    uint32_t       raw[32];
+                    __syncwarp(); // rows masked off below rejoin before the warp-wide load
+                    const uint32_t taddr = tmemBase + ((quad * 32u) << 16) + buf * BN + chunk * 32u;
+                    tmem_load_32x32b_x32(taddr, raw); // warp-wide: no divergence before it
+                    tmem_load_wait();
+                    const uint32_t col0 = tn * BN + chunk * 32;
+                    if(row < p.m && col0 < p.n)
+                        epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0);
+                }
+                tc_fence_before_sync();
+                mbar_arrive(&ctl->accEmpty[buf]);
+            }
+        }
+
+        // ---------------- teardown ----------------
+        tc_fence_before_sync();
+        __syncthreads();
+        if(warp == 1)
+        {
+            __syncwarp();
+            tc_fence_after_sync();
+            tmem_dealloc(tmemBase, TMEM_COLS);
+        }
+        if(threadIdx.x == 0 && ctl->abort.flag != 0u && p.status != nullptr)
+        {
+            atomicExch(&p.status[1], ctl->abort.code);
+            atomicExch(&p.status[0], 1u);
+        }
+    }
+
+    // ---- host side -----------------------------------------------------------------
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+    EncodeFn encoder()
+    {
+        static EncodeFn       fn = nullptr;
+        static std::once_flag once;
+        std::call_once(once, [] {
+            void*                           sym = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q)
+                   == cudaSuccess
+               && q == cudaDriverEntryPointSuccess)
+                fn = reinterpret_cast<EncodeFn>(sym);
+            else
+                (void)cudaGetLastError();
+        });
+        return fn;
+    }
+
+    // Tensor map of a K-major operand: `rows` rows of `k` elements, `ld` elements apart;
+    // box = one 128-byte swizzle row wide, boxRows tall.
+    int makeOperandMap(CUtensorMap* map, CUtensorMapDataType dt, size_t elemBytes, void const* base,
+                       uint32_t rows, uint32_t k, uint32_t ld, uint32_t boxRows)
+    {
+        EncodeFn fn = encoder();
+        if(!fn)
+            return B200WMMA_ERR_CUDA;
+        cuuint64_t dims[2]    = {k, rows};
+        cuuint64_t strides[1] = {cuuint64_t(ld) * elemBytes};
+        cuuint32_t box[2]     = {cuuint32_t(ROW_BYTES / elemBytes), boxRows};
+        cuuint32_t estr[2]    = {1, 1};
+        CUresult   r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS ? B200WMMA_OK : B200WMMA_ERR_CUDA;
+    }
+
+    template <typename InT, typename OutT, typename CompT>
+    int launch(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k, void const* a,
+               void const* b, void const* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+               uint32_t ldd, double alpha, double beta, cudaStream_t stream)
+    {
+        CUtensorMap mapA, mapB;
+        int         rc = makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, BM);
+        if(rc != B200WMMA_OK)
+            return rc;
+        rc = makeOperandMap(&mapB, dt, sizeof(InT), b, n, k, ldb, BN);
+        if(rc != B200WMMA_OK)
+            return rc;
+
+        auto              kernel = gemm_tcgen05_kernel<InT, OutT, CompT>;
+        static std::mutex attrMutex;
+        static bool       attrDone[64] = {};
+        {
+            // the opt-in shared-memory size is a per-device property of the kernel
+            std::lock_guard<std::mutex> lock(attrMutex);
+            int                         dev = 0;
+            B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
+            if(dev < 0 || dev >= 64 || !attrDone[dev])
+            {
+                B200WMMA_CUDA_TRY(cudaFuncSetAttribute(
+                    kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)));
+                if(dev >= 0 && dev < 64)
+                    attrDone[dev] = true;
+            }
+        }
+        const int sms = b200wmma::smCount();
+        if(sms <= 0)
+            return B200WMMA_ERR_CUDA;
+        const uint32_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+        const uint32_t grid  = tiles < uint32_t(sms) ? tiles : uint32_t(sms);
+
+        GemmParams p{m, n, k, c, d, ldc, ldd, alpha, beta, b200wmma::deviceStatusWord()};
+        kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(mapA, mapB, p);
+        return b200wmma::cudaToStatus(cudaGetLastError());
+    }
+
+    // out[c][r] = in[r][c]: turns an MN-major operand into the K-major form the
+    // tensor-core path reads.  rows x cols elements, 32x32 tiles through shared memory.
+    template <typename T>
+    __global__ void transposeKernel(T const* __restrict__ in, T* __restrict__ out, uint32_t rows,
+                                    uint32_t cols, uint32_t ldIn, uint32_t ldOut)
+    {
+        __shared__ T   tile[32][33];
+        const uint32_t c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+        for(uint32_t j = threadIdx.y; j < 32; j += blockDim.y)
+        {
+            const uint32_t r = r0 + j, c = c0 + threadIdx.x;
+            if(r < rows && c < cols)
+                tile[j][threadIdx.x] = in[size_t(r) * ldIn + c];
+        }
+        __syncthreads();
+        for(uint32_t j = threadIdx.y; j < 32; j += blockDim.y)
+        {
+            const uint32_t c = c0 + j, r = r0 + threadIdx.x;
+            if(r < rows && c < cols)
+                out[size_t(c) * ldOut + r] = tile[threadIdx.x][j];
+        }
+    }
+
+    template <typename T>
+    int transposeInto(T const* in, T* out, uint32_t rows, uint32_t cols, uint32_t ldIn,
+                      uint32_t ldOut, cudaStream_t stream)
+    {
+        dim3 block(32, 8);
+        dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+        transposeKernel<T><<<grid, block, 0, stream>>>(in, out, rows, cols, ldIn, ldOut);
+        return b200wmma::cudaToStatus(cudaGetLastError());
+    }
+
+    inline uint32_t roundUp(uint32_t v, uint32_t m)
+    {
+        return (v + m - 1) / m * m;
+    }
+
+    template <typename InT, typename OutT, typename CompT>
+    int run(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k, void const* a,
+            void const* b, void const* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+            uint32_t ldd, double alpha, double beta, int layoutA, int layoutB, cudaStream_t stream)
+    {
+        constexpr uint32_t E16 = 16 / sizeof(InT); // elements per 16 bytes
+        // A column-major / B row-major: bring them to K-major in scratch first.
+        if(layoutA == B200WMMA_COL_MAJOR || layoutB == B200WMMA_ROW_MAJOR)
+        {
+            const uint32_t kPad   = roundUp(k, E16);
+            const size_t   aBytes = layoutA == B200WMMA_COL_MAJOR ? size_t(m) * kPad * sizeof(InT) : 0;
+            const size_t   bBytes = layoutB == B200WMMA_ROW_MAJOR ? size_t(n) * kPad * sizeof(InT) : 0;
+            const size_t   aPad   = (aBytes + 255) / 256 * 256;
+            uint8_t* scratch = static_cast<uint8_t*>(b200wmma::deviceScratch(aPad + bBytes));
+            if(!scratch)
+                return B200WMMA_ERR_CUDA;
+            if(layoutA == B200WMMA_COL_MAJOR)
+            {
+                // stored as k rows of m (ld = lda); wanted: m rows of k
+                int rc = transposeInto(static_cast<InT const*>(a),
+                                       reinterpret_cast<InT*>(scratch), k, m, lda, kPad, stream);
+                if(rc != B200WMMA_OK)
+                    return rc;
+                a   = scratch;
+                lda = kPad;
+            }
+            if(layoutB == B200WMMA_ROW_MAJOR)
+            {
+                // stored as k rows of n (ld = ldb); wanted: n rows of k
+                int rc = transposeInto(static_cast<InT const*>(b),
+                                       reinterpret_cast<InT*>(scratch + aPad), k, n, ldb, kPad,
+                                       stream);
+                if(rc != B200WMMA_OK)
+                    return rc;
+                b   = scratch + aPad;
+                ldb = kPad;
+            }
+        }
+        auto misaligned = [](void const* ptr, uint32_t ld, size_t elem) {
+            return (reinterpret_cast<uintptr_t>(ptr) % 16) != 0 || (size_t(ld) * elem) % 16 != 0;
+        };
+        if(misaligned(a, lda, sizeof(InT)) || misaligned(b, ldb, sizeof(InT))
+           || misaligned(d, ldd, sizeof(OutT)) || (beta != 0.0 && misaligned(c, ldc, sizeof(OutT))))
+            return B200WMMA_ERR_ALIGNMENT;
+        if(lda < k || ldb < k || ldd < n || (beta != 0.0 && ldc < n))
+            return B200WMMA_ERR_INVALID_ARG;
+        return launch<InT, OutT, CompT>(dt, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+                                        stream);
+    }
+} // namespace
+
+namespace b200wmma
+{
+    // Implemented in gemm_f64.cu
+    int gemmF64(uint32_t m, uint32_t n, uint32_t k, double const* a, double const* b,
+                double const* c, double* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                double alpha, double beta, int layoutA, int layoutB, cudaStream_t stream);
+} // namespace b200wmma
+
+extern "C" int b200wmma_gemm(int in_dtype, int out_dtype, uint32_t m, uint32_t n, uint32_t k,
+                             const void* a, const void* b, const void* c, void* d, uint32_t lda,
+                             uint32_t ldb, uint32_t ldc, uint32_t ldd, double alpha, double beta,
+                             int layout_a, int layout_b, void* stream)
+{
+    if(!a || !b || !d || m == 0 || n == 0 || k == 0)
+        return B200WMMA_ERR_INVALID_ARG;
+    if(beta != 0.0 && !c)
+        return B200WMMA_ERR_INVALID_ARG;
+    if((layout_a != B200WMMA_ROW_MAJOR && layout_a != B200WMMA_COL_MAJOR)
+       || (layout_b != B200WMMA_ROW_MAJOR && layout_b != B200WMMA_COL_MAJOR))
+        return B200WMMA_ERR_INVALID_ARG;
+    auto s = static_cast<cudaStream_t>(stream);
+#define B200WMMA_GEMM_CASE(I, O, IT, OT, CT, TM)                                              \
+    if(in_dtype == I && out_dtype == O)                                                       \
+        return run<IT, OT, CT>(TM, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,      \
+                               layout_a, layout_b, s);
+    B200WMMA_GEMM_CASE(B200WMMA_F16, B200WMMA_F16, __half, __half, float,
+                       CU_TENSOR_MAP_DATA_TYPE_FLOAT16)
+    B200WMMA_GEMM_CASE(B200WMMA_F16, B200WMMA_F32, __half, float, float,
+                       CU_TENSOR_MAP_DATA_TYPE_FLOAT16)
+    B200WMMA_GEMM_CASE(B200WMMA_BF16, B200WMMA_F32, __nv_bfloat16, float, float,
+                       CU_TENSOR_MAP_DATA_TYPE_BFLOAT16)
+    B200WMMA_GEMM_CASE(B200WMMA_BF16, B200WMMA_BF16, __nv_bfloat16, __nv_bfloat16, float,
+                       CU_TENSOR_MAP_DATA_TYPE_BFLOAT16)
+    B200WMMA_GEMM_CASE(B200WMMA_XF32, B200WMMA_F32, float, float, float,
+                       CU_TENSOR_MAP_DATA_TYPE_FLOAT32)
+    B200WMMA_GEMM_CASE(B200WMMA_I8, B200WMMA_I32, int8_t, int32_t, int32_t,
+                       CU_TENSOR_MAP_DATA_TYPE_UINT8)
+    B200WMMA_GEMM_CASE(B200WMMA_E4M3, B200WMMA_BF16, __nv_fp8_e4m3, __nv_bfloat16, float,
+                       CU_TENSOR_MAP_DATA_TYPE_UINT8)
+    B200WMMA_GEMM_CASE(B200WMMA_E4M3, B200WMMA_F32, __nv_fp8_e4m3, float, float,
+                       CU_TENSOR_MAP_DATA_TYPE_UINT8)
+#undef B200WMMA_GEMM_CASE
+    if(in_dtype == B200WMMA_F64 && out_dtype == B200WMMA_F64)
+        return b200wmma::gemmF64(m, n, k, static_cast<double const*>(a),
+                                 static_cast<double const*>(b), static_cast<double const*>(c),
+                                 static_cast<double*>(d), lda, ldb, ldc, ldd, alpha, beta, layout_a,
+                                 layout_b, s);
+    return B200WMMA_ERR_UNSUPPORTED;
+}
+
+extern "C" int b200wmma_gemm_host(int in_dtype, int out_dtype, uint32_t m, uint32_t n, uint32_t k,
+                                  const void* a, const void* b, const void* c, void* d,
+                                  uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                                  double alpha, double beta, int layout_a, int layout_b,
+                                  void* stream)
+{
+    if(!a || !b || !d || m == 0 || n == 0 || k == 0 || (beta != 0.0 && !c))
+        return B200WMMA_ERR_INVALID_ARG;
+    const size_t inB = b200wmma::dtypeSize(in_dtype), outB = b200wmma::dtypeSize(out_dtype);
+    if(inB == 0 || outB == 0)
+        return B200WMMA_ERR_UNSUPPORTED;
+    auto         s      = static_cast<cudaStream_t>(stream);
+    const size_t aBytes = size_t(layout_a == B200WMMA_ROW_MAJOR ? m : k) * lda * inB;
+    const size_t bBytes = size_t(layout_b == B200WMMA_ROW_MAJOR ? k : n) * ldb * inB;
+    const size_t cBytes = beta != 0.0 ? size_t(m) * ldc * outB : 0;
+    const size_t dBytes = size_t(m) * ldd * outB;
+    void*        dA     = b200wmma::stagingBuffer(0, aBytes);
+    void*        dB     = b200wmma::stagingBuffer(1, bBytes);
+    void*        dC     = cBytes ? b200wmma::stagingBuffer(2, cBytes) : nullptr;
+    void*        dD     = b200wmma::stagingBuffer(3, dBytes);
+    if(!dA || !dB || !dD || (cBytes && !dC))
+        return B200WMMA_ERR_CUDA;
+    B200WMMA_CUDA_TRY(cudaMemcpyAsync(dA, a, aBytes, cudaMemcpyHostToDevice, s));
+    B200WMMA_CUDA_TRY(cudaMemcpyAsync(dB, b, bBytes, cudaMemcpyHostToDevice, s));
+    if(cBytes)
+        B200WMMA_CUDA_TRY(cudaMemcpyAsync(dC, c, cBytes, cudaMemcpyHostToDevice, s));
+    int rc = b200wmma_gemm(in_dtype, out_dtype, m, n, k, dA, dB, dC, dD, lda, ldb, ldc, ldd, alpha,
+                           beta, layout_a, layout_b, stream);
+    if(rc != B200WMMA_OK)
+        return rc;
+    B200WMMA_CUDA_TRY(cudaMemcpyAsync(d, dD, dBytes, cudaMemcpyDeviceToHost, s));
+    B200WMMA_CUDA_TRY(cudaStreamSynchronize(s));
+    return B200WMMA_OK;
+}

@@ -1,0 +1,200 @@
+// Per-device state shared by the launchers: the error word written by kernels
+// whose bounded waits ran out, cached device properties, staging buffers for
+// the host-buffer entry point, and the library-wide shutdown.
+#include "common.cuh"
+#include "runtime.cuh"
+#include <mutex>
+
+namespace b200wmma
+{
+    namespace
+    {
+        constexpr int MAX_DEVICES = 64;
+
+        struct DeviceState
+        {
+            uint32_t* status  = nullptr; // device uint32_t[4]
+            int       smCount = 0;
+            void*     scratch = nullptr; // general scratch (GEMV partial sums ...)
+            size_t    scratchBytes = 0;
+            void*     stage[4]      = {nullptr, nullptr, nullptr, nullptr}; // A, B, C, D staging
+            size_t    stageBytes[4] = {0, 0, 0, 0};
+        };
+
+        std::mutex  g_mutex;
+        DeviceState g_dev[MAX_DEVICES];
+
+        DeviceState* current()
+        {
+            int dev = -1;
+            if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+            {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+            return &g_dev[dev];
+        }
+    } // namespace
+
+    uint32_t* deviceStatusWord()
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceState*                st = current();
+        if(!st)
+            return nullptr;
+        if(!st->status)
+        {
+            if(cudaMalloc(&st->status, 4 * sizeof(uint32_t)) != cudaSuccess
+               || cudaMemset(st->status, 0, 4 * sizeof(uint32_t)) != cudaSuccess)
+            {
+                (void)cudaGetLastError();
+                st->status = nullptr;
+            }
+        }
+        return st->status;
+    }
+
+    int smCount()
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceState*                st = current();
+        if(!st)
+            return 0;
+        if(st->smCount == 0)
+        {
+            int dev = 0, n = 0;
+            if(cudaGetDevice(&dev) == cudaSuccess
+               && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess)
+                st->smCount = n;
+            else
+                (void)cudaGetLastError();
+        }
+        return st->smCount;
+    }
+
+    void* deviceScratch(size_t bytes)
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceState*                st = current();
+        if(!st)
+            return nullptr;
+        if(st->scratchBytes < bytes)
+        {
+            if(st->scratch)
+                (void)cudaFree(st->scratch);
+            st->scratch      = nullptr;
+            st->scratchBytes = 0;
+            if(cudaMalloc(&st->scratch, bytes) != cudaSuccess)
+            {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+            st->scratchBytes = bytes;
+        }
+        return st->scratch;
+    }
+
+    void* stagingBuffer(int slot, size_t bytes)
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceState*                st = current();
+        if(!st || slot < 0 || slot >= 4)
+            return nullptr;
+        if(st->stageBytes[slot] < bytes)
+        {
+            if(st->stage[slot])
+                (void)cudaFree(st->stage[slot]);
+            st->stage[slot]      = nullptr;
+            st->stageBytes[slot] = 0;
+            if(cudaMalloc(&st->stage[slot], bytes) != cudaSuccess)
+            {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+            st->stageBytes[slot] = bytes;
+        }
+        return st->stage[slot];
+    }
+} // namespace b200wmma
+
+using namespace b200wmma;
+
+extern "C" {
+
+int b200wmma_version(void)
+{
+    return 10700; // tracks the rocWMMA API level 1.7.0 this library mirrors
+}
+
+const char* b200wmma_status_string(int status)
+{
+    switch(status)
+    {
+    case B200WMMA_OK:
+        return "ok";
+    case B200WMMA_ERR_INVALID_ARG:
+        return "invalid argument";
+    case B200WMMA_ERR_UNSUPPORTED:
+        return "unsupported type, layout or shape";
+    case B200WMMA_ERR_ALIGNMENT:
+        return "pointer or leading dimension is not 16-byte aligned";
+    case B200WMMA_ERR_CUDA:
+        return "CUDA call failed (is a B200 visible?)";
+    case B200WMMA_ERR_DEVICE_WAIT:
+        return "a bounded wait inside a kernel ran out";
+    case B200WMMA_ERR_TOO_LARGE:
+        return "size beyond the documented maximum";
+    }
+    return "unknown status";
+}
+
+int b200wmma_check_device(void* stream, uint32_t* detail)
+{
+    B200WMMA_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    uint32_t* word = deviceStatusWord();
+    if(!word)
+        return B200WMMA_ERR_CUDA;
+    uint32_t host[4] = {0, 0, 0, 0};
+    B200WMMA_CUDA_TRY(cudaMemcpy(host, word, sizeof(host), cudaMemcpyDeviceToHost));
+    if(detail)
+        *detail = host[1];
+    if(host[0] != 0)
+    {
+        B200WMMA_CUDA_TRY(cudaMemset(word, 0, sizeof(host)));
+        return B200WMMA_ERR_DEVICE_WAIT;
+    }
+    return B200WMMA_OK;
+}
+
+int b200wmma_shutdown(void)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int                         prev = -1;
+    (void)cudaGetDevice(&prev);
+    for(int d = 0; d < MAX_DEVICES; ++d)
+    {
+        DeviceState& st = g_dev[d];
+        bool any = st.status || st.scratch || st.stage[0] || st.stage[1] || st.stage[2]
+                   || st.stage[3];
+        if(!any)
+            continue;
+        if(cudaSetDevice(d) != cudaSuccess)
+        {
+            (void)cudaGetLastError();
+            continue;
+        }
+        if(st.status)
+            (void)cudaFree(st.status);
+        if(st.scratch)
+            (void)cudaFree(st.scratch);
+        for(void*& p : st.stage)
+            if(p)
+                (void)cudaFree(p);
+        st = DeviceState{};
+    }
+    if(prev >= 0)
+        (void)cudaSetDevice(prev);
+    (void)cudaGetLastError();
+    return B200WMMA_OK;
+}
+}

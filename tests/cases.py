@@ -1,0 +1,74 @@
+"""Shared test cases and seeded input builders (host side, numpy)."""
+from __future__ import annotations
+
+import numpy as np
+
+from rocwmma_b200 import synth
+from rocwmma_b200.synth import BF16, E4M3, F16, F32, F64, I8, I32, XF32
+
+ROW, COL = 0, 1
+
+# Tolerances on max |a-b| / (|a|+|b|+1) per input type: bit-exact for i8 -> i32.
+TOLERANCE = {F16: 2e-3, BF16: 2e-3, E4M3: 1e-2, I8: 0.0, F32: 1e-4, XF32: 1e-4, F64: 1e-12}
+
+# (input type, output type) pairs of the simple (per-warp) GEMM
+SIMPLE_PAIRS = [(F16, F32), (F16, F16), (BF16, F32), (BF16, BF16), (E4M3, F32), (I8, I32),
+                (F32, F32), (XF32, F32), (F64, F64)]
+# pairs of the block-cooperative GEMM
+BLOCK_PAIRS = [(F16, F16), (F16, F32), (BF16, F32), (BF16, BF16), (XF32, F32), (I8, I32),
+               (E4M3, BF16), (E4M3, F32), (F64, F64)]
+
+
+def _dist(dt):
+    return {"dist": "int8"} if dt == I8 else ({"dist": "int32"} if dt == I32 else
+                                              {"dist": "uniform"})
+
+
+def gemm_inputs(case):
+    """A (m x k), B (k x n), C (m x n) as flat storage in the case's layouts.
+
+    The generator produces logical rows; a column-major operand is the
+    transposed storage of the same logical matrix."""
+    m, n, k, seed = case["m"], case["n"], case["k"], case["seed"]
+    it, ot = case["in_t"], case["out_t"]
+    dist = case.get("dist")
+    kw_in = {"dist": dist} if dist else _dist(it)
+    kw_out = {"dist": dist} if dist else _dist(ot)
+    a = synth.rows(seed, 1, it, 0, m, k, **kw_in)            # logical m x k
+    bt = synth.rows(seed, 2, it, 0, n, k, **kw_in)           # logical B^T: n x k
+    c = synth.rows(seed, 3, ot, 0, m, n, **kw_out)
+    a_st = a if case["la"] == ROW else np.ascontiguousarray(a.T)
+    b_st = bt if case["lb"] == COL else np.ascontiguousarray(bt.T)
+    return a_st.reshape(-1), b_st.reshape(-1), c.reshape(-1)
+
+
+def _case(in_t, out_t, m, n, k, la, lb, alpha, beta, seed, **kw):
+    d = dict(in_t=in_t, out_t=out_t, m=m, n=n, k=k, la=la, lb=lb, alpha=alpha, beta=beta,
+             seed=seed)
+    d.update(kw)
+    return d
+
+
+# Cases whose outputs are stored in tests/golden/gemm_ref_outputs.npz (made by the
+# reference's own gemm_CPU).  e4m3 and bf16 OUTPUT are absent: the reference's host code
+# for them lives in HIP headers outside its tree.
+GEMM_GOLDEN_CASES = {}
+for _it, _ot in [(F16, F32), (F16, F16), (BF16, F32), (I8, I32), (F32, F32), (XF32, F32),
+                 (F64, F64)]:
+    for _la, _lb in [(ROW, COL), (COL, ROW), (ROW, ROW), (COL, COL)]:
+        _ab = (1, 1) if _it == I8 else (2.0, -1.0)
+        GEMM_GOLDEN_CASES[f"t{_it}_{_ot}_l{_la}{_lb}"] = _case(_it, _ot, 48, 32, 64, _la, _lb,
+                                                            _ab[0], _ab[1], seed=100 + _it)
+
+
+def gemv_inputs(m, k, seed):
+    a = synth.rows(seed, 1, F32, 0, k, m).reshape(-1)   # column-major m x k = k rows of m
+    x = synth.rows(seed, 2, F32, 0, 1, k).reshape(-1)
+    y = synth.rows(seed, 3, F32, 0, 1, m).reshape(-1)
+    return a, x, y
+
+
+def dlrm_inputs(m, k, batch, seed):
+    x = synth.rows(seed, 1, F16, 0, batch, m * k, dist="normal").reshape(-1)
+    up = synth.rows(seed, 2, F16, 0, batch, k + m * (m - 1) // 2, dist="normal").reshape(-1)
+    return x, up

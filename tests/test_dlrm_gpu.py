@@ -1,0 +1,83 @@
+"""Fused DLRM dot-interaction forward/backward through the C ABI against the reference's
+stored known-answer vectors, stored reference outputs and the oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from rocwmma_b200 import api
+from tests.cases import dlrm_inputs
+from tests.gpu_util import to_device
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def _fwd(x, m, k, b):
+    return api.dlrm_fwd(to_device(x, O.F16), m, k, b).cpu().numpy()
+
+
+def _bwd(x, up, m, k, b):
+    mlp, grad = api.dlrm_bwd(to_device(x, O.F16), to_device(up, O.F16), m, k, b)
+    return mlp.cpu().numpy(), grad.cpu().numpy()
+
+
+def test_reference_known_answer_vectors(golden_dir):
+    f = np.load(os.path.join(golden_dir, "dlrm_reference_fixture.npz"))
+    x, up = f["input_fp16"], f["input_grad_fp16"]
+    b = x.size // (27 * 128)
+    out = _fwd(x, 27, 128, b)
+    assert 0 <= O.max_rel_err(O.F16, out, f["output_fp16"]) <= TOL
+    mlp, grad = _bwd(x, up, 27, 128, b)
+    assert np.array_equal(mlp.view(np.uint16), f["output_mlp_input_grad_fp16"].view(np.uint16))
+    assert 0 <= O.max_rel_err(O.F16, grad, f["output_input_grad_fp16"]) <= TOL
+
+
+def test_stored_reference_outputs(golden_dir):
+    g = np.load(os.path.join(golden_dir, "dlrm_ref_outputs.npz"))
+    x, up = dlrm_inputs(27, 128, 9, seed=4)       # 9 = one full group of 8 + a tail of 1
+    assert 0 <= O.max_rel_err(O.F16, _fwd(x, 27, 128, 9), g["fwd"]) <= TOL
+    mlp, grad = _bwd(x, up, 27, 128, 9)
+    assert np.array_equal(mlp.view(np.uint16), g["mlp"].view(np.uint16))
+    assert 0 <= O.max_rel_err(O.F16, grad, g["grad"]) <= TOL
+
+
+@pytest.mark.parametrize("m,k,b", [(27, 128, 1), (27, 128, 7), (27, 128, 64), (27, 128, 1003),
+                                   (32, 128, 64), (16, 64, 40), (5, 16, 17), (32, 256, 24),
+                                   (2, 32, 8)])
+def test_shapes_against_oracle(m, k, b):
+    x, up = dlrm_inputs(m, k, b, seed=7)
+    want = O.dlrm_fwd(O.F16, x, m, k, b)
+    assert 0 <= O.max_rel_err(O.F16, _fwd(x, m, k, b), want) <= TOL
+    wmlp, wgrad = O.dlrm_bwd(O.F16, x, up, m, k, b)
+    mlp, grad = _bwd(x, up, m, k, b)
+    assert np.array_equal(mlp.view(np.uint16), wmlp.view(np.uint16))
+    assert 0 <= O.max_rel_err(O.F16, grad, wgrad) <= TOL
+
+
+def test_config_batch_65536():
+    """Full configuration: batch 65536, 27 x 128.  Exact copies are checked everywhere,
+    the products on a sample of the batch."""
+    m, k, b = 27, 128, 65536
+    out_len = k + m * (m - 1) // 2
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(b * m * k, generator=g, device="cuda", dtype=torch.float32).half()
+    up = torch.randn(b * out_len, generator=g, device="cuda", dtype=torch.float32).half()
+    out = api.dlrm_fwd(x, m, k, b)
+    mlp, grad = api.dlrm_bwd(x, up, m, k, b)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(b, out_len)[:, :k], x.view(b, m, k)[:, 0, :])
+    assert torch.equal(mlp.view(b, k), up.view(b, out_len)[:, :k])
+    pick = torch.tensor(sorted({0, 7, 8, b - 1, b - 8, 12345, 40000, 65535 // 2}), device="cuda")
+    xs = x.view(b, m * k)[pick].cpu().numpy().reshape(-1)
+    ups = up.view(b, out_len)[pick].cpu().numpy().reshape(-1)
+    n = pick.numel()
+    want = O.dlrm_fwd(O.F16, xs, m, k, n)
+    got = out.view(b, out_len)[pick].cpu().numpy().reshape(-1)
+    assert 0 <= O.max_rel_err(O.F16, got, want) <= TOL
+    _, wgrad = O.dlrm_bwd(O.F16, xs, ups, m, k, n)
+    ggrad = grad.view(b, m * k)[pick].cpu().numpy().reshape(-1)
+    assert 0 <= O.max_rel_err(O.F16, ggrad, wgrad) <= TOL
+    assert torch.isfinite(out.float()).all() and torch.isfinite(grad.float()).all()

@@ -1,0 +1,151 @@
+"""Block-cooperative GEMM (TMA + tcgen05 + TMEM; fp64 on the warp-level path) through
+the C ABI against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from rocwmma_b200 import api, synth
+from tests.cases import BLOCK_PAIRS, TOLERANCE, gemm_inputs
+from tests.gpu_util import to_device, to_host
+
+pytestmark = pytest.mark.gpu
+ROW, COL = 0, 1
+
+
+def _run(case, with_c=True):
+    a, b, c = gemm_inputs(case)
+    m, n, k = case["m"], case["n"], case["k"]
+    want = O.gemm(case["in_t"], case["out_t"], m, n, k, a, b, c, case["alpha"], case["beta"],
+                  case["la"], case["lb"])
+    out = torch.full((m * n,), float("nan") if case["out_t"] != O.I32 else -7,
+                     dtype=api.torch_dtype(case["out_t"]), device="cuda")
+    got = api.gemm(case["in_t"], case["out_t"], m, n, k, to_device(a, case["in_t"]),
+                   to_device(b, case["in_t"]), to_device(c, case["out_t"]) if with_c else None,
+                   case["alpha"], case["beta"], case["la"], case["lb"], out=out)
+    api.check_device()
+    return to_host(got, case["out_t"]), want
+
+
+def _ab(in_t):
+    return (2, -1) if in_t == O.I8 else (2.0, -1.0)
+
+
+@pytest.mark.parametrize("in_t,out_t", BLOCK_PAIRS)
+def test_block_gemm_full_tiles(in_t, out_t):
+    al, be = _ab(in_t)
+    case = dict(in_t=in_t, out_t=out_t, m=256, n=512, k=512, la=ROW, lb=COL, alpha=al, beta=be,
+                seed=40 + in_t)
+    got, want = _run(case)
+    err = O.max_rel_err(out_t, got, want)
+    assert 0 <= err <= TOLERANCE[in_t], err
+
+
+@pytest.mark.parametrize("in_t,out_t", BLOCK_PAIRS)
+@pytest.mark.parametrize("m,n,k", [(200, 136, 272), (1, 8, 16), (129, 257, 48), (384, 1000, 1040)])
+def test_block_gemm_ragged_edges(in_t, out_t, m, n, k):
+    """Sizes that are not tile multiples: loads are zero-filled, stores masked."""
+    al, be = _ab(in_t)
+    case = dict(in_t=in_t, out_t=out_t, m=m, n=n, k=k, la=ROW, lb=COL, alpha=al, beta=be,
+                seed=50 + in_t)
+    got, want = _run(case)
+    err = O.max_rel_err(out_t, got, want)
+    assert 0 <= err <= TOLERANCE[in_t], err
+
+
+@pytest.mark.parametrize("in_t,out_t", [(O.F16, O.F16), (O.I8, O.I32), (O.XF32, O.F32),
+                                        (O.F64, O.F64)])
+@pytest.mark.parametrize("la,lb", [(COL, ROW), (ROW, ROW), (COL, COL)])
+def test_block_gemm_other_layouts(in_t, out_t, la, lb):
+    al, be = _ab(in_t)
+    case = dict(in_t=in_t, out_t=out_t, m=256, n=256, k=192, la=la, lb=lb, alpha=al, beta=be,
+                seed=60 + in_t)
+    got, want = _run(case)
+    assert 0 <= O.max_rel_err(out_t, got, want) <= TOLERANCE[in_t]
+
+
+def test_beta_zero_never_reads_c():
+    case = dict(in_t=O.F16, out_t=O.F16, m=256, n=256, k=128, la=ROW, lb=COL, alpha=1.0, beta=0.0,
+                seed=70)
+    got, want = _run(case, with_c=False)
+    assert 0 <= O.max_rel_err(O.F16, got, want) <= 2e-3
+
+
+def test_integer_pattern_inputs_are_exact():
+    for in_t, out_t in BLOCK_PAIRS:
+        case = dict(in_t=in_t, out_t=out_t, m=256, n=256, k=256, la=ROW, lb=COL, alpha=1, beta=1,
+                    seed=5, dist="pattern")
+        got, want = _run(case)
+        assert O.max_rel_err(out_t, got, want) == 0.0, (in_t, out_t)
+
+
+def test_padded_leading_dimensions_leave_padding_untouched():
+    """Contamination check: D has ldd > n; the columns beyond n must keep their fill."""
+    m, n, k = 256, 200, 128
+    lda, ldb, ldd = k + 8, k + 16, n + 8
+    rng = np.random.default_rng(3)
+    A = rng.uniform(-1, 1, (m, k)).astype(np.float16)
+    Bt = rng.uniform(-1, 1, (n, k)).astype(np.float16)
+    a = np.zeros((m, lda), np.float16); a[:, :k] = A
+    b = np.zeros((n, ldb), np.float16); b[:, :k] = Bt
+    c = np.zeros(m * n, np.float16)
+    want = O.gemm(O.F16, O.F16, m, n, k, A.reshape(-1), Bt.reshape(-1), c, 1.0, 0.0)
+    out = torch.full((m * ldd,), 777.0, dtype=torch.float16, device="cuda")
+    api.gemm(O.F16, O.F16, m, n, k, to_device(a.reshape(-1), O.F16), to_device(b.reshape(-1), O.F16),
+             None, 1.0, 0.0, lda=lda, ldb=ldb, ldd=ldd, out=out)
+    api.check_device()
+    got = out.cpu().numpy().reshape(m, ldd)
+    assert (got[:, n:] == 777.0).all()
+    assert 0 <= O.max_rel_err(O.F16, np.ascontiguousarray(got[:, :n]).reshape(-1), want) <= 2e-3
+
+
+def test_misaligned_arguments_are_refused():
+    t = torch.zeros(1 << 16, dtype=torch.float16, device="cuda")
+    with pytest.raises(api.B200WmmaError) as e:
+        api.gemm(O.F16, O.F16, 128, 128, 100, t, t, None, 1, 0, lda=100, ldb=100)  # 200-byte rows
+    assert e.value.status == -3
+    with pytest.raises(api.B200WmmaError) as e:
+        api.gemm(O.F16, O.F16, 128, 128, 128, t[1:], t, None, 1, 0)
+    assert e.value.status == -3
+
+
+def _rows_check(in_t, out_t, size, seed, alpha, beta, tol, nrows=24):
+    """Full-size problem, validated on a sample of rows (the oracle needs ~minutes for all)."""
+    m = n = k = size
+    kw = {"dist": "int8"} if in_t == O.I8 else {}
+    a = synth.rows(seed, 1, in_t, 0, m, k, **kw)
+    bt = synth.rows(seed, 2, in_t, 0, n, k, **kw)
+    d = api.gemm(in_t, out_t, m, n, k, to_device(a.reshape(-1), in_t),
+                 to_device(bt.reshape(-1), in_t), None, alpha, beta)
+    api.check_device()
+    got = to_host(d, out_t).reshape(m, n)
+    pick = np.unique(np.concatenate([[0, 127, 128, m - 1],
+                                     np.random.default_rng(seed).integers(0, m, nrows)]))
+    c0 = np.zeros(pick.size * n, dtype=O.np_dtype(out_t))
+    want = O.gemm(in_t, out_t, pick.size, n, k, np.ascontiguousarray(a[pick]).reshape(-1),
+                  bt.reshape(-1), c0, alpha, beta)
+    err = O.max_rel_err(out_t, np.ascontiguousarray(got[pick]).reshape(-1), want)
+    assert 0 <= err <= tol, err
+    return got
+
+
+def test_config_perf_hgemm_8192():
+    """M=N=K=8192, fp16 A row / B col, fp32 accumulate, fp16 D, alpha=1, beta=0."""
+    _rows_check(O.F16, O.F16, 8192, 1, 1.0, 0.0, 2e-3)
+
+
+def test_config_int8_8192_bit_exact():
+    _rows_check(O.I8, O.I32, 8192, 3, 1, 0, 0.0)
+
+
+def test_linearity_at_full_size():
+    """Size-independent property: gemm(A, B; alpha=2) == 2 * gemm(A, B; alpha=1) exactly
+    (scaling by 2 commutes with fp16 rounding), on 4096^3."""
+    m = n = k = 4096
+    a = to_device(synth.matrix(2, 1, O.F16, m, k), O.F16)
+    b = to_device(synth.matrix(2, 2, O.F16, n, k), O.F16)
+    d1 = api.gemm(O.F16, O.F32, m, n, k, a, b, None, 1.0, 0.0)
+    d2 = api.gemm(O.F16, O.F32, m, n, k, a, b, None, 2.0, 0.0)
+    api.check_device()
+    assert torch.equal(d2, 2 * d1)
+    assert torch.isfinite(d1).all()
