@@ -1,0 +1,341 @@
+#!/usr/bin/env python
+"""Headline benchmark: hgemm 8192^3 (fp16 A row-major, fp16 B col-major, fp32 accumulate,
+fp16 D, alpha = 1, beta = 0) in TFLOP/s on N B200s of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one pass of the block-cooperative GEMM over the whole problem.  With N > 1 the
+rows of A and D are split evenly over the ranks (B replicated, no collective in the timed
+region), so the total work is fixed: strong scaling.  Prints ONE JSON line on rank 0.
+
+`value`    device-resident throughput: 2*M*N*K*steps / time of the K launches (CUDA events
+           on the launching stream, max over ranks).
+`e2e`      the same metric through the C ABI's host-buffer entry point
+           (b200wmma_gemm_host): pinned host A, B -> device, kernel, D -> host, every step.
+`roofline` tensor-bound: achieved TFLOP/s of the kernel against the measured dense bf16/fp16
+           peak of this pool (MEASURED_PEAKS.json, burst figure: the kernel is timed alone).
+`cpu_baseline`  the reference's own OpenMP host GEMM (oracle/_ref, else the oracle port) on
+           a bounded sample of rows of the same problem, on the host cores; the same rows
+           of the GPU result are checked against it.
+
+--impl reference times only that CPU implementation, on the same config and metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M = N = K = 8192
+SEED = 1
+WORKLOAD = ("perf_hgemm 8192^3: fp16 A row-major, fp16 B col-major, fp32 accumulate, fp16 D, "
+            "alpha=1, beta=0")
+METRIC = "hgemm 8192^3 TFLOP/s"
+FALLBACK_PEAK_TFLOPS = 1590.0
+# dram bytes per launch of the GEMM kernel from the ncu capture summarised under profiles/
+# (None until a capture exists for the current kernel)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)", p
+    except Exception:
+        return FALLBACK_PEAK_TFLOPS, "fallback (no MEASURED_PEAKS.json)", {}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs
+    (read-only NVML queries)."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+
+    def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+            return
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self):
+        nv = self._nvml
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=1.0)
+        med = None
+        if self.samples:
+            s = sorted(self.samples)
+            med = s[len(s) // 2]
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            pass
+    return local_rank
+
+
+def cpu_reference_sample(rows_budget_s: float, a_rows_fn, bt, want_rows=None):
+    """Times the reference's host GEMM on a sample of rows of the 8192^3 problem.
+    Returns (tflops, info, rows_idx, d_rows)."""
+    import numpy as np
+
+    import oracle as O
+    use_ref = O.ref() is not None
+    kind = "reference" if use_ref else "port"
+
+    def run(a_rows):
+        nrows = a_rows.shape[0]
+        c0 = np.zeros(nrows * N, dtype=np.float16)
+        t0 = time.perf_counter()
+        if use_ref:
+            d = O.ref_gemm(O.F16, O.F16, nrows, N, K, np.ascontiguousarray(a_rows).reshape(-1), bt,
+                           c0, 1.0, 0.0)
+        else:
+            d = O.gemm(O.F16, O.F16, nrows, N, K, np.ascontiguousarray(a_rows).reshape(-1), bt, c0,
+                       1.0, 0.0)
+        return d, time.perf_counter() - t0
+
+    threads = O.num_threads()
+    probe_rows = max(threads, 8)
+    _, t_probe = run(a_rows_fn(probe_rows))
+    rate = probe_rows / max(t_probe, 1e-6)  # rows per second
+    nrows = int(max(probe_rows, min(2048, rate * rows_budget_s)))
+    nrows = max(threads, nrows // threads * threads)
+    a_rows = a_rows_fn(nrows)
+    d, t = run(a_rows)
+    tflops = 2.0 * nrows * N * K / t / 1e12
+    info = {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+            "sample": f"first {nrows} rows of A x all of B ({nrows}x{N}x{K}), "
+                      f"{t:.1f} s of {'rocWMMA gemm_CPU (OpenMP)' if use_ref else 'the oracle port'}"}
+    return tflops, info, nrows, d
+
+
+def run_reference_arm(args, rank, world):
+    """--impl reference: the reference's own CPU GEMM for this path on the host cores."""
+    if rank != 0:
+        return
+    import numpy as np
+
+    from rocwmma_b200 import synth
+    bt = synth.matrix(SEED, 2, synth.F16, N, K)
+    a_cache = {}
+
+    def a_rows(n):
+        if n not in a_cache:
+            a_cache[n] = synth.rows(SEED, 1, synth.F16, 0, (n + 127) // 128 * 128, K)[:n]
+        return a_cache[n]
+
+    # each step is a bounded sample; the whole run stays within a few minutes
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    budget = min(10.0, 120.0 / (steps + warmup))
+    vals, info, rows = [], None, 0
+    for i in range(warmup + steps):
+        tf, info, rows, _ = cpu_reference_sample(budget, a_rows, bt)
+        if i >= warmup:
+            vals.append(tf)
+    value = sum(vals) / len(vals)
+    ms = 2.0 * rows * N * K / (value * 1e12) * 1e3
+    info["value"] = value
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "seed": SEED},
+            "cpu_baseline": info,
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=None,
+                    help="steps of the host-buffer measurement (default: min(steps, 10))")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from rocwmma_b200 import api, synth
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
+    assert M % (world * synth.CHUNK_ROWS) == 0
+
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+    m_local = M // world
+    row0 = rank * m_local
+
+    # ---- synthetic inputs (seeded; every rank regenerates its own rows of A, all of B) ----
+    a_host = torch.from_numpy(synth.rows(SEED, 1, synth.F16, row0, m_local, K)).pin_memory()
+    b_host = torch.from_numpy(synth.rows(SEED, 2, synth.F16, 0, N, K)).pin_memory()
+    d_host = torch.empty((m_local, N), dtype=torch.float16).pin_memory()
+    a_dev = a_host.cuda(non_blocking=True)
+    b_dev = b_host.cuda(non_blocking=True)
+    d_dev = torch.empty(m_local * N, dtype=torch.float16, device="cuda")
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        api.gemm(api.F16, api.F16, m_local, N, K, a_dev, b_dev, None, 1.0, 0.0, out=d_dev)
+
+    stream = torch.cuda.current_stream()
+
+    # ---- device-resident measurement ----
+    for _ in range(warmup):
+        step()
+    api.check_device()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    api.check_device()
+    ms_total = e0.elapsed_time(e1)
+
+    # ---- end to end through the host-buffer C entry point ----
+    e2e_steps = args.e2e_steps if args.e2e_steps is not None else min(steps, 10)
+    for _ in range(2):
+        api.gemm_host(api.F16, api.F16, m_local, N, K, a_host, b_host, None, d_host, 1.0, 0.0)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(e2e_steps):
+        api.gemm_host(api.F16, api.F16, m_local, N, K, a_host, b_host, None, d_host, 1.0, 0.0)
+    f1.record(stream)
+    barrier()
+    e2e_ms_total = f0.elapsed_time(f1)
+
+    if world > 1:
+        t = torch.tensor([ms_total, e2e_ms_total], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms_total = t.tolist()
+
+    flops = 2.0 * M * N * K
+    ms_per_step = ms_total / steps
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    e2e_ms = e2e_ms_total / e2e_steps
+    e2e_value = flops / (e2e_ms * 1e-3) / 1e12
+
+    # ---- roofline of the dominant (only) kernel: this rank's launch ----
+    peak, peak_src, _ = measured_peaks()
+    kernel_tflops = 2.0 * m_local * N * K / (ms_per_step * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
+                "frac": kernel_tflops / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "peak_source": peak_src, "kernel": "gemm_tcgen05_kernel<half,half,float>",
+                "algorithmic_flops_per_launch": 2.0 * m_local * N * K}
+
+    # ---- CPU baseline (rank 0, N = 1 only) + parity of the same rows ----
+    cpu_info = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle as O
+        a_np, b_np = a_host.numpy(), b_host.numpy().reshape(-1)
+        _, cpu_info, nrows, d_cpu = cpu_reference_sample(10.0, lambda n: a_np[:n], b_np)
+        d_gpu = d_dev.view(m_local, N)[:nrows].cpu().numpy().reshape(-1)
+        err = O.max_rel_err(O.F16, d_gpu, d_cpu)
+        cpu_info["gpu_rows_checked"] = nrows
+        cpu_info["gpu_max_rel_err"] = err
+        cpu_info["gpu_within_tolerance_2e-3"] = bool(0 <= err <= 2e-3)
+        d_h = d_host[:nrows].numpy().reshape(-1)
+        cpu_info["e2e_rows_max_rel_err"] = O.max_rel_err(O.F16, d_h, d_cpu)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "seed": SEED, "partition": f"M-split x{world}, B replicated",
+                       "rows_per_gpu": m_local,
+                       "l2": "inputs (A+B = 256 MiB at N=1) exceed the 126 MB L2; no flush"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "steps": e2e_steps,
+                    "h2d_bytes_per_step": int(a_host.numel() * 2 + b_host.numel() * 2),
+                    "d2h_bytes_per_step": int(d_host.numel() * 2),
+                    "call": "b200wmma_gemm_host (pinned host buffers)"},
+            "gpu_launches": steps,
+            "roofline": roofline,
+        }
+        if cpu_info is not None:
+            line["cpu_baseline"] = cpu_info
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -32,6 +32,7 @@ namespace
     constexpr uint32_t GROUP   = 8; // samples per aligned group
     constexpr uint32_t MAX_K   = 256;
     constexpr uint32_t G_LD    = 40; // halves per row of the 32x32 G tile (80 bytes)
+    constexpr uint32_t MAX_WARPS = 8;
     constexpr uint32_t ZERO_BYTES = MAX_K * 2 + 16;
 
     __device__ inline uint32_t smemAddr(void const* p)
@@ -104,8 +105,8 @@ namespace
     // =====================================================================================
     // forward
     // =====================================================================================
-    template <uint32_t NWARPS, uint32_t NSTAGES>
-    __global__ void __launch_bounds__(NWARPS * 32, 1)
+    template <uint32_t NSTAGES>
+    __global__ void __launch_bounds__(MAX_WARPS * 32, 1)
         dlrmFwdKernel(__half const* __restrict__ input, __half* __restrict__ output, Shape sh)
     {
         extern __shared__ __align__(16) uint8_t smem[];
@@ -125,8 +126,9 @@ namespace
             reinterpret_cast<uint32_t*>(zeroRow)[i] = 0u;
         __syncthreads();
 
-        const uint32_t totalWarps = gridDim.x * NWARPS;
-        const uint32_t warpGlobal = blockIdx.x * NWARPS + warp;
+        const uint32_t nWarps     = blockDim.x / 32;
+        const uint32_t totalWarps = gridDim.x * nWarps;
+        const uint32_t warpGlobal = blockIdx.x * nWarps + warp;
         const uint32_t myGroups
             = warpGlobal < sh.numGroups ? (sh.numGroups - warpGlobal + totalWarps - 1) / totalWarps
                                         : 0;
@@ -249,8 +251,8 @@ namespace
     // =====================================================================================
     // backward
     // =====================================================================================
-    template <uint32_t NWARPS, uint32_t NSTAGES>
-    __global__ void __launch_bounds__(NWARPS * 32, 1)
+    template <uint32_t NSTAGES>
+    __global__ void __launch_bounds__(MAX_WARPS * 32, 1)
         dlrmBwdKernel(__half const* __restrict__ input, __half const* __restrict__ upstream,
                       __half* __restrict__ grad, __half* __restrict__ mlpGrad, Shape sh)
     {
@@ -283,8 +285,9 @@ namespace
             reinterpret_cast<uint32_t*>(gTile)[i] = 0u; // diagonal and padding stay zero
         __syncthreads();
 
-        const uint32_t totalWarps = gridDim.x * NWARPS;
-        const uint32_t warpGlobal = blockIdx.x * NWARPS + warp;
+        const uint32_t nWarps     = blockDim.x / 32;
+        const uint32_t totalWarps = gridDim.x * nWarps;
+        const uint32_t warpGlobal = blockIdx.x * nWarps + warp;
         const uint32_t myGroups
             = warpGlobal < sh.numGroups ? (sh.numGroups - warpGlobal + totalWarps - 1) / totalWarps
                                         : 0;
@@ -485,9 +488,41 @@ namespace
         return reinterpret_cast<uintptr_t>(p) % 16 == 0;
     }
 
-    constexpr uint32_t FWD_WARPS = 6, FWD_STAGES = 3;
-    constexpr uint32_t BWD_WARPS = 5, BWD_STAGES = 3;
     constexpr uint32_t SMEM_LIMIT = 227 * 1024;
+
+    // Warps per block and ring depth: as many bytes in flight as shared memory allows.
+    struct Plan
+    {
+        uint32_t warps = 0, stages = 0, smemBytes = 0;
+    };
+    Plan choosePlan(uint32_t fixedBytes, uint32_t stageBytes, uint32_t otherPerWarp)
+    {
+        Plan best;
+        for(uint32_t stages = 3; stages >= 2; --stages)
+        {
+            const uint32_t perWarp = stages * stageBytes + otherPerWarp;
+            if(fixedBytes + perWarp > SMEM_LIMIT)
+                continue;
+            uint32_t warps = (SMEM_LIMIT - fixedBytes) / perWarp;
+            warps          = warps > MAX_WARPS ? MAX_WARPS : warps;
+            if(warps * (stages - 1) > best.warps * (best.stages ? best.stages - 1 : 0))
+            {
+                best.warps     = warps;
+                best.stages    = stages;
+                best.smemBytes = fixedBytes + warps * perWarp;
+            }
+        }
+        return best;
+    }
+
+    // Opts the kernel in to the large dynamic shared-memory carve-out.
+    template <typename KernelT>
+    int prepare(KernelT kernel)
+    {
+        B200WMMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               int(SMEM_LIMIT)));
+        return B200WMMA_OK;
+    }
 } // namespace
 
 extern "C" int b200wmma_dlrm_fwd(int dtype, const void* input, void* output, uint32_t m, uint32_t k,
@@ -499,20 +534,29 @@ extern "C" int b200wmma_dlrm_fwd(int dtype, const void* input, void* output, uin
         return rc;
     if(!aligned16(input) || !aligned16(output))
         return B200WMMA_ERR_ALIGNMENT;
-    const uint32_t perWarp = FWD_STAGES * sh.stageBytes + GROUP * sh.outLen * 2;
-    const uint32_t smemBytes = ZERO_BYTES + FWD_WARPS * perWarp;
-    if(smemBytes > SMEM_LIMIT)
+    const Plan plan = choosePlan(ZERO_BYTES, sh.stageBytes, GROUP * sh.outLen * 2);
+    if(plan.warps == 0)
         return B200WMMA_ERR_UNSUPPORTED;
-    auto        kernel = dlrmFwdKernel<FWD_WARPS, FWD_STAGES>;
-    B200WMMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           int(smemBytes)));
     const int sms = b200wmma::smCount();
     if(sms <= 0)
         return B200WMMA_ERR_CUDA;
-    const uint32_t wanted = (sh.numGroups + FWD_WARPS - 1) / FWD_WARPS;
+    const uint32_t wanted = (sh.numGroups + plan.warps - 1) / plan.warps;
     const uint32_t grid   = wanted < uint32_t(sms) ? wanted : uint32_t(sms);
-    kernel<<<grid, FWD_WARPS * 32, smemBytes, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__half const*>(input), static_cast<__half*>(output), sh);
+    auto           s      = static_cast<cudaStream_t>(stream);
+    auto           in     = static_cast<__half const*>(input);
+    auto           out    = static_cast<__half*>(output);
+    if(plan.stages == 3)
+    {
+        if((rc = prepare(dlrmFwdKernel<3>)) != B200WMMA_OK)
+            return rc;
+        dlrmFwdKernel<3><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, out, sh);
+    }
+    else
+    {
+        if((rc = prepare(dlrmFwdKernel<2>)) != B200WMMA_OK)
+            return rc;
+        dlrmFwdKernel<2><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, out, sh);
+    }
     return b200wmma::cudaToStatus(cudaGetLastError());
 }
 
@@ -529,20 +573,31 @@ extern "C" int b200wmma_dlrm_bwd(int dtype, const void* input, const void* upstr
     if(!aligned16(input) || !aligned16(upstream) || !aligned16(grad) || !aligned16(mlp_grad))
         return B200WMMA_ERR_ALIGNMENT;
     const uint32_t triBytes = (m * (m - 1) / 2 * 2 + 15) / 16 * 16;
-    const uint32_t perWarp  = BWD_STAGES * sh.stageBytes + 2 * GROUP * sh.outLen * 2 + 32 * G_LD * 2;
-    const uint32_t smemBytes = ZERO_BYTES + triBytes + BWD_WARPS * perWarp;
-    if(smemBytes > SMEM_LIMIT)
+    const Plan     plan     = choosePlan(ZERO_BYTES + triBytes, sh.stageBytes,
+                                 2 * GROUP * sh.outLen * 2 + 32 * G_LD * 2);
+    if(plan.warps == 0)
         return B200WMMA_ERR_UNSUPPORTED;
-    auto kernel = dlrmBwdKernel<BWD_WARPS, BWD_STAGES>;
-    B200WMMA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           int(smemBytes)));
     const int sms = b200wmma::smCount();
     if(sms <= 0)
         return B200WMMA_ERR_CUDA;
-    const uint32_t wanted = (sh.numGroups + BWD_WARPS - 1) / BWD_WARPS;
+    const uint32_t wanted = (sh.numGroups + plan.warps - 1) / plan.warps;
     const uint32_t grid   = wanted < uint32_t(sms) ? wanted : uint32_t(sms);
-    kernel<<<grid, BWD_WARPS * 32, smemBytes, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__half const*>(input), static_cast<__half const*>(upstream),
-        static_cast<__half*>(grad), static_cast<__half*>(mlp_grad), sh);
+    auto           s      = static_cast<cudaStream_t>(stream);
+    auto           in     = static_cast<__half const*>(input);
+    auto           up     = static_cast<__half const*>(upstream);
+    auto           g      = static_cast<__half*>(grad);
+    auto           mg     = static_cast<__half*>(mlp_grad);
+    if(plan.stages == 3)
+    {
+        if((rc = prepare(dlrmBwdKernel<3>)) != B200WMMA_OK)
+            return rc;
+        dlrmBwdKernel<3><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, up, g, mg, sh);
+    }
+    else
+    {
+        if((rc = prepare(dlrmBwdKernel<2>)) != B200WMMA_OK)
+            return rc;
+        dlrmBwdKernel<2><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, up, g, mg, sh);
+    }
     return b200wmma::cudaToStatus(cudaGetLastError());
 }

@@ -2,165 +2,233 @@
 //
 // The reference sample pushes this through a 16x16x16 tensor-core tile of which one
 // column is useful (samples/simple_sgemv.cpp:103-155).  GEMV moves 4 bytes of A per
-// 2 flops, so on B200 it is bound by HBM bandwidth and the tensor cores cannot help:
-// this kernel streams A with 128-bit loads, consecutive threads on consecutive rows
-// (the contiguous direction of a column-major matrix), and splits K over enough
-// thread blocks to fill the machine.  Each block writes partial sums for its K slice
-// to a scratch array [kSplit][m]; a second small kernel adds the slices in a fixed
-// order (so results do not depend on scheduling) and applies alpha and beta.
+// 2 flops, so on B200 it is bound by HBM bandwidth and tensor cores cannot help.
+// What the kernel has to do is keep enough bytes of A in flight; the arithmetic is
+// cheap enough to be done EXACTLY as the host routine does it
+// (samples/simple_sgemv.cpp:46-67): one accumulator per row, products added one by
+// one in ascending column order, rounded multiply then rounded add, then
+// alpha * acc + beta * y.  Results are therefore bit-identical to the host routine,
+// whatever the size (a K-split or tree reduction would differ from it by the
+// rounding noise of a 16384-term fp32 sum, which alone exceeds 1e-4 relative).
 //
-// Arithmetic follows the host routine samples/simple_sgemv.cpp:46-67 except for the
-// order of the K summation.
+//   * a block owns ROWS consecutive rows; one warp-elected thread streams
+//     ROWS x COLS tiles of A through a ring of shared-memory slots with TMA
+//     (cp.async.bulk.tensor, no multicast), full/empty mbarriers per slot;
+//   * ROWS compute threads, one per row, read their row's element of each column
+//     from the slot (consecutive threads, consecutive addresses) and x[h] by a
+//     warp-uniform cached load;
+//   * 2 blocks per SM, ~80 KiB of TMA loads in flight per block.
+//
+// When pointer or leading dimension do not meet TMA's 16-byte rules a plain-load
+// kernel with the same summation order is used.
 #include "common.cuh"
-#include "gemv.cuh"
 #include "runtime.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <rocwmma/rocwmma_block.hpp>
 
-namespace b200wmma
+using namespace rocwmma::block;
+
+namespace
 {
-    namespace
+    constexpr uint32_t ROWS        = 64; // rows per block == compute threads
+    constexpr uint32_t TILE_BYTES  = 8192; // one ring slot: ROWS x COLS elements
+    constexpr uint32_t STAGES      = 10;
+    constexpr uint32_t THREADS     = ROWS + 32; // compute threads + the loader warp
+
+    struct Control
     {
-        constexpr uint32_t THREADS = 256;
-        constexpr uint32_t UNROLL  = 8; // columns in flight per thread
+        uint64_t   full[STAGES];
+        uint64_t   empty[STAGES];
+        AbortState abort;
+    };
+    constexpr uint32_t SMEM_BYTES = STAGES * TILE_BYTES + 128 /*alignment slack*/ + sizeof(Control);
 
-        template <typename T, uint32_t VEC>
-        struct alignas(sizeof(T) * VEC) Vec
+    __device__ inline float  mulRn(float a, float b) { return __fmul_rn(a, b); }
+    __device__ inline double mulRn(double a, double b) { return __dmul_rn(a, b); }
+    __device__ inline float  addRn(float a, float b) { return __fadd_rn(a, b); }
+    __device__ inline double addRn(double a, double b) { return __dadd_rn(a, b); }
+
+    template <typename T>
+    __global__ void __launch_bounds__(THREADS, 2)
+        gemvTmaKernel(const __grid_constant__ CUtensorMap tmapA, uint32_t m, uint32_t k,
+                      T const* __restrict__ x, T const* yIn, T* yOut, T alpha, T beta,
+                      uint32_t* status)
+    {
+        constexpr uint32_t COLS = TILE_BYTES / (ROWS * sizeof(T)); // 32 (fp32) / 16 (fp64)
+        extern __shared__ uint8_t smemRaw[];
+        const uint32_t            raw   = smem_addr(smemRaw);
+        uint8_t*                  tiles = smemRaw + ((128u - (raw & 127u)) & 127u);
+        Control* ctl = reinterpret_cast<Control*>(tiles + STAGES * TILE_BYTES);
+
+        const uint32_t row0   = blockIdx.x * ROWS;
+        const uint32_t numKB  = (k + COLS - 1) / COLS;
+
+        if(threadIdx.x == 0)
         {
-            T v[VEC];
-        };
-
-        // partial[ks][row] = sum over the block's K slice of A[row, h] * x[h]
-        template <typename T, uint32_t VEC>
-        __global__ void __launch_bounds__(THREADS)
-            gemvPartial(uint32_t m, uint32_t k, T const* __restrict__ a, T const* __restrict__ x,
-                        T* __restrict__ partial, uint32_t lda, uint32_t kChunk)
-        {
-            const uint32_t row0 = (blockIdx.x * THREADS + threadIdx.x) * VEC;
-            const uint32_t h0   = blockIdx.y * kChunk;
-            const uint32_t h1   = min(k, h0 + kChunk);
-
-            __shared__ T xs[1024];
-            T            acc[VEC];
-#pragma unroll
-            for(uint32_t v = 0; v < VEC; ++v)
-                acc[v] = T(0);
-
-            for(uint32_t hb = h0; hb < h1; hb += 1024)
+            for(uint32_t s = 0; s < STAGES; ++s)
             {
-                const uint32_t cnt = min(1024u, h1 - hb);
-                __syncthreads();
-                for(uint32_t i = threadIdx.x; i < cnt; i += THREADS)
-                    xs[i] = x[hb + i];
-                __syncthreads();
-                if(row0 < m)
+                mbar_init(&ctl->full[s], 1);
+                mbar_init(&ctl->empty[s], ROWS);
+            }
+            ctl->abort.flag = 0;
+            ctl->abort.code = 0;
+            mbar_init_fence();
+            tma_prefetch_descriptor(&tmapA);
+        }
+        __syncthreads();
+
+        if(threadIdx.x >= ROWS)
+        {
+            // ---- loader warp ----
+            if(elect_one())
+            {
+                uint32_t kb = 0;
+                bool     ok = true;
+                for(; kb < numKB; ++kb)
                 {
-                    T const* col = a + size_t(hb) * lda + row0;
-                    uint32_t i   = 0;
-                    for(; i + UNROLL <= cnt; i += UNROLL)
+                    const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
+                    if(!mbar_wait(&ctl->empty[s], ph ^ 1u, &ctl->abort, WAIT_STAGE_EMPTY))
                     {
-                        Vec<T, VEC> av[UNROLL];
-#pragma unroll
-                        for(uint32_t u = 0; u < UNROLL; ++u)
-                            av[u] = *reinterpret_cast<Vec<T, VEC> const*>(col + size_t(i + u) * lda);
-#pragma unroll
-                        for(uint32_t u = 0; u < UNROLL; ++u)
-                        {
-                            const T xv = xs[i + u];
-#pragma unroll
-                            for(uint32_t v = 0; v < VEC; ++v)
-                                acc[v] += av[u].v[v] * xv;
-                        }
+                        ok = false;
+                        break;
                     }
-                    for(; i < cnt; ++i)
+                    mbar_expect_tx(&ctl->full[s], TILE_BYTES);
+                    tma_load_2d(tiles + s * TILE_BYTES, &tmapA, &ctl->full[s], int32_t(row0),
+                                int32_t(kb * COLS));
+                }
+                if(!ok)
+                {
+                    const uint32_t pending = kb < STAGES ? kb : STAGES;
+                    for(uint32_t j = 0; j < pending; ++j)
                     {
-                        const Vec<T, VEC> av
-                            = *reinterpret_cast<Vec<T, VEC> const*>(col + size_t(i) * lda);
-                        const T xv = xs[i];
-#pragma unroll
-                        for(uint32_t v = 0; v < VEC; ++v)
-                            acc[v] += av.v[v] * xv;
+                        const uint32_t  prev = kb - 1 - j;
+                        const long long t0   = clock64();
+                        while(!mbar_try_wait(&ctl->full[prev % STAGES], (prev / STAGES) & 1u)
+                              && clock64() - t0 < 2000000ll)
+                        {
+                        }
                     }
                 }
             }
-            if(row0 < m)
+        }
+        else
+        {
+            // ---- one row per thread, columns in ascending order ----
+            const uint32_t r   = threadIdx.x;
+            T              acc = T(0);
+            for(uint32_t kb = 0; kb < numKB; ++kb)
             {
-                Vec<T, VEC> out;
+                const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
+                if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
+                    break;
+                T const*       tile = reinterpret_cast<T const*>(tiles + s * TILE_BYTES);
+                const uint32_t h0   = kb * COLS;
+                if(h0 + COLS <= k)
+                {
 #pragma unroll
-                for(uint32_t v = 0; v < VEC; ++v)
-                    out.v[v] = acc[v];
-                *reinterpret_cast<Vec<T, VEC>*>(partial + size_t(blockIdx.y) * m + row0) = out;
+                    for(uint32_t j = 0; j < COLS; ++j)
+                        acc = addRn(acc, mulRn(tile[j * ROWS + r], __ldg(x + h0 + j)));
+                }
+                else
+                {
+                    for(uint32_t j = 0; h0 + j < k; ++j)
+                        acc = addRn(acc, mulRn(tile[j * ROWS + r], __ldg(x + h0 + j)));
+                }
+                mbar_arrive(&ctl->empty[s]);
             }
+            if(row0 + r < m && ctl->abort.flag == 0u)
+                yOut[row0 + r] = addRn(mulRn(alpha, acc), mulRn(beta, yIn[row0 + r]));
         }
-
-        // y_out[i] = alpha * (partial[0][i] + partial[1][i] + ...) + beta * y_in[i]
-        template <typename T>
-        __global__ void gemvFinish(uint32_t m, uint32_t kSplit, T const* __restrict__ partial,
-                                   T const* yIn, T* yOut, T alpha, T beta)
+        __syncthreads();
+        if(threadIdx.x == 0 && ctl->abort.flag != 0u && status != nullptr)
         {
-            const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-            if(i >= m)
-                return;
-            T acc = T(0);
-            for(uint32_t s = 0; s < kSplit; ++s)
-                acc += partial[size_t(s) * m + i];
-            yOut[i] = alpha * acc + beta * yIn[i];
+            atomicExch(&status[1], ctl->abort.code);
+            atomicExch(&status[0], 1u);
         }
+    }
 
-        template <typename T, uint32_t VEC>
-        int launchPartial(uint32_t m, uint32_t k, T const* a, T const* x, T* partial, uint32_t lda,
-                          uint32_t kSplit, uint32_t kChunk, cudaStream_t stream)
-        {
-            dim3 grid((m + THREADS * VEC - 1) / (THREADS * VEC), kSplit);
-            gemvPartial<T, VEC><<<grid, THREADS, 0, stream>>>(m, k, a, x, partial, lda, kChunk);
-            return cudaToStatus(cudaGetLastError());
-        }
-    } // namespace
-
-    void gemvPlan(uint32_t m, uint32_t k, size_t elemBytes, int sms, uint32_t* kSplit,
-                  uint32_t* kChunk)
+    // Same arithmetic with plain loads, for operands TMA cannot address.
+    template <typename T>
+    __global__ void gemvPlainKernel(uint32_t m, uint32_t k, T const* __restrict__ a,
+                                    T const* __restrict__ x, T const* yIn, T* yOut, T alpha, T beta,
+                                    uint32_t lda)
     {
-        const uint32_t vec       = uint32_t(16 / elemBytes);
-        const uint32_t rowBlocks = (m + THREADS * vec - 1) / (THREADS * vec);
-        // about four blocks per SM, but never K slices shorter than 64 columns
-        uint32_t split = (4u * uint32_t(sms) + rowBlocks - 1) / rowBlocks;
-        split          = max(1u, min(split, max(1u, k / 64u)));
-        split          = min(split, 1024u);
-        *kChunk        = (k + split - 1) / split;
-        *kSplit        = (k + *kChunk - 1) / *kChunk;
+        const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+        if(i >= m)
+            return;
+        T acc = T(0);
+        for(uint32_t h = 0; h < k; ++h)
+            acc = addRn(acc, mulRn(a[size_t(h) * lda + i], __ldg(x + h)));
+        yOut[i] = addRn(mulRn(alpha, acc), mulRn(beta, yIn[i]));
+    }
+
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    EncodeFn encoder()
+    {
+        static EncodeFn       fn = nullptr;
+        static std::once_flag once;
+        std::call_once(once, [] {
+            void*                           sym = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q)
+                   == cudaSuccess
+               && q == cudaDriverEntryPointSuccess)
+                fn = reinterpret_cast<EncodeFn>(sym);
+            else
+                (void)cudaGetLastError();
+        });
+        return fn;
     }
 
     template <typename T>
-    int gemvRun(uint32_t m, uint32_t k, T const* a, T const* x, T const* yIn, T* yOut, T alpha,
-                T beta, uint32_t lda, T* partial, uint32_t kSplit, uint32_t kChunk,
-                cudaStream_t stream)
+    int run(uint32_t m, uint32_t k, T const* a, T const* x, T const* yIn, T* yOut, T alpha, T beta,
+            uint32_t lda, cudaStream_t stream)
     {
-        constexpr uint32_t VEC = 16 / sizeof(T);
-        const bool vecOK = (m % VEC == 0) && (lda % VEC == 0)
-                           && (reinterpret_cast<uintptr_t>(a) % 16 == 0)
-                           && (reinterpret_cast<uintptr_t>(partial) % 16 == 0);
-        int rc;
-        if(vecOK)
-            rc = launchPartial<T, VEC>(m, k, a, x, partial, lda, kSplit, kChunk, stream);
-        else
+        const bool tmaOK = (reinterpret_cast<uintptr_t>(a) % 16 == 0)
+                           && ((size_t(lda) * sizeof(T)) % 16 == 0) && m >= ROWS;
+        if(!tmaOK)
         {
-            // scalar rows: the row-block count differs, the K split is reused as is
-            rc = launchPartial<T, 1>(m, k, a, x, partial, lda, kSplit, kChunk, stream);
+            gemvPlainKernel<T><<<(m + 127) / 128, 128, 0, stream>>>(m, k, a, x, yIn, yOut, alpha,
+                                                                  beta, lda);
+            return b200wmma::cudaToStatus(cudaGetLastError());
         }
-        if(rc != B200WMMA_OK)
-            return rc;
-        gemvFinish<T><<<(m + 255) / 256, 256, 0, stream>>>(m, kSplit, partial, yIn, yOut, alpha,
-                                                          beta);
-        return cudaToStatus(cudaGetLastError());
+        EncodeFn fn = encoder();
+        if(!fn)
+            return B200WMMA_ERR_CUDA;
+        constexpr uint32_t COLS = TILE_BYTES / (ROWS * sizeof(T));
+        CUtensorMap        map;
+        cuuint64_t         dims[2]    = {m, k};
+        cuuint64_t         strides[1] = {cuuint64_t(lda) * sizeof(T)};
+        cuuint32_t         box[2]     = {ROWS, COLS};
+        cuuint32_t         estr[2]    = {1, 1};
+        const CUtensorMapDataType dt
+            = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT64;
+        if(fn(&map, dt, 2, const_cast<T*>(a), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+           != CUDA_SUCCESS)
+            return B200WMMA_ERR_CUDA;
+
+        static bool attrDone[64] = {};
+        int         dev          = 0;
+        B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
+        if(dev < 0 || dev >= 64 || !attrDone[dev])
+        {
+            B200WMMA_CUDA_TRY(cudaFuncSetAttribute(gemvTmaKernel<T>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   int(SMEM_BYTES)));
+            if(dev >= 0 && dev < 64)
+                attrDone[dev] = true;
+        }
+        gemvTmaKernel<T><<<(m + ROWS - 1) / ROWS, THREADS, SMEM_BYTES, stream>>>(
+            map, m, k, x, yIn, yOut, alpha, beta, b200wmma::deviceStatusWord());
+        return b200wmma::cudaToStatus(cudaGetLastError());
     }
-
-    template int gemvRun<float>(uint32_t, uint32_t, float const*, float const*, float const*,
-                                float*, float, float, uint32_t, float*, uint32_t, uint32_t,
-                                cudaStream_t);
-    template int gemvRun<double>(uint32_t, uint32_t, double const*, double const*, double const*,
-                                 double*, double, double, uint32_t, double*, uint32_t, uint32_t,
-                                 cudaStream_t);
-} // namespace b200wmma
-
-using namespace b200wmma;
+} // namespace
 
 extern "C" int b200wmma_gemv(int dtype, uint32_t m, uint32_t k, const void* a, const void* x,
                              const void* y_in, void* y_out, double alpha, double beta,
@@ -170,22 +238,12 @@ extern "C" int b200wmma_gemv(int dtype, uint32_t m, uint32_t k, const void* a, c
         return B200WMMA_ERR_INVALID_ARG;
     if(dtype != B200WMMA_F32 && dtype != B200WMMA_F64)
         return B200WMMA_ERR_UNSUPPORTED;
-    const size_t elem = dtypeSize(dtype);
-    const int    sms  = smCount();
-    if(sms <= 0)
-        return B200WMMA_ERR_CUDA;
-    uint32_t kSplit = 1, kChunk = k;
-    gemvPlan(m, k, elem, sms, &kSplit, &kChunk);
-    void* partial = deviceScratch(size_t(kSplit) * m * elem);
-    if(!partial)
-        return B200WMMA_ERR_CUDA;
     auto s = static_cast<cudaStream_t>(stream);
     if(dtype == B200WMMA_F32)
-        return gemvRun<float>(m, k, static_cast<float const*>(a), static_cast<float const*>(x),
-                              static_cast<float const*>(y_in), static_cast<float*>(y_out),
-                              float(alpha), float(beta), lda, static_cast<float*>(partial), kSplit,
-                              kChunk, s);
-    return gemvRun<double>(m, k, static_cast<double const*>(a), static_cast<double const*>(x),
-                           static_cast<double const*>(y_in), static_cast<double*>(y_out), alpha,
-                           beta, lda, static_cast<double*>(partial), kSplit, kChunk, s);
+        return run<float>(m, k, static_cast<float const*>(a), static_cast<float const*>(x),
+                          static_cast<float const*>(y_in), static_cast<float*>(y_out), float(alpha),
+                          float(beta), lda, s);
+    return run<double>(m, k, static_cast<double const*>(a), static_cast<double const*>(x),
+                       static_cast<double const*>(y_in), static_cast<double*>(y_out), alpha, beta,
+                       lda, s);
 }
