@@ -11,7 +11,8 @@
 //
 // It plays the role of the reference's cooperative global->LDS staging
 // (rocwmma_coop.hpp, samples/perf_hgemm.cpp:592-685), redone for the hardware.
-// No function here uses cluster multicast.
+// No load here uses cluster multicast; the only multicast is the completion signal of
+// tcgen05.commit for CTA pairs.
 //
 // Every wait gives up after a time limit, raises a block-wide abort flag and
 // returns false; callers leave their loops, release what they hold and return,
@@ -260,6 +261,109 @@ namespace rocwmma
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::
                              "r"(smem_addr(bar))
                          : "memory");
+        }
+
+        // =============================================================================
+        // CTA pairs (cta_group::2): two thread blocks of a cluster, on the two SMs of
+        // one TPC, drive ONE tcgen05.mma of M = 256.  Each block stages its own 128
+        // rows of A and its own half of the B tile (plain TMA loads into its own
+        // shared memory -- no multicast), the even block of the pair issues the MMA,
+        // and each block's tensor core writes its 128 accumulator rows to its own TMEM.
+        // =============================================================================
+        ROCWMMA_DEVICE inline uint32_t cluster_cta_rank()
+        {
+            uint32_t r;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+            return r;
+        }
+        // Shared-memory address of the same variable in block `rank` of the cluster.
+        ROCWMMA_DEVICE inline uint32_t map_to_cta(uint32_t smemAddr, uint32_t rank)
+        {
+            uint32_t r;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smemAddr), "r"(rank));
+            return r;
+        }
+        ROCWMMA_DEVICE inline void cluster_sync()
+        {
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
+        // Arrive on an mbarrier that may live in the other block of the pair
+        // (`clusterAddr` from map_to_cta).
+        ROCWMMA_DEVICE inline void mbar_arrive_cluster(uint32_t clusterAddr)
+        {
+            asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
+                             clusterAddr)
+                         : "memory");
+        }
+        // TMA tile load issued by either block of a pair: data lands in the issuing
+        // block's shared memory, the byte count is signalled on `barClusterAddr`, which
+        // may be the pair leader's barrier.
+        ROCWMMA_DEVICE inline void tma_load_2d_pair(void* dst, void const* tensorMap,
+                                                    uint32_t barClusterAddr, int32_t x, int32_t y)
+        {
+            asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global"
+                         ".mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                             smem_addr(dst)),
+                         "l"(reinterpret_cast<uint64_t>(tensorMap)), "r"(barClusterAddr), "r"(x),
+                         "r"(y)
+                         : "memory");
+        }
+        ROCWMMA_DEVICE inline void tmem_alloc_pair(uint32_t* slot, uint32_t columns)
+        {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_addr(slot)),
+                         "r"(columns)
+                         : "memory");
+        }
+        ROCWMMA_DEVICE inline void tmem_relinquish_alloc_permit_pair()
+        {
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        }
+        ROCWMMA_DEVICE inline void tmem_dealloc_pair(uint32_t base, uint32_t columns)
+        {
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base),
+                         "r"(columns)
+                         : "memory");
+        }
+        // Pair MMA (M = 256 over both blocks).  Issued by ONE thread of the even block.
+        template <MmaKind Kind>
+        ROCWMMA_DEVICE inline void mma_ss_pair(uint32_t dTmem, uint64_t descA, uint64_t descB,
+                                               uint32_t idesc, uint32_t accumulate)
+        {
+            if constexpr(Kind == MmaKind::F16)
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                             "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+                                 dTmem),
+                             "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+                             : "memory");
+            else if constexpr(Kind == MmaKind::TF32)
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                             "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+                                 dTmem),
+                             "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+                             : "memory");
+            else if constexpr(Kind == MmaKind::I8)
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                             "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+                                 dTmem),
+                             "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+                             : "memory");
+            else
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                             "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+                                 dTmem),
+                             "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+                             : "memory");
+        }
+        // Completion of all pair MMAs issued so far arrives (one count) on the barrier at
+        // the same shared-memory offset in every block named in ctaMask.
+        ROCWMMA_DEVICE inline void mma_commit_pair(uint64_t* bar, uint16_t ctaMask)
+        {
+            // clang-format off
+            asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                         :: "r"(smem_addr(bar)), "h"(ctaMask) : "memory");
+            // clang-format on
         }
 
         // Reads 32 consecutive 32-bit columns of this thread's TMEM lane

@@ -93,8 +93,11 @@ B200WMMA_API int b200wmma_gemm_simple(int in_dtype, int out_dtype, uint32_t m, u
  * XF32->F32, I8->I32, E4M3->BF16, E4M3->F32; F64->F64 runs on the warp-level
  * double-precision tensor path with a shared-memory pipeline.
  * Requirements: a, b, c, d 16-byte aligned; lda, ldb, ldc, ldd times the element
- * size multiples of 16 bytes; k a multiple of 16 bytes worth of elements.
- * Any m, n >= 1 (edge tiles are masked).
+ * size multiples of 16 bytes.  Any m, n, k >= 1 (edge tiles are zero-filled on
+ * load and masked on store).  A row-major with B column-major is the native
+ * operand form; any other layout is first transposed into a per-device scratch
+ * buffer that is allocated on first use and grown on demand, so such calls on
+ * different streams of one device must not overlap.
  */
 B200WMMA_API int b200wmma_gemm(int in_dtype, int out_dtype, uint32_t m, uint32_t n, uint32_t k, const void* a,
                   const void* b, const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
@@ -117,7 +120,9 @@ B200WMMA_API int b200wmma_gemm_host(int in_dtype, int out_dtype, uint32_t m, uin
  * y_out = alpha * A * x + beta * y_in, A column-major m x k with leading
  * dimension lda >= m (reference: samples/simple_sgemv.cpp:103-155, host routine
  * :46-67; simple_dgemv.cpp).  dtype F32 or F64.  y_out may alias y_in.
- * Uses a per-device scratch buffer for partial sums, allocated on first use.
+ * Each row is summed in ascending column order with a rounded multiply and a
+ * rounded add per term, exactly like the host routine, so results are
+ * bit-identical to it.  Needs no scratch memory.
  */
 B200WMMA_API int b200wmma_gemv(int dtype, uint32_t m, uint32_t k, const void* a, const void* x,
                   const void* y_in, void* y_out, double alpha, double beta, uint32_t lda,

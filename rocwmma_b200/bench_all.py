@@ -1,0 +1,161 @@
+"""Per-configuration throughput of every kernel in the library, one JSON line each.
+
+    python -m rocwmma_b200.bench_all [--only NAME[,NAME...]] [--iters N] [--small]
+
+Covers the configurations the headline benchmark (bench.py at the repository root) does
+not: the simple one-tile-per-warp GEMM, the precision sweep, the quantised GEMMs, GEMV
+and the DLRM passes.  GEMMs report TFLOP/s = 2*M*N*K / time against the measured dense
+bf16 peak scaled per type; GEMV and DLRM report algorithmic bytes / time against the
+measured HBM copy bandwidth.  Inputs are random device tensors (timing only; parity is
+the test-suite's job).  Timed with CUDA events over `iters` back-to-back launches after
+3 warm-ups; every working set exceeds the 126 MB L2 except where noted.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import api
+from ._lib import BF16, COL_MAJOR, E4M3, F16, F32, F64, I8, I32, ROW_MAJOR, XF32
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops"]), float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+def timed(fn, iters):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    api.check_device()
+    return e0.elapsed_time(e1) / iters
+
+
+def rand(n, code):
+    dev = "cuda"
+    if code in (F16, BF16, F32, XF32, F64):
+        t = torch.rand(n, device=dev, dtype=torch.float32) * 2 - 1
+        if code == XF32:
+            return (t.view(torch.int32) & -8192).view(torch.float32)
+        return t.to(api.torch_dtype(code))
+    if code == I8:
+        return torch.randint(-128, 128, (n,), device=dev, dtype=torch.int8)
+    if code == I32:
+        return torch.randint(-100, 100, (n,), device=dev, dtype=torch.int32)
+    if code == E4M3:
+        return (torch.randn(n, device=dev) * 80).clamp(-448, 448).to(torch.float8_e4m3fn).view(
+            torch.uint8)
+    raise ValueError(code)
+
+
+def gemm_case(name, in_t, out_t, size, alpha, beta, peak_scale, simple=False, iters=20):
+    m = n = k = size
+    a, b = rand(m * k, in_t), rand(k * n, in_t)
+    c = rand(m * n, out_t) if beta != 0 else None
+    d = torch.empty(m * n, dtype=api.torch_dtype(out_t), device="cuda")
+    if simple:
+        fn = lambda: api.gemm_simple(in_t, out_t, m, n, k, a, b, c, alpha, beta, ROW_MAJOR,  # noqa
+                                     COL_MAJOR, ROW_MAJOR, 16, out=d)
+    else:
+        fn = lambda: api.gemm(in_t, out_t, m, n, k, a, b, c, alpha, beta, out=d)  # noqa: E731
+    ms = timed(fn, iters)
+    tf = 2.0 * m * n * k / ms / 1e9
+    peak_bf16, _, src = peaks()
+    peak = peak_bf16 * peak_scale if peak_scale else 40.0
+    return {"config": name, "ms": ms, "value": tf, "unit": "TFLOP/s", "bound": "tensor",
+            "peak": peak, "frac": tf / peak,
+            "peak_source": (f"{src} bf16 peak x {peak_scale}" if peak_scale
+                            else "nominal fp64 tensor 40 TFLOP/s")}
+
+
+def gemv_case(size, iters=50):
+    m = k = size
+    a, x, y = rand(m * k, F32), rand(k, F32), rand(m, F32)
+    out = torch.empty_like(y)
+    ms = timed(lambda: api.gemv(F32, m, k, a, x, y, 2.1, 2.1, out=out), iters)
+    nbytes = m * k * 4 + k * 4 + 2 * m * 4
+    _, hbm, src = peaks()
+    gbs = nbytes / ms / 1e6
+    return {"config": f"sgemv {size}^2 fp32 col-major", "ms": ms, "value": gbs, "unit": "GB/s",
+            "bound": "hbm", "algorithmic_bytes": nbytes, "peak": hbm, "frac": gbs / hbm,
+            "peak_source": f"{src} copy bandwidth"}
+
+
+def dlrm_cases(batch, iters=20):
+    m, k = 27, 128
+    out_len = k + m * (m - 1) // 2
+    x = torch.randn(batch * m * k, device="cuda").half()
+    up = torch.randn(batch * out_len, device="cuda").half()
+    out = torch.empty(batch * out_len, device="cuda", dtype=torch.float16)
+    grad = torch.empty(batch * m * k, device="cuda", dtype=torch.float16)
+    mlp = torch.empty(batch * k, device="cuda", dtype=torch.float16)
+    _, hbm, src = peaks()
+    res = []
+    ms = timed(lambda: api.dlrm_fwd(x, m, k, batch, out=out), iters)
+    nb = batch * (m * k + out_len) * 2
+    res.append({"config": f"dlrm fwd b={batch} 27x128 fp16", "ms": ms, "value": nb / ms / 1e6,
+                "unit": "GB/s", "bound": "hbm", "algorithmic_bytes": nb, "peak": hbm,
+                "frac": nb / ms / 1e6 / hbm, "peak_source": f"{src} copy bandwidth"})
+    ms = timed(lambda: api.dlrm_bwd(x, up, m, k, batch, grad=grad, mlp_grad=mlp), iters)
+    nb = batch * (m * k + out_len + m * k + k) * 2
+    res.append({"config": f"dlrm bwd b={batch} 27x128 fp16", "ms": ms, "value": nb / ms / 1e6,
+                "unit": "GB/s", "bound": "hbm", "algorithmic_bytes": nb, "peak": hbm,
+                "frac": nb / ms / 1e6 / hbm, "peak_source": f"{src} copy bandwidth"})
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--iters", type=int, default=0)
+    ap.add_argument("--small", action="store_true",
+                    help="reduced sizes (for profiler captures): GEMMs 2048^3, DLRM b=8192, "
+                         "GEMV 8192^2")
+    args = ap.parse_args()
+    only = set(filter(None, args.only.split(",")))
+    big, mid = (2048, 2048) if args.small else (8192, 4096)
+    it = (lambda d: args.iters or d)
+
+    cases = {
+        "simple_hgemm": lambda: gemm_case("simple_hgemm 1024^3 f16->f32 16x16x16", F16, F32, 1024,
+                                          1.5, 0.5, 1.0, simple=True, iters=it(20)),
+        "hgemm": lambda: gemm_case(f"perf_hgemm {big}^3 f16->f16", F16, F16, big, 1.0, 0.0, 1.0,
+                                   iters=it(20)),
+        "bf16": lambda: gemm_case(f"gemm {mid}^3 bf16->f32", BF16, F32, mid, 2.0, -1.0, 1.0,
+                                  iters=it(20)),
+        "xf32": lambda: gemm_case(f"gemm {mid}^3 xf32->f32", XF32, F32, mid, 2.0, -1.0, 0.5,
+                                  iters=it(20)),
+        "f64": lambda: gemm_case(f"gemm {mid}^3 f64", F64, F64, mid, 2.0, -1.0, None,
+                                 iters=it(5)),
+        "i8": lambda: gemm_case(f"gemm {big}^3 i8->i32", I8, I32, big, 1, 0, 2.0, iters=it(20)),
+        "fp8": lambda: gemm_case(f"gemm {big}^3 e4m3->bf16", E4M3, BF16, big, 1.0, 0.0, 2.0,
+                                 iters=it(20)),
+        "sgemv": lambda: gemv_case(8192 if args.small else 16384, iters=it(50)),
+        "dlrm": lambda: dlrm_cases(8192 if args.small else 65536, iters=it(20)),
+    }
+    for name, fn in cases.items():
+        if only and name not in only:
+            continue
+        res = fn()
+        for r in (res if isinstance(res, list) else [res]):
+            print(json.dumps(r), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -26,6 +26,7 @@
 #include "runtime.cuh"
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cstdlib>
 #include <cuda_fp16.h>
 #include <mutex>
 #include <rocwmma/rocwmma_block.hpp>
@@ -381,6 +382,222 @@ namespace
         }
     }
 
+    // =====================================================================================
+    // CTA-pair variant: a cluster of two blocks (the two SMs of a TPC) computes a
+    // 256 x 256 tile with tcgen05.mma.cta_group::2.  Block r of the pair loads rows
+    // [128 r, 128 r + 128) of the A tile and of the B tile into its OWN shared memory
+    // (plain TMA loads; nothing is multicast), the even block issues the M = 256 MMAs
+    // for both, and each block's tensor core leaves its 128 accumulator rows in its own
+    // TMEM.  Per block and K step that is 32 KiB of operands instead of 48 KiB, which
+    // buys a 6-slot ring and a third less L2 -> shared-memory traffic per flop.
+    //
+    // Barriers: the leader's full[s] collects the bytes of BOTH blocks (the peer's TMA
+    // signals it remotely); empty[s] and accFull[b] are completed in both blocks by one
+    // multicast tcgen05.commit; the leader's accEmpty[b] counts the epilogue threads of
+    // both blocks.
+    // =====================================================================================
+    constexpr uint32_t P_TILE_M      = 256; // rows per pair
+    constexpr uint32_t P_STAGES      = 6;
+    constexpr uint32_t P_A_BYTES     = 128 * ROW_BYTES; // 16 KiB: this block's rows of A
+    constexpr uint32_t P_B_BYTES     = 128 * ROW_BYTES; // 16 KiB: this block's half of B
+    constexpr uint32_t P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+
+    struct PairControl
+    {
+        uint64_t   full[P_STAGES];
+        uint64_t   empty[P_STAGES];
+        uint64_t   accFull[ACC_BUFS];
+        uint64_t   accEmpty[ACC_BUFS];
+        uint32_t   tmemBase;
+        AbortState abort;
+    };
+    constexpr uint32_t P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + sizeof(PairControl) + 64;
+
+    template <typename InT, typename OutT, typename CompT>
+    __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+        gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmapA,
+                                 const __grid_constant__ CUtensorMap tmapB,
+                                 const GemmParams                    p)
+    {
+        constexpr uint32_t BK     = ROW_BYTES / sizeof(InT);
+        constexpr uint32_t UMMA_K = 32 / sizeof(InT);
+        constexpr uint32_t IDESC  = make_instr_desc(KindOf<InT>::acc, KindOf<InT>::fmt,
+                                                   KindOf<InT>::fmt, P_TILE_M, BN);
+
+        extern __shared__ uint8_t smemRaw[];
+        const uint32_t            rawAddr = smem_addr(smemRaw);
+        uint8_t*     tiles = smemRaw + ((1024u - (rawAddr & 1023u)) & 1023u);
+        PairControl* ctl   = reinterpret_cast<PairControl*>(tiles + P_STAGES * P_STAGE_BYTES);
+
+        const uint32_t warp   = threadIdx.x / 32;
+        const uint32_t lane   = threadIdx.x % 32;
+        const uint32_t rank   = cluster_cta_rank(); // 0 = leader of the pair
+        const uint32_t pairId = blockIdx.x / 2;
+        const uint32_t nPairs = gridDim.x / 2;
+
+        const uint32_t tilesM   = (p.m + P_TILE_M - 1) / P_TILE_M;
+        const uint32_t tilesN   = (p.n + BN - 1) / BN;
+        const uint32_t numTiles = tilesM * tilesN;
+        const uint32_t numKB    = (p.k + BK - 1) / BK;
+
+        if(threadIdx.x == 0)
+        {
+            for(uint32_t s = 0; s < P_STAGES; ++s)
+            {
+                mbar_init(&ctl->full[s], 1);
+                mbar_init(&ctl->empty[s], 1);
+            }
+            for(uint32_t b = 0; b < ACC_BUFS; ++b)
+            {
+                mbar_init(&ctl->accFull[b], 1);
+                mbar_init(&ctl->accEmpty[b], 2 * EPI_THREADS);
+            }
+            ctl->abort.flag = 0;
+            ctl->abort.code = 0;
+            mbar_init_fence();
+            tma_prefetch_descriptor(&tmapA);
+            tma_prefetch_descriptor(&tmapB);
+        }
+        if(warp == 1)
+        {
+            tmem_alloc_pair(&ctl->tmemBase, TMEM_COLS);
+            tmem_relinquish_alloc_permit_pair();
+        }
+        tc_fence_before_sync();
+        __syncthreads();
+        cluster_sync(); // both blocks' barriers exist before anything signals them remotely
+        tc_fence_after_sync();
+        const uint32_t tmemBase = ctl->tmemBase;
+
+        if(warp == 0)
+        {
+            // ---------------- TMA producer (both blocks) ----------------
+            if(elect_one())
+            {
+                uint32_t it = 0;
+                bool     ok = true;
+                for(uint32_t t = pairId; ok && t < numTiles; t += nPairs)
+                {
+                    uint32_t tm, tn;
+                    tileCoord(t, tilesM, tilesN, tm, tn);
+                    const int32_t rowA = int32_t(tm * P_TILE_M + rank * 128u);
+                    const int32_t rowB = int32_t(tn * BN + rank * 128u);
+                    for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
+                    {
+                        const uint32_t s  = it % P_STAGES;
+                        const uint32_t ph = (it / P_STAGES) & 1u;
+                        if(!mbar_wait(&ctl->empty[s], ph ^ 1u, &ctl->abort, WAIT_STAGE_EMPTY))
+                        {
+                            ok = false;
+                            break;
+                        }
+                        uint8_t* slot = tiles + s * P_STAGE_BYTES;
+                        if(rank == 0)
+                            mbar_expect_tx(&ctl->full[s], 2u * P_STAGE_BYTES); // both blocks' bytes
+                        const uint32_t leaderFull = map_to_cta(smem_addr(&ctl->full[s]), 0);
+                        tma_load_2d_pair(slot, &tmapA, leaderFull, int32_t(kb * BK), rowA);
+                        tma_load_2d_pair(slot + P_A_BYTES, &tmapB, leaderFull, int32_t(kb * BK),
+                                         rowB);
+                    }
+                }
+            }
+        }
+        else if(warp == 1)
+        {
+            // ---------------- MMA issuer (leader block only) ----------------
+            if(rank == 0 && elect_one())
+            {
+                uint32_t it = 0, tileIter = 0;
+                bool     ok = true;
+                for(uint32_t t = pairId; ok && t < numTiles; t += nPairs, ++tileIter)
+                {
+                    const uint32_t buf   = tileIter & 1u;
+                    const uint32_t accPh = (tileIter >> 1) & 1u;
+                    if(!mbar_wait(&ctl->accEmpty[buf], accPh ^ 1u, &ctl->abort, WAIT_ACC_EMPTY))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t dTmem = tmemBase + buf * BN;
+                    for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
+                    {
+                        const uint32_t s  = it % P_STAGES;
+                        const uint32_t ph = (it / P_STAGES) & 1u;
+                        if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
+                        {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t aAddr = smem_addr(tiles + s * P_STAGE_BYTES);
+                        const uint32_t bAddr = aAddr + P_A_BYTES;
+#pragma unroll
+                        for(uint32_t ks = 0; ks < BK / UMMA_K; ++ks)
+                        {
+                            const uint64_t da = smem_desc_kmajor_sw128(aAddr + ks * 32u);
+                            const uint64_t db = smem_desc_kmajor_sw128(bAddr + ks * 32u);
+                            mma_ss_pair<KindOf<InT>::kind>(dTmem, da, db, IDESC, (kb | ks) != 0u);
+                        }
+                        mma_commit_pair(&ctl->empty[s], 0x3); // frees the slot in both blocks
+                    }
+                    if(ok)
+                        mma_commit_pair(&ctl->accFull[buf], 0x3);
+                }
+            }
+        }
+        else
+        {
+            // ---------------- epilogue (both blocks, own 128 rows) ----------------
+            const uint32_t quad  = warp % 4;
+            const CompT    alpha = CompT(p.alpha);
+            const CompT    beta  = CompT(p.beta);
+            const bool     useC  = (p.beta != 0.0) && (p.c != nullptr);
+            uint32_t       tileIter = 0;
+            for(uint32_t t = pairId; t < numTiles; t += nPairs, ++tileIter)
+            {
+                uint32_t tm, tn;
+                tileCoord(t, tilesM, tilesN, tm, tn);
+                const uint32_t buf   = tileIter & 1u;
+                const uint32_t accPh = (tileIter >> 1) & 1u;
+                if(!mbar_wait(&ctl->accFull[buf], accPh, &ctl->abort, WAIT_ACC_FULL))
+                    break;
+                tc_fence_after_sync();
+                const uint32_t row = tm * P_TILE_M + rank * 128u + quad * 32u + lane;
+#pragma unroll 1
+                for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+                {
+                    uint32_t raw[32];
+                    __syncwarp();
+                    const uint32_t taddr = tmemBase + ((quad * 32u) << 16) + buf * BN + chunk * 32u;
+                    tmem_load_32x32b_x32(taddr, raw);
+                    tmem_load_wait();
+                    const uint32_t col0 = tn * BN + chunk * 32;
+                    if(row < p.m && col0 < p.n)
+                        epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0);
+                }
+                tc_fence_before_sync();
+                mbar_arrive_cluster(map_to_cta(smem_addr(&ctl->accEmpty[buf]), 0));
+            }
+        }
+
+        // ---------------- teardown ----------------
+        tc_fence_before_sync();
+        __syncthreads();
+        cluster_sync(); // neither block leaves while the other may still signal it
+        if(warp == 1)
+        {
+            __syncwarp();
+            tc_fence_after_sync();
+            tmem_dealloc_pair(tmemBase, TMEM_COLS);
+        }
+        if(threadIdx.x == 0 && ctl->abort.flag != 0u && p.status != nullptr)
+        {
+            atomicExch(&p.status[1], ctl->abort.code);
+            atomicExch(&p.status[0], 1u);
+        }
+    }
+
     // ---- host side -----------------------------------------------------------------
     using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -422,42 +639,78 @@ namespace
         return r == CUDA_SUCCESS ? B200WMMA_OK : B200WMMA_ERR_CUDA;
     }
 
+    // The pair kernel is the default whenever a 256-row tile makes sense; the environment
+    // variable B200WMMA_GEMM_PAIR=0 selects the single-block kernel (for comparison).
+    bool pairEnabled()
+    {
+        static const bool on = [] {
+            const char* e = getenv("B200WMMA_GEMM_PAIR");
+            return !(e && e[0] == '0');
+        }();
+        return on;
+    }
+
+    template <typename KernelT>
+    int optInSharedMemory(KernelT kernel, uint32_t bytes, bool (&done)[64])
+    {
+        static std::mutex           attrMutex;
+        std::lock_guard<std::mutex> lock(attrMutex);
+        int                         dev = 0;
+        B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
+        if(dev < 0 || dev >= 64 || !done[dev])
+        {
+            // the opt-in shared-memory size is a per-device property of the kernel
+            B200WMMA_CUDA_TRY(cudaFuncSetAttribute(
+                kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
+            if(dev >= 0 && dev < 64)
+                done[dev] = true;
+        }
+        return B200WMMA_OK;
+    }
+
     template <typename InT, typename OutT, typename CompT>
     int launch(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k, void const* a,
                void const* b, void const* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
                uint32_t ldd, double alpha, double beta, cudaStream_t stream)
     {
+        const int sms = b200wmma::smCount();
+        if(sms <= 0)
+            return B200WMMA_ERR_CUDA;
+        GemmParams  p{m, n, k, c, d, ldc, ldd, alpha, beta, b200wmma::deviceStatusWord()};
         CUtensorMap mapA, mapB;
-        int         rc = makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, BM);
+
+        if(pairEnabled() && m > BM && sms >= 2)
+        {
+            int rc = makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, 128);
+            if(rc != B200WMMA_OK)
+                return rc;
+            rc = makeOperandMap(&mapB, dt, sizeof(InT), b, n, k, ldb, 128);
+            if(rc != B200WMMA_OK)
+                return rc;
+            auto        kernel = gemm_tcgen05_pair_kernel<InT, OutT, CompT>;
+            static bool done[64] = {};
+            rc = optInSharedMemory(kernel, P_SMEM_BYTES, done);
+            if(rc != B200WMMA_OK)
+                return rc;
+            const uint32_t tiles = ((m + P_TILE_M - 1) / P_TILE_M) * ((n + BN - 1) / BN);
+            const uint32_t pairs = tiles < uint32_t(sms / 2) ? tiles : uint32_t(sms / 2);
+            kernel<<<2 * pairs, NUM_THREADS, P_SMEM_BYTES, stream>>>(mapA, mapB, p);
+            return b200wmma::cudaToStatus(cudaGetLastError());
+        }
+
+        int rc = makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, BM);
         if(rc != B200WMMA_OK)
             return rc;
         rc = makeOperandMap(&mapB, dt, sizeof(InT), b, n, k, ldb, BN);
         if(rc != B200WMMA_OK)
             return rc;
-
-        auto              kernel = gemm_tcgen05_kernel<InT, OutT, CompT>;
-        static std::mutex attrMutex;
-        static bool       attrDone[64] = {};
-        {
-            // the opt-in shared-memory size is a per-device property of the kernel
-            std::lock_guard<std::mutex> lock(attrMutex);
-            int                         dev = 0;
-            B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
-            if(dev < 0 || dev >= 64 || !attrDone[dev])
-            {
-                B200WMMA_CUDA_TRY(cudaFuncSetAttribute(
-                    kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)));
-                if(dev >= 0 && dev < 64)
-                    attrDone[dev] = true;
-            }
-        }
-        const int sms = b200wmma::smCount();
-        if(sms <= 0)
-            return B200WMMA_ERR_CUDA;
+        auto        kernel = gemm_tcgen05_kernel<InT, OutT, CompT>;
+        static bool done[64] = {};
+        rc = optInSharedMemory(kernel, SMEM_BYTES, done);
+        if(rc != B200WMMA_OK)
+            return rc;
         const uint32_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
         const uint32_t grid  = tiles < uint32_t(sms) ? tiles : uint32_t(sms);
-
-        GemmParams p{m, n, k, c, d, ldc, ldd, alpha, beta, b200wmma::deviceStatusWord()};
         kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(mapA, mapB, p);
         return b200wmma::cudaToStatus(cudaGetLastError());
     }

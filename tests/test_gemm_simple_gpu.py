@@ -7,7 +7,7 @@ import pytest
 
 import oracle as O
 from rocwmma_b200 import api
-from tests.cases import (GEMM_GOLDEN_CASES, SIMPLE_PAIRS, TOLERANCE, gemm_inputs)
+from tests.cases import (GEMM_GOLDEN_CASES, SIMPLE_PAIRS, TOLERANCE, gemm_inputs, tolerance)
 from tests.gpu_util import to_device, to_host
 
 pytestmark = pytest.mark.gpu
@@ -38,7 +38,7 @@ def test_simple_gemm_types_layouts_blocks(in_t, out_t, la, lb, block):
                 seed=20 + in_t)
     got, want = _run_simple(case, ROW, block)
     err = O.max_rel_err(out_t, got, want)
-    assert 0 <= err <= TOLERANCE[in_t], (err, TOLERANCE[in_t])
+    assert 0 <= err <= tolerance(in_t, out_t), (err, tolerance(in_t, out_t))
 
 
 @pytest.mark.parametrize("in_t,out_t", [(O.F16, O.F32), (O.I8, O.I32), (O.F64, O.F64)])

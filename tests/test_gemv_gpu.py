@@ -1,4 +1,7 @@
-"""GEMV through the C ABI against the oracle and the stored reference output."""
+"""GEMV through the C ABI against the oracle and the stored reference output.
+
+The kernel adds each row's products in the host routine's order with the same two
+roundings per term, so fp32 and fp64 results are required to be bit-identical."""
 import os
 
 import numpy as np
@@ -17,16 +20,18 @@ def test_gemv_against_stored_reference_output(golden_dir):
     a, x, y = gemv_inputs(256, 192, seed=11)
     got = api.gemv(O.F32, 256, 192, to_device(a, O.F32), to_device(x, O.F32), to_device(y, O.F32),
                    2.1, 2.1).cpu().numpy()
-    assert 0 <= O.max_rel_err(O.F32, got, want) <= 1e-4
+    assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("m,k", [(256, 256), (1000, 333), (4096, 4096), (3, 5), (8192, 100)])
+@pytest.mark.parametrize("m,k", [(256, 256), (1000, 333), (4096, 4096), (3, 5), (8192, 100),
+                                 (64, 1), (65, 33), (1026, 2050)])
 def test_sgemv_sizes(m, k):
     a, x, y = gemv_inputs(m, k, seed=12)
     want = O.gemv(O.F32, m, k, a, x, y, 2.1, 2.1)
     got = api.gemv(O.F32, m, k, to_device(a, O.F32), to_device(x, O.F32), to_device(y, O.F32), 2.1,
                    2.1).cpu().numpy()
-    assert 0 <= O.max_rel_err(O.F32, got, want) <= 1e-4
+    api.check_device()
+    assert np.array_equal(got, want)
 
 
 def test_dgemv_and_padded_lda():
@@ -38,7 +43,7 @@ def test_dgemv_and_padded_lda():
     want = O.gemv(O.F64, m, k, a.reshape(-1), x, y, 2.1, -0.5, lda=lda)
     got = api.gemv(O.F64, m, k, to_device(a.reshape(-1), O.F64), to_device(x, O.F64),
                    to_device(y, O.F64), 2.1, -0.5, lda=lda).cpu().numpy()
-    assert 0 <= O.max_rel_err(O.F64, got, want) <= 1e-12
+    assert np.array_equal(got, want)
 
 
 def test_config_sgemv_16384():
@@ -47,4 +52,5 @@ def test_config_sgemv_16384():
     want = O.gemv(O.F32, m, k, a, x, y, 2.1, 2.1)
     got = api.gemv(O.F32, m, k, to_device(a, O.F32), to_device(x, O.F32), to_device(y, O.F32), 2.1,
                    2.1).cpu().numpy()
-    assert 0 <= O.max_rel_err(O.F32, got, want) <= 1e-4
+    api.check_device()
+    assert np.array_equal(got, want)
