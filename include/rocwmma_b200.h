@@ -117,6 +117,41 @@ B200WMMA_API int b200wmma_gemm_host(int in_dtype, int out_dtype, uint32_t m, uin
                        int layout_a, int layout_b, void* stream);
 
 /*
+ * b200wmma_gemm for callers that cannot allocate device memory.  (This entry point has
+ * no counterpart in the reference.)
+ *
+ * Who needs it: a process whose own allocator has already claimed the whole GPU (an
+ * inference server or a training framework with a caching pool), where a cudaMalloc
+ * issued behind its back can fail or push it over its budget; and code on a latency
+ * budget, since cudaFree (and, depending on the driver, cudaMalloc) waits for the whole
+ * device and so stalls every stream that is running.  b200wmma_gemm gets the scratch it needs for non-native
+ * operand layouts (A column-major, B row-major are first transposed) from cudaMalloc on
+ * first use; this variant keeps that scratch in a fixed array inside the library image
+ * instead and calls neither cudaMalloc, cudaFree nor any other allocating routine.
+ *
+ * Same arguments, same arithmetic and same results as b200wmma_gemm, for the same type
+ * pairs except F64.  Differences:
+ *   - limit: the transposed copies, m * k' elements of A (if column-major) plus n * k'
+ *     of B (if row-major), k' = k rounded up to 16 bytes, must fit in 8 MiB together;
+ *     larger problems are refused with B200WMMA_ERR_TOO_LARGE.  Native layouts need no
+ *     scratch and have no size limit.  The array occupies 8 MiB on every GPU that loads
+ *     the library, for the life of the process.
+ *   - the first call on each device looks up the device address of that array.  Make
+ *     that first call during set-up, before any stream capture is begun.
+ *   - all calls on a device share the one array and it keeps the previous call's
+ *     contents; the entry point rewrites everything it later reads, so no clearing is
+ *     needed, but two calls whose kernels can overlap on the GPU (different streams)
+ *     race on it.  Keep calls on one device in one stream, or order them with events.
+ *   - a kernel that gives up on a bounded wait still exits cleanly, but the event is
+ *     not reported through b200wmma_check_device (that flag lives in allocated memory).
+ */
+B200WMMA_API int b200wmma_gemm_noalloc(int in_dtype, int out_dtype, uint32_t m, uint32_t n,
+                                       uint32_t k, const void* a, const void* b, const void* c,
+                                       void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                                       uint32_t ldd, double alpha, double beta, int layout_a,
+                                       int layout_b, void* stream);
+
+/*
  * y_out = alpha * A * x + beta * y_in, A column-major m x k with leading
  * dimension lda >= m (reference: samples/simple_sgemv.cpp:103-155, host routine
  * :46-67; simple_dgemv.cpp).  dtype F32 or F64.  y_out may alias y_in.

@@ -33,6 +33,8 @@ SIGNATURES = {
                            _d, _d, _i, _i, _p]),
     "b200wmma_gemm_host": (_i, [_i, _i, _u32, _u32, _u32, _p, _p, _p, _p, _u32, _u32, _u32, _u32,
                                 _d, _d, _i, _i, _p]),
+    "b200wmma_gemm_noalloc": (_i, [_i, _i, _u32, _u32, _u32, _p, _p, _p, _p, _u32, _u32, _u32, _u32,
+                                   _d, _d, _i, _i, _p]),
     "b200wmma_gemv": (_i, [_i, _u32, _u32, _p, _p, _p, _p, _d, _d, _u32, _p]),
     "b200wmma_dlrm_fwd": (_i, [_i, _p, _p, _u32, _u32, _u32, _p]),
     "b200wmma_dlrm_bwd": (_i, [_i, _p, _p, _p, _p, _u32, _u32, _u32, _p]),

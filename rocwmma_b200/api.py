@@ -80,6 +80,26 @@ def gemm(in_t, out_t, m, n, k, a, b, c, alpha, beta, layout_a=ROW_MAJOR, layout_
     return d
 
 
+def gemm_noalloc(in_t, out_t, m, n, k, a, b, c, alpha, beta, layout_a=ROW_MAJOR,
+                 layout_b=COL_MAJOR, lda=None, ldb=None, ldc=None, ldd=None, out=None,
+                 stream=None):
+    """gemm() through the entry point that never allocates device memory: the scratch for
+    transposed operand layouts is a fixed 8 MiB array inside the library.  `out` must be
+    given by callers that cannot allocate; problems whose transposed operands exceed the
+    array raise B200WmmaError (status -6).  Calls on one device must not overlap."""
+    _require_cuda(a, b, c)
+    lda = lda or _natural_ld(layout_a, m, k)
+    ldb = ldb or _natural_ld(layout_b, k, n)
+    ldc = ldc or n
+    ldd = ldd or n
+    d = out if out is not None else torch.empty(m * ldd, dtype=_TORCH[out_t], device=a.device)
+    rc = L.lib().b200wmma_gemm_noalloc(in_t, out_t, m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d),
+                                       lda, ldb, ldc, ldd, float(alpha), float(beta), layout_a,
+                                       layout_b, _stream(stream))
+    L.check(rc, "b200wmma_gemm_noalloc")
+    return d
+
+
 def gemm_host(in_t, out_t, m, n, k, a, b, c, d, alpha, beta, layout_a=ROW_MAJOR,
               layout_b=COL_MAJOR, stream=None):
     """Same with HOST tensors (ideally pinned): copies in, computes, copies D back, waits."""

@@ -668,15 +668,17 @@ namespace
         return B200WMMA_OK;
     }
 
+    // `status`: device word that records a bounded wait giving up (may be nullptr).
     template <typename InT, typename OutT, typename CompT>
-    int launch(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k, void const* a,
-               void const* b, void const* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
-               uint32_t ldd, double alpha, double beta, cudaStream_t stream)
+    int launchWithStatus(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k,
+                         void const* a, void const* b, void const* c, void* d, uint32_t lda,
+                         uint32_t ldb, uint32_t ldc, uint32_t ldd, double alpha, double beta,
+                         cudaStream_t stream, uint32_t* status)
     {
         const int sms = b200wmma::smCount();
         if(sms <= 0)
             return B200WMMA_ERR_CUDA;
-        GemmParams  p{m, n, k, c, d, ldc, ldd, alpha, beta, b200wmma::deviceStatusWord()};
+        GemmParams  p{m, n, k, c, d, ldc, ldd, alpha, beta, status};
         CUtensorMap mapA, mapB;
 
         if(pairEnabled() && m > BM && sms >= 2)
@@ -713,6 +715,16 @@ namespace
         const uint32_t grid  = tiles < uint32_t(sms) ? tiles : uint32_t(sms);
         kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(mapA, mapB, p);
         return b200wmma::cudaToStatus(cudaGetLastError());
+    }
+
+    template <typename InT, typename OutT, typename CompT>
+    int launch(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k, void const* a,
+               void const* b, void const* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+               uint32_t ldd, double alpha, double beta, cudaStream_t stream)
+    {
+        return launchWithStatus<InT, OutT, CompT>(dt, m, n, k, a, b, c, d, lda, ldb, ldc, ldd,
+                                                  alpha, beta, stream,
+                                                  b200wmma::deviceStatusWord());
     }
 
     // out[c][r] = in[r][c]: turns an MN-major operand into the K-major form the
@@ -887,4 +899,133 @@ extern "C" int b200wmma_gemm_host(int in_dtype, int out_dtype, uint32_t m, uint3
     B200WMMA_CUDA_TRY(cudaMemcpyAsync(d, dD, dBytes, cudaMemcpyDeviceToHost, s));
     B200WMMA_CUDA_TRY(cudaStreamSynchronize(s));
     return B200WMMA_OK;
+}
+
+
+// =========================================================================================
+// GEMM for callers that must not allocate
+// =========================================================================================
+namespace
+{
+    // Transposition scratch that is part of the library image instead of coming from
+    // cudaMalloc.  Every GPU that loads this library carries these 8 MiB until the process
+    // exits, whether or not the entry point below is ever called.
+    constexpr size_t NOALLOC_SCRATCH_BYTES = size_t(8) << 20;
+    static __device__ __align__(256) uint8_t g_noallocScratch[NOALLOC_SCRATCH_BYTES];
+
+    // In host code `g_noallocScratch` is only a handle for the symbol; the address a kernel
+    // can use is asked from the runtime once per device and remembered here.
+    std::mutex g_noallocMutex;
+    uint8_t*   g_noallocAddress[64] = {};
+
+    int noallocScratch(uint8_t** out)
+    {
+        int dev = -1;
+        B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
+        if(dev < 0 || dev >= 64)
+            return B200WMMA_ERR_CUDA;
+        std::lock_guard<std::mutex> lock(g_noallocMutex);
+        if(!g_noallocAddress[dev])
+        {
+            void* p = nullptr;
+            B200WMMA_CUDA_TRY(cudaGetSymbolAddress(&p, g_noallocScratch));
+            if(!p)
+                return B200WMMA_ERR_CUDA;
+            g_noallocAddress[dev] = static_cast<uint8_t*>(p);
+        }
+        *out = g_noallocAddress[dev];
+        return B200WMMA_OK;
+    }
+
+    template <typename InT, typename OutT, typename CompT>
+    int runNoAlloc(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k, void const* a,
+                   void const* b, void const* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                   uint32_t ldd, double alpha, double beta, int layoutA, int layoutB,
+                   cudaStream_t stream)
+    {
+        constexpr uint32_t E16 = 16 / sizeof(InT);
+        if(layoutA == B200WMMA_COL_MAJOR || layoutB == B200WMMA_ROW_MAJOR)
+        {
+            const uint32_t kPad   = roundUp(k, E16);
+            const size_t   aBytes = layoutA == B200WMMA_COL_MAJOR ? size_t(m) * kPad * sizeof(InT) : 0;
+            const size_t   bBytes = layoutB == B200WMMA_ROW_MAJOR ? size_t(n) * kPad * sizeof(InT) : 0;
+            const size_t   aPad   = (aBytes + 255) / 256 * 256;
+            if(aPad + bBytes > NOALLOC_SCRATCH_BYTES)
+                return B200WMMA_ERR_TOO_LARGE;
+            uint8_t* scratch = nullptr;
+            int      rc      = noallocScratch(&scratch);
+            if(rc != B200WMMA_OK)
+                return rc;
+            // The array still holds whatever the previous call left there.  Nothing has to
+            // be cleared: every element inside the [rows x k] extents the tensor maps cover
+            // is rewritten below, and the row padding beyond k is never read.
+            if(layoutA == B200WMMA_COL_MAJOR)
+            {
+                rc = transposeInto(static_cast<InT const*>(a), reinterpret_cast<InT*>(scratch), k,
+                                   m, lda, kPad, stream);
+                if(rc != B200WMMA_OK)
+                    return rc;
+                a   = scratch;
+                lda = kPad;
+            }
+            if(layoutB == B200WMMA_ROW_MAJOR)
+            {
+                rc = transposeInto(static_cast<InT const*>(b),
+                                   reinterpret_cast<InT*>(scratch + aPad), k, n, ldb, kPad, stream);
+                if(rc != B200WMMA_OK)
+                    return rc;
+                b   = scratch + aPad;
+                ldb = kPad;
+            }
+        }
+        auto misaligned = [](void const* ptr, uint32_t ld, size_t elem) {
+            return (reinterpret_cast<uintptr_t>(ptr) % 16) != 0 || (size_t(ld) * elem) % 16 != 0;
+        };
+        if(misaligned(a, lda, sizeof(InT)) || misaligned(b, ldb, sizeof(InT))
+           || misaligned(d, ldd, sizeof(OutT)) || (beta != 0.0 && misaligned(c, ldc, sizeof(OutT))))
+            return B200WMMA_ERR_ALIGNMENT;
+        if(lda < k || ldb < k || ldd < n || (beta != 0.0 && ldc < n))
+            return B200WMMA_ERR_INVALID_ARG;
+        // No status word: the library's one comes from cudaMalloc.
+        return launchWithStatus<InT, OutT, CompT>(dt, m, n, k, a, b, c, d, lda, ldb, ldc, ldd,
+                                                  alpha, beta, stream, nullptr);
+    }
+} // namespace
+
+extern "C" int b200wmma_gemm_noalloc(int in_dtype, int out_dtype, uint32_t m, uint32_t n,
+                                     uint32_t k, const void* a, const void* b, const void* c,
+                                     void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                                     uint32_t ldd, double alpha, double beta, int layout_a,
+                                     int layout_b, void* stream)
+{
+    if(!a || !b || !d || m == 0 || n == 0 || k == 0)
+        return B200WMMA_ERR_INVALID_ARG;
+    if(beta != 0.0 && !c)
+        return B200WMMA_ERR_INVALID_ARG;
+    if((layout_a != B200WMMA_ROW_MAJOR && layout_a != B200WMMA_COL_MAJOR)
+       || (layout_b != B200WMMA_ROW_MAJOR && layout_b != B200WMMA_COL_MAJOR))
+        return B200WMMA_ERR_INVALID_ARG;
+    auto s = static_cast<cudaStream_t>(stream);
+#define B200WMMA_NOALLOC_CASE(I, O, IT, OT, CT, TM)                                            \
+    if(in_dtype == I && out_dtype == O)                                                        \
+        return runNoAlloc<IT, OT, CT>(TM, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, \
+                                      layout_a, layout_b, s);
+    B200WMMA_NOALLOC_CASE(B200WMMA_F16, B200WMMA_F16, __half, __half, float,
+                          CU_TENSOR_MAP_DATA_TYPE_FLOAT16)
+    B200WMMA_NOALLOC_CASE(B200WMMA_F16, B200WMMA_F32, __half, float, float,
+                          CU_TENSOR_MAP_DATA_TYPE_FLOAT16)
+    B200WMMA_NOALLOC_CASE(B200WMMA_BF16, B200WMMA_F32, __nv_bfloat16, float, float,
+                          CU_TENSOR_MAP_DATA_TYPE_BFLOAT16)
+    B200WMMA_NOALLOC_CASE(B200WMMA_BF16, B200WMMA_BF16, __nv_bfloat16, __nv_bfloat16, float,
+                          CU_TENSOR_MAP_DATA_TYPE_BFLOAT16)
+    B200WMMA_NOALLOC_CASE(B200WMMA_XF32, B200WMMA_F32, float, float, float,
+                          CU_TENSOR_MAP_DATA_TYPE_FLOAT32)
+    B200WMMA_NOALLOC_CASE(B200WMMA_I8, B200WMMA_I32, int8_t, int32_t, int32_t,
+                          CU_TENSOR_MAP_DATA_TYPE_UINT8)
+    B200WMMA_NOALLOC_CASE(B200WMMA_E4M3, B200WMMA_BF16, __nv_fp8_e4m3, __nv_bfloat16, float,
+                          CU_TENSOR_MAP_DATA_TYPE_UINT8)
+    B200WMMA_NOALLOC_CASE(B200WMMA_E4M3, B200WMMA_F32, __nv_fp8_e4m3, float, float,
+                          CU_TENSOR_MAP_DATA_TYPE_UINT8)
+#undef B200WMMA_NOALLOC_CASE
+    return B200WMMA_ERR_UNSUPPORTED;
 }
