@@ -25,6 +25,7 @@
 //
 // Limits: fp16, m <= 32, k a multiple of 16 and <= 256, pointers 16-byte aligned.
 #include "common.cuh"
+#include <cstdlib>
 #include <cuda_fp16.h>
 
 namespace
@@ -32,7 +33,7 @@ namespace
     constexpr uint32_t GROUP   = 8; // samples per aligned group
     constexpr uint32_t MAX_K   = 256;
     constexpr uint32_t G_LD    = 40; // halves per row of the 32x32 G tile (80 bytes)
-    constexpr uint32_t MAX_WARPS = 8;
+    constexpr uint32_t MAX_WARPS = 12;
     constexpr uint32_t ZERO_BYTES = MAX_K * 2 + 16;
 
     __device__ inline uint32_t smemAddr(void const* p)
@@ -260,17 +261,15 @@ namespace
         const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
         const uint32_t g = lane >> 2, t = lane & 3;
 
-        // layout: [zero row][triangle index table][warp 0: ring, 2 x upstream group, G][...]
+        // layout: [zero row][triangle index table][warp 0: ring, G][warp 1: ...]
         const uint32_t triCount   = sh.m * (sh.m - 1) / 2;
         const uint32_t triBytes   = (triCount * 2 + 15) / 16 * 16;
-        const uint32_t upBytes    = GROUP * sh.outLen * 2;
         const uint32_t gBytes     = 32 * G_LD * 2;
-        const uint32_t perWarp    = NSTAGES * sh.stageBytes + 2 * upBytes + gBytes;
+        const uint32_t perWarp    = NSTAGES * sh.stageBytes + gBytes;
         uint8_t*       zeroRow    = smem;
         uint16_t*      tri        = reinterpret_cast<uint16_t*>(smem + ZERO_BYTES);
         uint8_t*       mine       = smem + ZERO_BYTES + triBytes + warp * perWarp;
-        uint8_t*       upStage    = mine + NSTAGES * sh.stageBytes;
-        __half*        gTile      = reinterpret_cast<__half*>(upStage + 2 * upBytes);
+        __half*        gTile      = reinterpret_cast<__half*>(mine + NSTAGES * sh.stageBytes);
         const uint32_t ringAddr   = smemAddr(mine);
         const uint32_t zeroAddr   = smemAddr(zeroRow);
         const uint32_t gAddr      = smemAddr(gTile);
@@ -294,28 +293,30 @@ namespace
         const uint32_t numQ = myGroups * GROUP;
         const bool     twoM = sh.m > 16;
 
-        // Issues sample q; with the first sample of a group also the group's upstream rows.
         auto issue = [&](uint32_t q) {
             const uint32_t s = sampleOf(q, warpGlobal, totalWarps);
-            if(s >= sh.batch)
-                return;
-            issueSample(ringAddr + (q % NSTAGES) * sh.stageBytes, input + size_t(s) * sh.m * sh.k,
-                        sh, lane);
-            if(q % GROUP == 0)
+            if(s < sh.batch)
+                issueSample(ringAddr + (q % NSTAGES) * sh.stageBytes,
+                            input + size_t(s) * sh.m * sh.k, sh, lane);
+        };
+
+        // The packed upstream row of a sample is only 2-byte aligned, and each value is used
+        // once, so it never goes through shared memory: a lane reads its share of the NEXT
+        // sample's triangle (entries lane, lane+32, ...) into registers one iteration ahead;
+        // a warp-wide 2-byte load covers 64 contiguous bytes.
+        constexpr uint32_t TRI_REGS = 16; // ceil(496 / 32) for m = 32
+        __half             triNext[TRI_REGS];
+        auto prefetchTriangle = [&](uint32_t q) {
+            const uint32_t s = q < numQ ? sampleOf(q, warpGlobal, totalWarps) : sh.batch;
+            if(s < sh.batch)
             {
-                uint8_t*       dst = upStage + ((q / GROUP) & 1u) * upBytes;
-                const uint32_t cnt = min(GROUP, sh.batch - s);
-                __half const*  src = upstream + size_t(s) * sh.outLen;
-                if(cnt == GROUP)
+                __half const* src = upstream + size_t(s) * sh.outLen + sh.k;
+#pragma unroll
+                for(uint32_t i = 0; i < TRI_REGS; ++i)
                 {
-                    for(uint32_t i = lane; i < sh.outLen; i += 32)
-                        cpAsync16(smemAddr(dst) + i * 16,
-                                  reinterpret_cast<uint8_t const*>(src) + size_t(i) * 16);
-                }
-                else
-                {
-                    for(uint32_t i = lane; i < cnt * sh.outLen; i += 32)
-                        reinterpret_cast<__half*>(dst)[i] = src[i];
+                    const uint32_t idx = i * 32u + lane;
+                    if(idx < triCount)
+                        triNext[i] = src[idx];
                 }
             }
         };
@@ -327,6 +328,7 @@ namespace
                 issue(q);
             cpAsyncCommit();
         }
+        prefetchTriangle(0);
 
         const uint32_t lmRow = ((lane >> 3) & 1u) * 8u + (lane & 7u);
         const uint32_t lmCol = (lane >> 4) * 8u;
@@ -341,31 +343,36 @@ namespace
 
             const uint32_t sample = sampleOf(q, warpGlobal, totalWarps);
             if(sample >= sh.batch)
-                continue;
-            const uint32_t slot     = q % GROUP;
+                continue; // only the padding of the last group; nothing follows it
             uint8_t*       slotPtr  = mine + (q % NSTAGES) * sh.stageBytes;
             const uint32_t slotAddr = ringAddr + (q % NSTAGES) * sh.stageBytes;
-            __half const*  up = reinterpret_cast<__half const*>(upStage + ((q / GROUP) & 1u) * upBytes)
-                               + slot * sh.outLen;
 
-            // bottom-MLP gradient: the first k upstream values
-            for(uint32_t c = lane; c < sh.k / 8; c += 32)
-            {
-                alignas(16) __half v[8];
+            // this sample's triangle (fetched one iteration ago), then start on the next one's
+            __half triCur[TRI_REGS];
 #pragma unroll
-                for(uint32_t e = 0; e < 8; ++e)
-                    v[e] = up[c * 8 + e];
-                reinterpret_cast<uint4*>(mlpGrad + size_t(sample) * sh.k)[c]
-                    = *reinterpret_cast<uint4 const*>(v);
+            for(uint32_t i = 0; i < TRI_REGS; ++i)
+                triCur[i] = triNext[i];
+            prefetchTriangle(q + 1);
+
+            // bottom-MLP gradient: the first k upstream values, copied as they are
+            {
+                __half const* up  = upstream + size_t(sample) * sh.outLen;
+                __half*       dst = mlpGrad + size_t(sample) * sh.k;
+                for(uint32_t j = lane; j < sh.k; j += 32)
+                    dst[j] = up[j];
             }
 
             // symmetric G (fp16, zero diagonal) from the packed triangle
-            for(uint32_t i = lane; i < triCount; i += 32)
+#pragma unroll
+            for(uint32_t i = 0; i < TRI_REGS; ++i)
             {
-                const uint32_t rc = tri[i], r = rc >> 8, c = rc & 0xffu;
-                const __half   v  = up[sh.k + i];
-                gTile[r * G_LD + c] = v;
-                gTile[c * G_LD + r] = v;
+                const uint32_t idx = i * 32u + lane;
+                if(idx < triCount)
+                {
+                    const uint32_t rc = tri[idx], r = rc >> 8, c = rc & 0xffu;
+                    gTile[r * G_LD + c] = triCur[i];
+                    gTile[c * G_LD + r] = triCur[i];
+                }
             }
             __syncwarp();
 
@@ -495,17 +502,30 @@ namespace
     {
         uint32_t warps = 0, stages = 0, smemBytes = 0;
     };
+    // With one sample per warp every dependent latency inside a sample is hidden only by
+    // other warps, so warps count first; a second ring slot is all a warp needs to keep a
+    // load in flight while it computes, a third helps when few warps fit.
+    // B200WMMA_DLRM_STAGES / B200WMMA_DLRM_WARPS override the choice (tuning only).
     Plan choosePlan(uint32_t fixedBytes, uint32_t stageBytes, uint32_t otherPerWarp)
     {
+        const char* es = getenv("B200WMMA_DLRM_STAGES");
+        const char* ew = getenv("B200WMMA_DLRM_WARPS");
+        const uint32_t forceStages = es ? uint32_t(atoi(es)) : 0u;
+        const uint32_t forceWarps  = ew ? uint32_t(atoi(ew)) : 0u;
         Plan best;
-        for(uint32_t stages = 3; stages >= 2; --stages)
+        for(uint32_t stages = 2; stages <= 3; ++stages)
         {
+            if(forceStages && stages != forceStages)
+                continue;
             const uint32_t perWarp = stages * stageBytes + otherPerWarp;
             if(fixedBytes + perWarp > SMEM_LIMIT)
                 continue;
             uint32_t warps = (SMEM_LIMIT - fixedBytes) / perWarp;
             warps          = warps > MAX_WARPS ? MAX_WARPS : warps;
-            if(warps * (stages - 1) > best.warps * (best.stages ? best.stages - 1 : 0))
+            if(forceWarps && forceWarps < warps)
+                warps = forceWarps;
+            // 3 slots only if that costs no warps
+            if(warps > best.warps || (warps == best.warps && stages > best.stages))
             {
                 best.warps     = warps;
                 best.stages    = stages;
@@ -573,8 +593,7 @@ extern "C" int b200wmma_dlrm_bwd(int dtype, const void* input, const void* upstr
     if(!aligned16(input) || !aligned16(upstream) || !aligned16(grad) || !aligned16(mlp_grad))
         return B200WMMA_ERR_ALIGNMENT;
     const uint32_t triBytes = (m * (m - 1) / 2 * 2 + 15) / 16 * 16;
-    const Plan     plan     = choosePlan(ZERO_BYTES + triBytes, sh.stageBytes,
-                                 2 * GROUP * sh.outLen * 2 + 32 * G_LD * 2);
+    const Plan     plan     = choosePlan(ZERO_BYTES + triBytes, sh.stageBytes, 32 * G_LD * 2);
     if(plan.warps == 0)
         return B200WMMA_ERR_UNSUPPORTED;
     const int sms = b200wmma::smCount();

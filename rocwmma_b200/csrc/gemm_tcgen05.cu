@@ -69,6 +69,7 @@ namespace
         uint32_t    ldc, ldd;
         double      alpha, beta;
         uint32_t*   status;
+        uint32_t    chunkKB; // k-blocks per accumulation chain; 0 = all of K in one chain
     };
 
     template <typename T>
@@ -141,14 +142,29 @@ namespace
         return OutT(v); // __half(float), __nv_bfloat16(float): round to nearest even
     }
 
+    // How one pass of the epilogue treats the accumulator it just read.  With chunked K
+    // accumulation (fp32 outputs only) D doubles as the fp32 running sum between chunks.
+    enum EpilogueMode : uint32_t
+    {
+        EPI_WHOLE  = 0, // D = alpha * acc + beta * C            (K accumulated in one chain)
+        EPI_FIRST  = 1, // D = acc                               (first chunk of several)
+        EPI_MIDDLE = 2, // D = D + acc
+        EPI_LAST   = 3  // D = alpha * (D + acc) + beta * C
+    };
+
     // Stores (and optionally reads C for) 32 consecutive columns of one output row.
     template <typename OutT, typename CompT>
     __device__ inline void epilogueRow(uint32_t const (&raw)[32], GemmParams const& p, CompT alpha,
-                                       CompT beta, bool useC, uint32_t row, uint32_t col0)
+                                       CompT beta, bool useC, uint32_t row, uint32_t col0,
+                                       uint32_t mode = EPI_WHOLE)
     {
         constexpr uint32_t VEC = 16 / sizeof(OutT); // elements per 128-bit access
+        constexpr bool     CAN_CHUNK
+            = std::is_same<OutT, float>::value && std::is_same<CompT, float>::value;
         OutT const*        cRow = static_cast<OutT const*>(p.c) + size_t(row) * p.ldc;
         OutT*              dRow = static_cast<OutT*>(p.d) + size_t(row) * p.ldd;
+        const bool         readC = useC && (mode == EPI_WHOLE || mode == EPI_LAST);
+        const bool         readD = CAN_CHUNK && (mode == EPI_MIDDLE || mode == EPI_LAST);
 #pragma unroll
         for(uint32_t v = 0; v < 32 / VEC; ++v)
         {
@@ -157,14 +173,23 @@ namespace
                 break;
             alignas(16) OutT out[VEC];
             alignas(16) OutT cin[VEC];
+            alignas(16) OutT din[VEC];
             const bool       whole = (col + VEC <= p.n);
-            if(useC)
+            if(readC)
             {
                 if(whole)
                     *reinterpret_cast<uint4*>(cin) = *reinterpret_cast<uint4 const*>(cRow + col);
                 else
                     for(uint32_t e = 0; e < VEC; ++e)
                         cin[e] = (col + e < p.n) ? cRow[col + e] : OutT(0);
+            }
+            if(readD)
+            {
+                if(whole)
+                    *reinterpret_cast<uint4*>(din) = *reinterpret_cast<uint4 const*>(dRow + col);
+                else
+                    for(uint32_t e = 0; e < VEC; ++e)
+                        din[e] = (col + e < p.n) ? dRow[col + e] : OutT(0);
             }
 #pragma unroll
             for(uint32_t e = 0; e < VEC; ++e)
@@ -174,11 +199,21 @@ namespace
                     acc = __uint_as_float(raw[v * VEC + e]);
                 else
                     acc = int32_t(raw[v * VEC + e]);
-                CompT r = useC ? scaleAdd(alpha, acc, beta, CompT(toCompute(cin[e])))
-                               : (std::is_same<CompT, float>::value
-                                      ? CompT(__fmul_rn(float(alpha), float(acc)))
-                                      : CompT(alpha * acc));
-                out[e]  = fromCompute<OutT, CompT>(r);
+                if constexpr(CAN_CHUNK)
+                {
+                    if(readD)
+                        acc = __fadd_rn(float(din[e]), acc);
+                }
+                CompT r;
+                if(mode == EPI_FIRST || mode == EPI_MIDDLE)
+                    r = acc;
+                else if(readC)
+                    r = scaleAdd(alpha, acc, beta, CompT(toCompute(cin[e])));
+                else if constexpr(std::is_same<CompT, float>::value)
+                    r = CompT(__fmul_rn(float(alpha), float(acc)));
+                else
+                    r = CompT(alpha * acc);
+                out[e] = fromCompute<OutT, CompT>(r);
             }
             if(whole)
                 *reinterpret_cast<uint4*>(dRow + col) = *reinterpret_cast<uint4 const*>(out);
@@ -212,6 +247,8 @@ namespace
         const uint32_t tilesN   = (p.n + BN - 1) / BN;
         const uint32_t numTiles = tilesM * tilesN;
         const uint32_t numKB    = (p.k + BK - 1) / BK;
+        const uint32_t chunkKB  = p.chunkKB != 0u ? p.chunkKB : numKB; // K blocks per chain
+        const uint32_t numChunks = (numKB + chunkKB - 1) / chunkKB;
 
         if(threadIdx.x == 0)
         {
@@ -292,42 +329,49 @@ namespace
             // ---------------- MMA issuer ----------------
             if(elect_one())
             {
-                uint32_t it = 0, tileIter = 0;
+                uint32_t it = 0, accIter = 0;
                 bool     ok = true;
-                for(uint32_t t = blockIdx.x; ok && t < numTiles; t += gridDim.x, ++tileIter)
+                for(uint32_t t = blockIdx.x; ok && t < numTiles; t += gridDim.x)
                 {
-                    const uint32_t buf   = tileIter & 1u;
-                    const uint32_t accPh = (tileIter >> 1) & 1u;
-                    if(!mbar_wait(&ctl->accEmpty[buf], accPh ^ 1u, &ctl->abort, WAIT_ACC_EMPTY))
+                    // one accumulation chain per chunk of K, alternating TMEM buffers
+                    for(uint32_t kb0 = 0; ok && kb0 < numKB; kb0 += chunkKB, ++accIter)
                     {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t dTmem = tmemBase + buf * BN;
-                    for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
-                    {
-                        const uint32_t s  = it % STAGES;
-                        const uint32_t ph = (it / STAGES) & 1u;
-                        if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
+                        const uint32_t buf   = accIter & 1u;
+                        const uint32_t accPh = (accIter >> 1) & 1u;
+                        if(!mbar_wait(&ctl->accEmpty[buf], accPh ^ 1u, &ctl->abort,
+                                      WAIT_ACC_EMPTY))
                         {
                             ok = false;
                             break;
                         }
                         tc_fence_after_sync();
-                        const uint32_t aAddr = smem_addr(tiles + s * STAGE_BYTES);
-                        const uint32_t bAddr = aAddr + A_BYTES;
-#pragma unroll
-                        for(uint32_t ks = 0; ks < BK / UMMA_K; ++ks)
+                        const uint32_t dTmem = tmemBase + buf * BN;
+                        const uint32_t kb1   = min(numKB, kb0 + chunkKB);
+                        for(uint32_t kb = kb0; kb < kb1; ++kb, ++it)
                         {
-                            const uint64_t da = smem_desc_kmajor_sw128(aAddr + ks * 32u);
-                            const uint64_t db = smem_desc_kmajor_sw128(bAddr + ks * 32u);
-                            mma_ss<KindOf<InT>::kind>(dTmem, da, db, IDESC, (kb | ks) != 0u);
+                            const uint32_t s  = it % STAGES;
+                            const uint32_t ph = (it / STAGES) & 1u;
+                            if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
+                            {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            const uint32_t aAddr = smem_addr(tiles + s * STAGE_BYTES);
+                            const uint32_t bAddr = aAddr + A_BYTES;
+#pragma unroll
+                            for(uint32_t ks = 0; ks < BK / UMMA_K; ++ks)
+                            {
+                                const uint64_t da = smem_desc_kmajor_sw128(aAddr + ks * 32u);
+                                const uint64_t db = smem_desc_kmajor_sw128(bAddr + ks * 32u);
+                                mma_ss<KindOf<InT>::kind>(dTmem, da, db, IDESC,
+                                                          (kb > kb0 || ks > 0u) ? 1u : 0u);
+                            }
+                            mma_commit(&ctl->empty[s]); // slot reusable once these MMAs are done
                         }
-                        mma_commit(&ctl->empty[s]); // slot reusable once these MMAs are done
+                        if(ok)
+                            mma_commit(&ctl->accFull[buf]); // this chain is complete
                     }
-                    if(ok)
-                        mma_commit(&ctl->accFull[buf]); // accumulator complete
                 }
             }
         }
@@ -338,31 +382,43 @@ namespace
             const CompT    alpha = CompT(p.alpha);
             const CompT    beta  = CompT(p.beta);
             const bool     useC  = (p.beta != 0.0) && (p.c != nullptr);
-            uint32_t       tileIter = 0;
-            for(uint32_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileIter)
+            uint32_t       accIter = 0;
+            bool           ok      = true;
+            for(uint32_t t = blockIdx.x; ok && t < numTiles; t += gridDim.x)
             {
                 uint32_t tm, tn;
                 tileCoord(t, tilesM, tilesN, tm, tn);
-                const uint32_t buf   = tileIter & 1u;
-                const uint32_t accPh = (tileIter >> 1) & 1u;
-                if(!mbar_wait(&ctl->accFull[buf], accPh, &ctl->abort, WAIT_ACC_FULL))
-                    break;
-                tc_fence_after_sync();
                 const uint32_t row = tm * BM + quad * 32 + lane;
-#pragma unroll 1
-                for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+                for(uint32_t ch = 0; ch < numChunks; ++ch, ++accIter)
                 {
-                    uint32_t       raw[32];
-                    __syncwarp(); // rows masked off below rejoin before the warp-wide load
-                    const uint32_t taddr = tmemBase + ((quad * 32u) << 16) + buf * BN + chunk * 32u;
-                    tmem_load_32x32b_x32(taddr, raw); // warp-wide: no divergence before it
-                    tmem_load_wait();
-                    const uint32_t col0 = tn * BN + chunk * 32;
-                    if(row < p.m && col0 < p.n)
-                        epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0);
+                    const uint32_t buf   = accIter & 1u;
+                    const uint32_t accPh = (accIter >> 1) & 1u;
+                    if(!mbar_wait(&ctl->accFull[buf], accPh, &ctl->abort, WAIT_ACC_FULL))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t mode = numChunks == 1u       ? EPI_WHOLE
+                                          : ch == 0u            ? EPI_FIRST
+                                          : ch + 1u < numChunks ? EPI_MIDDLE
+                                                                : EPI_LAST;
+#pragma unroll 1
+                    for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+                    {
+                        uint32_t raw[32];
+                        __syncwarp(); // rows masked off below rejoin before the warp-wide load
+                        const uint32_t taddr
+                            = tmemBase + ((quad * 32u) << 16) + buf * BN + chunk * 32u;
+                        tmem_load_32x32b_x32(taddr, raw); // warp-wide: no divergence before it
+                        tmem_load_wait();
+                        const uint32_t col0 = tn * BN + chunk * 32;
+                        if(row < p.m && col0 < p.n)
+                            epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0, mode);
+                    }
+                    tc_fence_before_sync();
+                    mbar_arrive(&ctl->accEmpty[buf]);
                 }
-                tc_fence_before_sync();
-                mbar_arrive(&ctl->accEmpty[buf]);
             }
         }
 
@@ -439,6 +495,8 @@ namespace
         const uint32_t tilesN   = (p.n + BN - 1) / BN;
         const uint32_t numTiles = tilesM * tilesN;
         const uint32_t numKB    = (p.k + BK - 1) / BK;
+        const uint32_t chunkKB  = p.chunkKB != 0u ? p.chunkKB : numKB; // K blocks per chain
+        const uint32_t numChunks = (numKB + chunkKB - 1) / chunkKB;
 
         if(threadIdx.x == 0)
         {
@@ -507,42 +565,48 @@ namespace
             // ---------------- MMA issuer (leader block only) ----------------
             if(rank == 0 && elect_one())
             {
-                uint32_t it = 0, tileIter = 0;
+                uint32_t it = 0, accIter = 0;
                 bool     ok = true;
-                for(uint32_t t = pairId; ok && t < numTiles; t += nPairs, ++tileIter)
+                for(uint32_t t = pairId; ok && t < numTiles; t += nPairs)
                 {
-                    const uint32_t buf   = tileIter & 1u;
-                    const uint32_t accPh = (tileIter >> 1) & 1u;
-                    if(!mbar_wait(&ctl->accEmpty[buf], accPh ^ 1u, &ctl->abort, WAIT_ACC_EMPTY))
+                    for(uint32_t kb0 = 0; ok && kb0 < numKB; kb0 += chunkKB, ++accIter)
                     {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t dTmem = tmemBase + buf * BN;
-                    for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
-                    {
-                        const uint32_t s  = it % P_STAGES;
-                        const uint32_t ph = (it / P_STAGES) & 1u;
-                        if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
+                        const uint32_t buf   = accIter & 1u;
+                        const uint32_t accPh = (accIter >> 1) & 1u;
+                        if(!mbar_wait(&ctl->accEmpty[buf], accPh ^ 1u, &ctl->abort,
+                                      WAIT_ACC_EMPTY))
                         {
                             ok = false;
                             break;
                         }
                         tc_fence_after_sync();
-                        const uint32_t aAddr = smem_addr(tiles + s * P_STAGE_BYTES);
-                        const uint32_t bAddr = aAddr + P_A_BYTES;
-#pragma unroll
-                        for(uint32_t ks = 0; ks < BK / UMMA_K; ++ks)
+                        const uint32_t dTmem = tmemBase + buf * BN;
+                        const uint32_t kb1   = min(numKB, kb0 + chunkKB);
+                        for(uint32_t kb = kb0; kb < kb1; ++kb, ++it)
                         {
-                            const uint64_t da = smem_desc_kmajor_sw128(aAddr + ks * 32u);
-                            const uint64_t db = smem_desc_kmajor_sw128(bAddr + ks * 32u);
-                            mma_ss_pair<KindOf<InT>::kind>(dTmem, da, db, IDESC, (kb | ks) != 0u);
+                            const uint32_t s  = it % P_STAGES;
+                            const uint32_t ph = (it / P_STAGES) & 1u;
+                            if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
+                            {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            const uint32_t aAddr = smem_addr(tiles + s * P_STAGE_BYTES);
+                            const uint32_t bAddr = aAddr + P_A_BYTES;
+#pragma unroll
+                            for(uint32_t ks = 0; ks < BK / UMMA_K; ++ks)
+                            {
+                                const uint64_t da = smem_desc_kmajor_sw128(aAddr + ks * 32u);
+                                const uint64_t db = smem_desc_kmajor_sw128(bAddr + ks * 32u);
+                                mma_ss_pair<KindOf<InT>::kind>(dTmem, da, db, IDESC,
+                                                               (kb > kb0 || ks > 0u) ? 1u : 0u);
+                            }
+                            mma_commit_pair(&ctl->empty[s], 0x3); // frees the slot in both blocks
                         }
-                        mma_commit_pair(&ctl->empty[s], 0x3); // frees the slot in both blocks
+                        if(ok)
+                            mma_commit_pair(&ctl->accFull[buf], 0x3);
                     }
-                    if(ok)
-                        mma_commit_pair(&ctl->accFull[buf], 0x3);
                 }
             }
         }
@@ -553,31 +617,43 @@ namespace
             const CompT    alpha = CompT(p.alpha);
             const CompT    beta  = CompT(p.beta);
             const bool     useC  = (p.beta != 0.0) && (p.c != nullptr);
-            uint32_t       tileIter = 0;
-            for(uint32_t t = pairId; t < numTiles; t += nPairs, ++tileIter)
+            uint32_t       accIter = 0;
+            bool           ok      = true;
+            for(uint32_t t = pairId; ok && t < numTiles; t += nPairs)
             {
                 uint32_t tm, tn;
                 tileCoord(t, tilesM, tilesN, tm, tn);
-                const uint32_t buf   = tileIter & 1u;
-                const uint32_t accPh = (tileIter >> 1) & 1u;
-                if(!mbar_wait(&ctl->accFull[buf], accPh, &ctl->abort, WAIT_ACC_FULL))
-                    break;
-                tc_fence_after_sync();
                 const uint32_t row = tm * P_TILE_M + rank * 128u + quad * 32u + lane;
-#pragma unroll 1
-                for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+                for(uint32_t ch = 0; ch < numChunks; ++ch, ++accIter)
                 {
-                    uint32_t raw[32];
-                    __syncwarp();
-                    const uint32_t taddr = tmemBase + ((quad * 32u) << 16) + buf * BN + chunk * 32u;
-                    tmem_load_32x32b_x32(taddr, raw);
-                    tmem_load_wait();
-                    const uint32_t col0 = tn * BN + chunk * 32;
-                    if(row < p.m && col0 < p.n)
-                        epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0);
+                    const uint32_t buf   = accIter & 1u;
+                    const uint32_t accPh = (accIter >> 1) & 1u;
+                    if(!mbar_wait(&ctl->accFull[buf], accPh, &ctl->abort, WAIT_ACC_FULL))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t mode = numChunks == 1u       ? EPI_WHOLE
+                                          : ch == 0u            ? EPI_FIRST
+                                          : ch + 1u < numChunks ? EPI_MIDDLE
+                                                                : EPI_LAST;
+#pragma unroll 1
+                    for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+                    {
+                        uint32_t raw[32];
+                        __syncwarp();
+                        const uint32_t taddr
+                            = tmemBase + ((quad * 32u) << 16) + buf * BN + chunk * 32u;
+                        tmem_load_32x32b_x32(taddr, raw);
+                        tmem_load_wait();
+                        const uint32_t col0 = tn * BN + chunk * 32;
+                        if(row < p.m && col0 < p.n)
+                            epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0, mode);
+                    }
+                    tc_fence_before_sync();
+                    mbar_arrive_cluster(map_to_cta(smem_addr(&ctl->accEmpty[buf]), 0));
                 }
-                tc_fence_before_sync();
-                mbar_arrive_cluster(map_to_cta(smem_addr(&ctl->accEmpty[buf]), 0));
             }
         }
 
@@ -678,7 +754,20 @@ namespace
         const int sms = b200wmma::smCount();
         if(sms <= 0)
             return B200WMMA_ERR_CUDA;
-        GemmParams  p{m, n, k, c, d, ldc, ldd, alpha, beta, status};
+        // xf32 -> fp32: the tensor core's fp32 accumulator truncates when it aligns addends, a
+        // bias that grows with the length of the accumulation chain (measured: 5e-4 in the
+        // parity metric after 4096 terms).  Chains are therefore cut every 512 elements of K
+        // and the partial sums are added in fp32 with round-to-nearest by the epilogue, using
+        // D as the running sum.  Not possible in place (c == d with beta != 0).
+        uint32_t chunkKB = 0;
+        if(std::is_same<InT, float>::value && std::is_same<OutT, float>::value
+           && !(beta != 0.0 && c == d))
+        {
+            constexpr uint32_t kbPerChunk = 512u / (ROW_BYTES / uint32_t(sizeof(InT)));
+            if((k + ROW_BYTES / sizeof(InT) - 1) / (ROW_BYTES / sizeof(InT)) > kbPerChunk)
+                chunkKB = kbPerChunk;
+        }
+        GemmParams  p{m, n, k, c, d, ldc, ldd, alpha, beta, status, chunkKB};
         CUtensorMap mapA, mapB;
 
         if(pairEnabled() && m > BM && sms >= 2)
@@ -888,6 +977,57 @@ extern "C" int b200wmma_gemm_host(int in_dtype, int out_dtype, uint32_t m, uint3
     void*        dD     = b200wmma::stagingBuffer(3, dBytes);
     if(!dA || !dB || !dD || (cBytes && !dC))
         return B200WMMA_ERR_CUDA;
+    // Pipelined form (A row-major): B goes first, then A (and C) in row slabs on a copy
+    // stream; the GEMM of slab i runs as soon as slab i has landed, and its rows of D return
+    // on a second copy stream while later slabs are still arriving.  The transfer of the
+    // inputs is the critical path; compute and the D copies hide behind it.
+    b200wmma::HostPipe* pipe = b200wmma::hostPipe();
+    if(pipe && layout_a == B200WMMA_ROW_MAJOR && m >= 1024)
+    {
+        const uint32_t nChunks   = 8;
+        const uint32_t chunkRows = ((m + nChunks - 1) / nChunks + 255) / 256 * 256;
+        B200WMMA_CUDA_TRY(cudaEventRecord(pipe->start, s));
+        B200WMMA_CUDA_TRY(cudaStreamWaitEvent(pipe->h2d, pipe->start, 0));
+        B200WMMA_CUDA_TRY(cudaStreamWaitEvent(pipe->d2h, pipe->start, 0));
+        B200WMMA_CUDA_TRY(cudaMemcpyAsync(dB, b, bBytes, cudaMemcpyHostToDevice, pipe->h2d));
+        B200WMMA_CUDA_TRY(cudaEventRecord(pipe->bReady, pipe->h2d));
+        B200WMMA_CUDA_TRY(cudaStreamWaitEvent(s, pipe->bReady, 0));
+        uint32_t chunk = 0;
+        for(uint32_t r0 = 0; r0 < m; r0 += chunkRows, ++chunk)
+        {
+            const uint32_t rows = (m - r0) < chunkRows ? (m - r0) : chunkRows;
+            const size_t   aOff = size_t(r0) * lda * inB, cOff = size_t(r0) * ldc * outB;
+            const size_t   dOff = size_t(r0) * ldd * outB;
+            B200WMMA_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(dA) + aOff,
+                                              static_cast<uint8_t const*>(a) + aOff,
+                                              size_t(rows) * lda * inB, cudaMemcpyHostToDevice,
+                                              pipe->h2d));
+            if(cBytes)
+                B200WMMA_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(dC) + cOff,
+                                                  static_cast<uint8_t const*>(c) + cOff,
+                                                  size_t(rows) * ldc * outB,
+                                                  cudaMemcpyHostToDevice, pipe->h2d));
+            B200WMMA_CUDA_TRY(cudaEventRecord(pipe->in[chunk], pipe->h2d));
+            B200WMMA_CUDA_TRY(cudaStreamWaitEvent(s, pipe->in[chunk], 0));
+            int rc = b200wmma_gemm(in_dtype, out_dtype, rows, n, k,
+                                   static_cast<uint8_t*>(dA) + aOff, dB,
+                                   cBytes ? static_cast<uint8_t*>(dC) + cOff : nullptr,
+                                   static_cast<uint8_t*>(dD) + dOff, lda, ldb, ldc, ldd, alpha,
+                                   beta, layout_a, layout_b, stream);
+            if(rc != B200WMMA_OK)
+                return rc;
+            B200WMMA_CUDA_TRY(cudaEventRecord(pipe->out[chunk], s));
+            B200WMMA_CUDA_TRY(cudaStreamWaitEvent(pipe->d2h, pipe->out[chunk], 0));
+            B200WMMA_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(d) + dOff,
+                                              static_cast<uint8_t*>(dD) + dOff,
+                                              size_t(rows) * ldd * outB, cudaMemcpyDeviceToHost,
+                                              pipe->d2h));
+        }
+        B200WMMA_CUDA_TRY(cudaStreamSynchronize(pipe->d2h));
+        B200WMMA_CUDA_TRY(cudaStreamSynchronize(s));
+        return B200WMMA_OK;
+    }
+
     B200WMMA_CUDA_TRY(cudaMemcpyAsync(dA, a, aBytes, cudaMemcpyHostToDevice, s));
     B200WMMA_CUDA_TRY(cudaMemcpyAsync(dB, b, bBytes, cudaMemcpyHostToDevice, s));
     if(cBytes)

@@ -23,6 +23,7 @@
 // kernel with the same summation order is used.
 #include "common.cuh"
 #include "runtime.cuh"
+#include <cstdlib>
 #include <cuda.h>
 #include <mutex>
 #include <rocwmma/rocwmma_block.hpp>
@@ -31,26 +32,30 @@ using namespace rocwmma::block;
 
 namespace
 {
-    constexpr uint32_t ROWS        = 64; // rows per block == compute threads
-    constexpr uint32_t TILE_BYTES  = 8192; // one ring slot: ROWS x COLS elements
-    constexpr uint32_t STAGES      = 10;
-    constexpr uint32_t THREADS     = ROWS + 32; // compute threads + the loader warp
+    constexpr uint32_t TILE_BYTES = 8192; // one ring slot: ROWS x COLS elements
+    constexpr uint32_t MAX_STAGES = 26;
 
+    // ROWS = rows per block = compute threads; the contiguous run of one column that a
+    // TMA box row fetches is ROWS * sizeof(T) bytes, so taller blocks mean longer DRAM
+    // bursts but fewer blocks.
     struct Control
     {
-        uint64_t   full[STAGES];
-        uint64_t   empty[STAGES];
+        uint64_t   full[MAX_STAGES];
+        uint64_t   empty[MAX_STAGES];
         AbortState abort;
     };
-    constexpr uint32_t SMEM_BYTES = STAGES * TILE_BYTES + 128 /*alignment slack*/ + sizeof(Control);
+    constexpr uint32_t smemBytes(uint32_t stages)
+    {
+        return stages * TILE_BYTES + 128 /*alignment slack*/ + uint32_t(sizeof(Control));
+    }
 
     __device__ inline float  mulRn(float a, float b) { return __fmul_rn(a, b); }
     __device__ inline double mulRn(double a, double b) { return __dmul_rn(a, b); }
     __device__ inline float  addRn(float a, float b) { return __fadd_rn(a, b); }
     __device__ inline double addRn(double a, double b) { return __dadd_rn(a, b); }
 
-    template <typename T>
-    __global__ void __launch_bounds__(THREADS, 2)
+    template <typename T, uint32_t ROWS, uint32_t STAGES>
+    __global__ void __launch_bounds__(ROWS + 32)
         gemvTmaKernel(const __grid_constant__ CUtensorMap tmapA, uint32_t m, uint32_t k,
                       T const* __restrict__ x, T const* yIn, T* yOut, T alpha, T beta,
                       uint32_t* status)
@@ -184,22 +189,17 @@ namespace
         return fn;
     }
 
-    template <typename T>
-    int run(uint32_t m, uint32_t k, T const* a, T const* x, T const* yIn, T* yOut, T alpha, T beta,
-            uint32_t lda, cudaStream_t stream)
+    template <typename T, uint32_t ROWS, uint32_t STAGES>
+    int runTma(uint32_t m, uint32_t k, T const* a, T const* x, T const* yIn, T* yOut, T alpha,
+               T beta, uint32_t lda, cudaStream_t stream)
     {
-        const bool tmaOK = (reinterpret_cast<uintptr_t>(a) % 16 == 0)
-                           && ((size_t(lda) * sizeof(T)) % 16 == 0) && m >= ROWS;
-        if(!tmaOK)
-        {
-            gemvPlainKernel<T><<<(m + 127) / 128, 128, 0, stream>>>(m, k, a, x, yIn, yOut, alpha,
-                                                                  beta, lda);
-            return b200wmma::cudaToStatus(cudaGetLastError());
-        }
+        static_assert(STAGES <= MAX_STAGES, "ring deeper than the control block");
         EncodeFn fn = encoder();
         if(!fn)
             return B200WMMA_ERR_CUDA;
-        constexpr uint32_t COLS = TILE_BYTES / (ROWS * sizeof(T));
+        constexpr uint32_t COLS       = TILE_BYTES / (ROWS * sizeof(T));
+        constexpr uint32_t SMEM_BYTES = smemBytes(STAGES);
+        constexpr uint32_t THREADS    = ROWS + 32;
         CUtensorMap        map;
         cuuint64_t         dims[2]    = {m, k};
         cuuint64_t         strides[1] = {cuuint64_t(lda) * sizeof(T)};
@@ -218,15 +218,43 @@ namespace
         B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
         if(dev < 0 || dev >= 64 || !attrDone[dev])
         {
-            B200WMMA_CUDA_TRY(cudaFuncSetAttribute(gemvTmaKernel<T>,
+            B200WMMA_CUDA_TRY(cudaFuncSetAttribute(gemvTmaKernel<T, ROWS, STAGES>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    int(SMEM_BYTES)));
             if(dev >= 0 && dev < 64)
                 attrDone[dev] = true;
         }
-        gemvTmaKernel<T><<<(m + ROWS - 1) / ROWS, THREADS, SMEM_BYTES, stream>>>(
+        gemvTmaKernel<T, ROWS, STAGES><<<(m + ROWS - 1) / ROWS, THREADS, SMEM_BYTES, stream>>>(
             map, m, k, x, yIn, yOut, alpha, beta, b200wmma::deviceStatusWord());
         return b200wmma::cudaToStatus(cudaGetLastError());
+    }
+
+    template <typename T>
+    int run(uint32_t m, uint32_t k, T const* a, T const* x, T const* yIn, T* yOut, T alpha, T beta,
+            uint32_t lda, cudaStream_t stream)
+    {
+        const bool tmaOK = (reinterpret_cast<uintptr_t>(a) % 16 == 0)
+                           && ((size_t(lda) * sizeof(T)) % 16 == 0) && m >= 64;
+        if(!tmaOK)
+        {
+            gemvPlainKernel<T><<<(m + 127) / 128, 128, 0, stream>>>(m, k, a, x, yIn, yOut, alpha,
+                                                                  beta, lda);
+            return b200wmma::cudaToStatus(cudaGetLastError());
+        }
+        // Rows per block: B200WMMA_GEMV_ROWS overrides (tuning only).
+        static const int forced = [] {
+            const char* e = getenv("B200WMMA_GEMV_ROWS");
+            return e ? atoi(e) : 0;
+        }();
+        const int sms  = b200wmma::smCount();
+        uint32_t  rows = forced ? uint32_t(forced) : 128u;
+        if(!forced && m / 128u < uint32_t(sms > 0 ? sms : 1) / 2u)
+            rows = 64u; // small problems: more, shorter blocks
+        if(rows >= 256u && m >= 256u)
+            return runTma<T, 256, 24>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
+        if(rows >= 128u && m >= 128u)
+            return runTma<T, 128, 12>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
+        return runTma<T, 64, 10>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
     }
 } // namespace
 

@@ -19,6 +19,7 @@ namespace b200wmma
             size_t    scratchBytes = 0;
             void*     stage[4]      = {nullptr, nullptr, nullptr, nullptr}; // A, B, C, D staging
             size_t    stageBytes[4] = {0, 0, 0, 0};
+            HostPipe  pipe;
         };
 
         std::mutex  g_mutex;
@@ -115,6 +116,34 @@ namespace b200wmma
         }
         return st->stage[slot];
     }
+
+    HostPipe* hostPipe()
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceState*                st = current();
+        if(!st)
+            return nullptr;
+        HostPipe& p = st->pipe;
+        if(!p.ok)
+        {
+            bool good = cudaStreamCreateWithFlags(&p.h2d, cudaStreamNonBlocking) == cudaSuccess
+                        && cudaStreamCreateWithFlags(&p.d2h, cudaStreamNonBlocking) == cudaSuccess
+                        && cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming) == cudaSuccess
+                        && cudaEventCreateWithFlags(&p.bReady, cudaEventDisableTiming)
+                               == cudaSuccess;
+            for(int i = 0; good && i < HOST_PIPE_MAX_CHUNKS; ++i)
+                good = cudaEventCreateWithFlags(&p.in[i], cudaEventDisableTiming) == cudaSuccess
+                       && cudaEventCreateWithFlags(&p.out[i], cudaEventDisableTiming)
+                              == cudaSuccess;
+            if(!good)
+            {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+            p.ok = true;
+        }
+        return &p;
+    }
 } // namespace b200wmma
 
 using namespace b200wmma;
@@ -175,7 +204,7 @@ int b200wmma_shutdown(void)
     {
         DeviceState& st = g_dev[d];
         bool any = st.status || st.scratch || st.stage[0] || st.stage[1] || st.stage[2]
-                   || st.stage[3];
+                   || st.stage[3] || st.pipe.ok;
         if(!any)
             continue;
         if(cudaSetDevice(d) != cudaSuccess)
@@ -190,6 +219,18 @@ int b200wmma_shutdown(void)
         for(void*& p : st.stage)
             if(p)
                 (void)cudaFree(p);
+        if(st.pipe.ok)
+        {
+            (void)cudaStreamDestroy(st.pipe.h2d);
+            (void)cudaStreamDestroy(st.pipe.d2h);
+            (void)cudaEventDestroy(st.pipe.start);
+            (void)cudaEventDestroy(st.pipe.bReady);
+            for(int i = 0; i < HOST_PIPE_MAX_CHUNKS; ++i)
+            {
+                (void)cudaEventDestroy(st.pipe.in[i]);
+                (void)cudaEventDestroy(st.pipe.out[i]);
+            }
+        }
         st = DeviceState{};
     }
     if(prev >= 0)

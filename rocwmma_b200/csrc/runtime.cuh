@@ -2,6 +2,7 @@
 #ifndef ROCWMMA_B200_CSRC_RUNTIME_CUH
 #define ROCWMMA_B200_CSRC_RUNTIME_CUH
 #include <cstddef>
+#include <cuda_runtime.h>
 
 namespace b200wmma
 {
@@ -10,5 +11,18 @@ namespace b200wmma
     void* deviceScratch(size_t bytes);
     // Staging buffers for the host-buffer GEMM entry point; slot 0..3 = A, B, C, D.
     void* stagingBuffer(int slot, size_t bytes);
+
+    // Copy streams and events for the host-buffer GEMM entry point (created on first use,
+    // one set per device, destroyed by b200wmma_shutdown).
+    constexpr int HOST_PIPE_MAX_CHUNKS = 16;
+    struct HostPipe
+    {
+        cudaStream_t h2d = nullptr, d2h = nullptr;
+        cudaEvent_t  start = nullptr, bReady = nullptr;
+        cudaEvent_t  in[HOST_PIPE_MAX_CHUNKS]  = {};
+        cudaEvent_t  out[HOST_PIPE_MAX_CHUNKS] = {};
+        bool         ok = false;
+    };
+    HostPipe* hostPipe();
 } // namespace b200wmma
 #endif

@@ -75,7 +75,7 @@ def test_block_gemm_full_tiles(in_t, out_t):
 
 @pytest.mark.parametrize("in_t,out_t", BLOCK_PAIRS)
 @pytest.mark.parametrize("m,n,k", [(200, 136, 272), (1, 8, 16), (129, 257, 48), (384, 1000, 528),
-                                   (130, 3, 7)])
+                                   (130, 3, 7), (260, 264, 1040)])
 def test_block_gemm_ragged_edges(in_t, out_t, m, n, k):
     """Sizes that are not tile multiples: loads are zero-filled, stores masked."""
     al, be = _ab(in_t)
@@ -250,3 +250,21 @@ def test_config_fp8_8192_bf16_output():
                   bt.reshape(-1), c0, alpha, 0.0)
     err = O.max_rel_err(O.BF16, np.ascontiguousarray(got[pick]).reshape(-1), want)
     assert 0 <= err <= 1e-2, err
+
+
+@pytest.mark.parametrize("m,beta", [(2304, 0.5), (300, 0.0), (1024, -1.0)])
+def test_host_buffer_entry_point(m, beta):
+    """b200wmma_gemm_host: pinned host buffers in, host buffer out (slab-pipelined copies for
+    m >= 1024, one-shot below)."""
+    n, k = 512, 384
+    case = dict(in_t=O.F16, out_t=O.F16, m=m, n=n, k=k, la=ROW, lb=COL, alpha=1.5, beta=beta,
+                seed=80)
+    a, b, c = gemm_inputs(case)
+    want = O.gemm(O.F16, O.F16, m, n, k, a, b, c, 1.5, beta)
+    ta, tb, tc = (torch.from_numpy(v).pin_memory() for v in (a, b, c))
+    td = torch.full((m * n,), float("nan"), dtype=torch.float16).pin_memory()
+    for _ in range(2):   # the second call reuses the cached staging buffers and streams
+        td.fill_(float("nan"))
+        api.gemm_host(O.F16, O.F16, m, n, k, ta, tb, tc if beta != 0 else None, td, 1.5, beta)
+        assert 0 <= O.max_rel_err(O.F16, td.numpy(), want) <= 2e-3
+    api.check_device()
