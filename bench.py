@@ -216,7 +216,7 @@ def main():
     import torch
     import torch.distributed as dist
 
-    from rocwmma_b200 import api, synth
+    from rocwmma_b200 import api, shard, synth
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
@@ -228,8 +228,7 @@ def main():
 
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
-    m_local = M // world
-    row0 = rank * m_local
+    row0, m_local = shard.gemm_shard(M, world, rank)
 
     # ---- synthetic inputs (seeded; every rank regenerates its own rows of A, all of B) ----
     a_host = torch.from_numpy(synth.rows(SEED, 1, synth.F16, row0, m_local, K)).pin_memory()
@@ -280,10 +279,8 @@ def main():
     barrier()
     e2e_ms_total = f0.elapsed_time(f1)
 
-    if world > 1:
-        t = torch.tensor([ms_total, e2e_ms_total], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, e2e_ms_total = t.tolist()
+    ms_total = shard.max_over_ranks(ms_total, device="cuda")
+    e2e_ms_total = shard.max_over_ranks(e2e_ms_total, device="cuda")
 
     flops = 2.0 * M * N * K
     ms_per_step = ms_total / steps

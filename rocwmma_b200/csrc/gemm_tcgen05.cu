@@ -70,6 +70,7 @@ namespace
         double      alpha, beta;
         uint32_t*   status;
         uint32_t    chunkKB; // k-blocks per accumulation chain; 0 = all of K in one chain
+        uint32_t    wide; // 1: rows of C and D are 32-byte aligned (256-bit accesses)
     };
 
     template <typename T>
@@ -152,13 +153,44 @@ namespace
         EPI_LAST   = 3  // D = alpha * (D + acc) + beta * C
     };
 
-    // Stores (and optionally reads C for) 32 consecutive columns of one output row.
-    template <typename OutT, typename CompT>
-    __device__ inline void epilogueRow(uint32_t const (&raw)[32], GemmParams const& p, CompT alpha,
-                                       CompT beta, bool useC, uint32_t row, uint32_t col0,
-                                       uint32_t mode = EPI_WHOLE)
+    // 16- and 32-byte global accesses.  The 32-byte forms move one whole L2 sector per
+    // thread and instruction, which spares L2 the merging of two half-sector writes.
+    template <uint32_t BYTES>
+    __device__ inline void ldVec(void* dst, void const* src)
     {
-        constexpr uint32_t VEC = 16 / sizeof(OutT); // elements per 128-bit access
+        uint32_t* d = static_cast<uint32_t*>(dst);
+        if constexpr(BYTES == 32)
+            asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]),
+                           "=r"(d[6]), "=r"(d[7])
+                         : "l"(src));
+        else
+            asm volatile("ld.global.v4.b32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                         : "l"(src));
+    }
+    template <uint32_t BYTES>
+    __device__ inline void stVec(void* dst, void const* src)
+    {
+        uint32_t const* v = static_cast<uint32_t const*>(src);
+        if constexpr(BYTES == 32)
+            asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(v[0]),
+                         "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+                         "r"(v[7])
+                         : "memory");
+        else
+            asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(v[0]), "r"(v[1]),
+                         "r"(v[2]), "r"(v[3])
+                         : "memory");
+    }
+
+    // Stores (and optionally reads C for) 32 consecutive columns of one output row.
+    template <typename OutT, typename CompT, uint32_t VBYTES>
+    __device__ inline void epilogueRowV(uint32_t const (&raw)[32], GemmParams const& p,
+                                        CompT alpha, CompT beta, bool useC, uint32_t row,
+                                        uint32_t col0, uint32_t mode, float const* dPre)
+    {
+        constexpr uint32_t VEC = VBYTES / sizeof(OutT); // elements per access
         constexpr bool     CAN_CHUNK
             = std::is_same<OutT, float>::value && std::is_same<CompT, float>::value;
         OutT const*        cRow = static_cast<OutT const*>(p.c) + size_t(row) * p.ldc;
@@ -171,25 +203,34 @@ namespace
             const uint32_t col = col0 + v * VEC;
             if(col >= p.n)
                 break;
-            alignas(16) OutT out[VEC];
-            alignas(16) OutT cin[VEC];
-            alignas(16) OutT din[VEC];
+            alignas(32) OutT out[VEC];
+            alignas(32) OutT cin[VEC];
+            alignas(32) OutT din[VEC];
             const bool       whole = (col + VEC <= p.n);
             if(readC)
             {
                 if(whole)
-                    *reinterpret_cast<uint4*>(cin) = *reinterpret_cast<uint4 const*>(cRow + col);
+                    ldVec<VBYTES>(cin, cRow + col);
                 else
                     for(uint32_t e = 0; e < VEC; ++e)
                         cin[e] = (col + e < p.n) ? cRow[col + e] : OutT(0);
             }
             if(readD)
             {
-                if(whole)
-                    *reinterpret_cast<uint4*>(din) = *reinterpret_cast<uint4 const*>(dRow + col);
-                else
-                    for(uint32_t e = 0; e < VEC; ++e)
-                        din[e] = (col + e < p.n) ? dRow[col + e] : OutT(0);
+                if constexpr(CAN_CHUNK)
+                {
+                    if(dPre != nullptr) // running sum already fetched by the caller
+                    {
+#pragma unroll
+                        for(uint32_t e = 0; e < VEC; ++e)
+                            din[e] = dPre[v * VEC + e];
+                    }
+                    else if(whole)
+                        ldVec<VBYTES>(din, dRow + col);
+                    else
+                        for(uint32_t e = 0; e < VEC; ++e)
+                            din[e] = (col + e < p.n) ? dRow[col + e] : OutT(0);
+                }
             }
 #pragma unroll
             for(uint32_t e = 0; e < VEC; ++e)
@@ -216,12 +257,115 @@ namespace
                 out[e] = fromCompute<OutT, CompT>(r);
             }
             if(whole)
-                *reinterpret_cast<uint4*>(dRow + col) = *reinterpret_cast<uint4 const*>(out);
+                stVec<VBYTES>(dRow + col, out);
             else
                 for(uint32_t e = 0; e < VEC; ++e)
                     if(col + e < p.n)
                         dRow[col + e] = out[e];
         }
+    }
+
+    template <typename OutT, typename CompT>
+    __device__ inline void epilogueRow(uint32_t const (&raw)[32], GemmParams const& p, CompT alpha,
+                                       CompT beta, bool useC, uint32_t row, uint32_t col0,
+                                       uint32_t mode = EPI_WHOLE, float const* dPre = nullptr)
+    {
+        if(p.wide) // C and D rows are 32-byte aligned: whole-sector accesses
+            epilogueRowV<OutT, CompT, 32>(raw, p, alpha, beta, useC, row, col0, mode, dPre);
+        else
+            epilogueRowV<OutT, CompT, 16>(raw, p, alpha, beta, useC, row, col0, mode, dPre);
+    }
+
+    // 32 consecutive fp32 values of row `rowPtr` starting at column col0 (zeros outside n).
+    __device__ inline void loadRunningSum(float (&dst)[32], float const* rowPtr, uint32_t col0,
+                                          uint32_t n, bool rowValid, bool wide)
+    {
+        if(wide && rowValid && col0 + 32u <= n)
+        {
+#pragma unroll
+            for(uint32_t v = 0; v < 4; ++v)
+                ldVec<32>(&dst[v * 8u], rowPtr + col0 + v * 8u);
+            return;
+        }
+#pragma unroll
+        for(uint32_t v = 0; v < 8; ++v)
+        {
+            const uint32_t col = col0 + v * 4u;
+            if(rowValid && col + 4u <= n)
+                ldVec<16>(&dst[v * 4u], rowPtr + col);
+            else
+            {
+#pragma unroll
+                for(uint32_t e = 0; e < 4; ++e)
+                    dst[v * 4u + e] = (rowValid && col + e < n) ? rowPtr[col + e] : 0.0f;
+            }
+        }
+    }
+
+    // Waits for one accumulator buffer and writes its 128 x 256 values out (one row per
+    // thread).  In the chunked modes that add to the running sum kept in D, the sum for the
+    // next two 32-column groups is fetched ahead of use -- the first two even before the
+    // accumulator is ready -- so that the L2 round trips overlap instead of adding up.
+    template <typename OutT, typename CompT>
+    __device__ inline bool drainAccumulator(uint64_t* accFullBar, uint32_t accPh,
+                                            AbortState* abort, uint32_t taddrRowBase,
+                                            GemmParams const& p, CompT alpha, CompT beta,
+                                            bool useC, uint32_t row, uint32_t colBase,
+                                            uint32_t mode)
+    {
+        constexpr bool CAN_CHUNK
+            = std::is_same<OutT, float>::value && std::is_same<CompT, float>::value;
+        if constexpr(CAN_CHUNK)
+        {
+            if(mode == EPI_MIDDLE || mode == EPI_LAST)
+            {
+                constexpr uint32_t AHEAD = 2;
+                float              dq[AHEAD + 1][32];
+                float const*       dRow
+                    = static_cast<float const*>(p.d) + size_t(row < p.m ? row : 0u) * p.ldd;
+                const bool rowValid = row < p.m;
+#pragma unroll
+                for(uint32_t c = 0; c < AHEAD; ++c)
+                    loadRunningSum(dq[c], dRow, colBase + c * 32u, p.n, rowValid, p.wide != 0u);
+                if(!mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL))
+                    return false;
+                tc_fence_after_sync();
+#pragma unroll
+                for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+                {
+                    if(chunk + AHEAD < BN / 32)
+                        loadRunningSum(dq[(chunk + AHEAD) % (AHEAD + 1)], dRow,
+                                       colBase + (chunk + AHEAD) * 32u, p.n, rowValid,
+                                       p.wide != 0u);
+                    uint32_t raw[32];
+                    __syncwarp();
+                    tmem_load_32x32b_x32(taddrRowBase + chunk * 32u, raw);
+                    tmem_load_wait();
+                    const uint32_t col0 = colBase + chunk * 32u;
+                    if(rowValid && col0 < p.n)
+                        epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0, mode,
+                                                 dq[chunk % (AHEAD + 1)]);
+                }
+                tc_fence_before_sync();
+                return true;
+            }
+        }
+        if(!mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL))
+            return false;
+        tc_fence_after_sync();
+#pragma unroll 1
+        for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+        {
+            uint32_t raw[32];
+            __syncwarp(); // rows masked off below rejoin before the warp-wide load
+            tmem_load_32x32b_x32(taddrRowBase + chunk * 32u, raw); // warp-wide
+            tmem_load_wait();
+            const uint32_t col0 = colBase + chunk * 32u;
+            if(row < p.m && col0 < p.n)
+                epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0, mode);
+        }
+        tc_fence_before_sync();
+        return true;
     }
 
     template <typename InT, typename OutT, typename CompT>
@@ -393,30 +537,18 @@ namespace
                 {
                     const uint32_t buf   = accIter & 1u;
                     const uint32_t accPh = (accIter >> 1) & 1u;
-                    if(!mbar_wait(&ctl->accFull[buf], accPh, &ctl->abort, WAIT_ACC_FULL))
-                    {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
                     const uint32_t mode = numChunks == 1u       ? EPI_WHOLE
                                           : ch == 0u            ? EPI_FIRST
                                           : ch + 1u < numChunks ? EPI_MIDDLE
                                                                 : EPI_LAST;
-#pragma unroll 1
-                    for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+                    if(!drainAccumulator<OutT, CompT>(
+                           &ctl->accFull[buf], accPh, &ctl->abort,
+                           tmemBase + ((quad * 32u) << 16) + buf * BN, p, alpha, beta, useC, row,
+                           tn * BN, mode))
                     {
-                        uint32_t raw[32];
-                        __syncwarp(); // rows masked off below rejoin before the warp-wide load
-                        const uint32_t taddr
-                            = tmemBase + ((quad * 32u) << 16) + buf * BN + chunk * 32u;
-                        tmem_load_32x32b_x32(taddr, raw); // warp-wide: no divergence before it
-                        tmem_load_wait();
-                        const uint32_t col0 = tn * BN + chunk * 32;
-                        if(row < p.m && col0 < p.n)
-                            epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0, mode);
+                        ok = false;
+                        break;
                     }
-                    tc_fence_before_sync();
                     mbar_arrive(&ctl->accEmpty[buf]);
                 }
             }
@@ -628,30 +760,18 @@ namespace
                 {
                     const uint32_t buf   = accIter & 1u;
                     const uint32_t accPh = (accIter >> 1) & 1u;
-                    if(!mbar_wait(&ctl->accFull[buf], accPh, &ctl->abort, WAIT_ACC_FULL))
-                    {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
                     const uint32_t mode = numChunks == 1u       ? EPI_WHOLE
                                           : ch == 0u            ? EPI_FIRST
                                           : ch + 1u < numChunks ? EPI_MIDDLE
                                                                 : EPI_LAST;
-#pragma unroll 1
-                    for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+                    if(!drainAccumulator<OutT, CompT>(
+                           &ctl->accFull[buf], accPh, &ctl->abort,
+                           tmemBase + ((quad * 32u) << 16) + buf * BN, p, alpha, beta, useC, row,
+                           tn * BN, mode))
                     {
-                        uint32_t raw[32];
-                        __syncwarp();
-                        const uint32_t taddr
-                            = tmemBase + ((quad * 32u) << 16) + buf * BN + chunk * 32u;
-                        tmem_load_32x32b_x32(taddr, raw);
-                        tmem_load_wait();
-                        const uint32_t col0 = tn * BN + chunk * 32;
-                        if(row < p.m && col0 < p.n)
-                            epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0, mode);
+                        ok = false;
+                        break;
                     }
-                    tc_fence_before_sync();
                     mbar_arrive_cluster(map_to_cta(smem_addr(&ctl->accEmpty[buf]), 0));
                 }
             }
@@ -767,7 +887,15 @@ namespace
             if((k + ROW_BYTES / sizeof(InT) - 1) / (ROW_BYTES / sizeof(InT)) > kbPerChunk)
                 chunkKB = kbPerChunk;
         }
-        GemmParams  p{m, n, k, c, d, ldc, ldd, alpha, beta, status, chunkKB};
+        auto aligned32 = [](void const* ptr, uint32_t ld, size_t elem) {
+            return (reinterpret_cast<uintptr_t>(ptr) % 32) == 0 && (size_t(ld) * elem) % 32 == 0;
+        };
+        const uint32_t wide = aligned32(d, ldd, sizeof(OutT))
+                                      && (beta == 0.0 || c == nullptr
+                                          || aligned32(c, ldc, sizeof(OutT)))
+                                  ? 1u
+                                  : 0u;
+        GemmParams  p{m, n, k, c, d, ldc, ldd, alpha, beta, status, chunkKB, wide};
         CUtensorMap mapA, mapB;
 
         if(pairEnabled() && m > BM && sms >= 2)

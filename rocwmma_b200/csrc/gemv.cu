@@ -11,111 +11,139 @@
 // whatever the size (a K-split or tree reduction would differ from it by the
 // rounding noise of a 16384-term fp32 sum, which alone exceeds 1e-4 relative).
 //
-//   * a block owns ROWS consecutive rows; one warp-elected thread streams
-//     ROWS x COLS tiles of A through a ring of shared-memory slots with TMA
-//     (cp.async.bulk.tensor, no multicast), full/empty mbarriers per slot;
-//   * ROWS compute threads, one per row, read their row's element of each column
-//     from the slot (consecutive threads, consecutive addresses) and x[h] by a
-//     warp-uniform cached load;
-//   * 2 blocks per SM, ~80 KiB of TMA loads in flight per block.
+//   * a block owns 64 consecutive rows; four loader warps stream 64-row x 32-column
+//     tiles of A through a 10-slot shared-memory ring with 16-byte cp.async copies,
+//     full/empty mbarriers per slot; the 32 values of x that belong to a tile travel in
+//     the same slot, so that no compute thread ever waits on a global load (with x read
+//     straight from global memory the kernel was bound by that latency, 3.8 TB/s);
+//   * 64 compute threads, one per row, read their row's element of each column from
+//     the slot (consecutive threads, consecutive addresses) and x[h] by warp-uniform
+//     vector loads;
+//   * 2 blocks per SM, 80 KiB of loads in flight per block.
 //
-// When pointer or leading dimension do not meet TMA's 16-byte rules a plain-load
-// kernel with the same summation order is used.
+// When pointer or leading dimension are not 16-byte multiples a plain-load kernel with
+// the same summation order is used.
 #include "common.cuh"
 #include "runtime.cuh"
-#include <cstdlib>
-#include <cuda.h>
-#include <mutex>
 #include <rocwmma/rocwmma_block.hpp>
 
 using namespace rocwmma::block;
 
 namespace
 {
-    constexpr uint32_t TILE_BYTES = 8192; // one ring slot: ROWS x COLS elements
-    constexpr uint32_t MAX_STAGES = 26;
+    constexpr uint32_t ROWS       = 64; // rows per block, one compute thread per row
+    constexpr uint32_t TILE_BYTES = 8192; // COLS columns x ROWS rows of A
+    constexpr uint32_t XSEG_BYTES = 128; // the COLS values of x that go with them
+    constexpr uint32_t SLOT_BYTES = TILE_BYTES + XSEG_BYTES; // one ring slot
+    constexpr uint32_t STAGES     = 10;
+    constexpr uint32_t CWARPS     = ROWS / 32; // compute warps
+    constexpr uint32_t LWARPS     = 4; // loader warps
+    constexpr uint32_t LTHREADS   = LWARPS * 32;
+    constexpr uint32_t THREADS    = ROWS + LTHREADS;
 
-    // ROWS = rows per block = compute threads; the contiguous run of one column that a
-    // TMA box row fetches is ROWS * sizeof(T) bytes, so taller blocks mean longer DRAM
-    // bursts but fewer blocks.
     struct Control
     {
-        uint64_t   full[MAX_STAGES];
-        uint64_t   empty[MAX_STAGES];
+        uint64_t   full[STAGES];
+        uint64_t   empty[STAGES];
         AbortState abort;
     };
-    constexpr uint32_t smemBytes(uint32_t stages)
-    {
-        return stages * TILE_BYTES + 128 /*alignment slack*/ + uint32_t(sizeof(Control));
-    }
+    constexpr uint32_t SMEM_BYTES = STAGES * SLOT_BYTES + 128 /*alignment slack*/ + sizeof(Control);
 
     __device__ inline float  mulRn(float a, float b) { return __fmul_rn(a, b); }
     __device__ inline double mulRn(double a, double b) { return __dmul_rn(a, b); }
     __device__ inline float  addRn(float a, float b) { return __fadd_rn(a, b); }
     __device__ inline double addRn(double a, double b) { return __dadd_rn(a, b); }
 
-    template <typename T, uint32_t ROWS, uint32_t STAGES>
-    __global__ void __launch_bounds__(ROWS + 32)
-        gemvTmaKernel(const __grid_constant__ CUtensorMap tmapA, uint32_t m, uint32_t k,
-                      T const* __restrict__ x, T const* yIn, T* yOut, T alpha, T beta,
-                      uint32_t* status)
+    // 16-byte asynchronous copy global -> shared; bytes beyond srcBytes are zero-filled.
+    __device__ inline void cpAsync16(uint32_t dst, void const* src, uint32_t srcBytes)
     {
-        constexpr uint32_t COLS = TILE_BYTES / (ROWS * sizeof(T)); // 32 (fp32) / 16 (fp64)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+                     "r"(srcBytes)
+                     : "memory");
+    }
+    // One arrival on `bar` once all cp.async issued so far by this thread have landed.
+    __device__ inline void cpAsyncArriveOn(uint64_t* bar)
+    {
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(bar))
+                     : "memory");
+    }
+
+    template <typename T, uint32_t N>
+    struct alignas(sizeof(T) * N) Vec
+    {
+        T v[N];
+    };
+
+    template <typename T>
+    __global__ void __launch_bounds__(THREADS, 2)
+        gemvStreamKernel(uint32_t m, uint32_t k, T const* __restrict__ a, T const* __restrict__ x,
+                         T const* yIn, T* yOut, T alpha, T beta, uint32_t lda, uint32_t* status)
+    {
+        constexpr uint32_t COLS   = TILE_BYTES / (ROWS * sizeof(T)); // 32 (fp32) / 16 (fp64)
+        constexpr uint32_t CPC    = ROWS * sizeof(T) / 16; // 16-byte chunks per column
+        constexpr uint32_t CHUNKS = COLS * CPC; // per ring slot (512)
+        constexpr uint32_t XV     = 16 / sizeof(T);
         extern __shared__ uint8_t smemRaw[];
         const uint32_t            raw   = smem_addr(smemRaw);
         uint8_t*                  tiles = smemRaw + ((128u - (raw & 127u)) & 127u);
-        Control* ctl = reinterpret_cast<Control*>(tiles + STAGES * TILE_BYTES);
+        Control* ctl = reinterpret_cast<Control*>(tiles + STAGES * SLOT_BYTES);
 
-        const uint32_t row0   = blockIdx.x * ROWS;
-        const uint32_t numKB  = (k + COLS - 1) / COLS;
+        static_assert(COLS * sizeof(T) == XSEG_BYTES, "x segment size");
+        const uint32_t row0  = blockIdx.x * ROWS;
+        const uint32_t numKB = (k + COLS - 1) / COLS;
+        // x travels through the ring with its columns of A when it can be copied in 16-byte
+        // pieces; otherwise the compute threads read it from global memory themselves
+        const bool xStaged = (reinterpret_cast<uintptr_t>(x) % 16) == 0;
 
         if(threadIdx.x == 0)
         {
             for(uint32_t s = 0; s < STAGES; ++s)
             {
-                mbar_init(&ctl->full[s], 1);
-                mbar_init(&ctl->empty[s], ROWS);
+                mbar_init(&ctl->full[s], LTHREADS);
+                mbar_init(&ctl->empty[s], CWARPS);
             }
             ctl->abort.flag = 0;
             ctl->abort.code = 0;
             mbar_init_fence();
-            tma_prefetch_descriptor(&tmapA);
         }
         __syncthreads();
 
         if(threadIdx.x >= ROWS)
         {
-            // ---- loader warp ----
-            if(elect_one())
+            // ---- loader warps ----
+            const uint32_t t         = threadIdx.x - ROWS;
+            const uint32_t tilesAddr = smem_addr(tiles);
+            const uint32_t rowsValid = (m - row0) < ROWS ? (m - row0) : ROWS;
+            for(uint32_t kb = 0; kb < numKB; ++kb)
             {
-                uint32_t kb = 0;
-                bool     ok = true;
-                for(; kb < numKB; ++kb)
+                const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
+                if(!mbar_wait(&ctl->empty[s], ph ^ 1u, &ctl->abort, WAIT_STAGE_EMPTY))
+                    break;
+                const uint32_t h0 = kb * COLS;
+#pragma unroll
+                for(uint32_t i = 0; i < CHUNKS / LTHREADS; ++i)
                 {
-                    const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
-                    if(!mbar_wait(&ctl->empty[s], ph ^ 1u, &ctl->abort, WAIT_STAGE_EMPTY))
-                    {
-                        ok = false;
-                        break;
-                    }
-                    mbar_expect_tx(&ctl->full[s], TILE_BYTES);
-                    tma_load_2d(tiles + s * TILE_BYTES, &tmapA, &ctl->full[s], int32_t(row0),
-                                int32_t(kb * COLS));
+                    const uint32_t c    = t + i * LTHREADS;
+                    const uint32_t col  = c / CPC, part = c % CPC;
+                    const uint32_t r    = part * XV; // first row of the chunk inside the block
+                    uint32_t       bytes = 0;
+                    if(h0 + col < k && r < rowsValid)
+                        bytes = (rowsValid - r >= XV) ? 16u : uint32_t((rowsValid - r) * sizeof(T));
+                    T const* src = bytes ? a + size_t(h0 + col) * lda + row0 + r : a;
+                    cpAsync16(tilesAddr + s * SLOT_BYTES + c * 16u, src, bytes);
                 }
-                if(!ok)
+                if(xStaged && t < XSEG_BYTES / 16u)
                 {
-                    const uint32_t pending = kb < STAGES ? kb : STAGES;
-                    for(uint32_t j = 0; j < pending; ++j)
-                    {
-                        const uint32_t  prev = kb - 1 - j;
-                        const long long t0   = clock64();
-                        while(!mbar_try_wait(&ctl->full[prev % STAGES], (prev / STAGES) & 1u)
-                              && clock64() - t0 < 2000000ll)
-                        {
-                        }
-                    }
+                    const uint32_t j     = t * XV; // first column of this piece
+                    uint32_t       bytes = 0;
+                    if(h0 + j < k)
+                        bytes = (k - h0 - j >= XV) ? 16u : uint32_t((k - h0 - j) * sizeof(T));
+                    cpAsync16(tilesAddr + s * SLOT_BYTES + TILE_BYTES + t * 16u,
+                              bytes ? x + h0 + j : x, bytes);
                 }
+                cpAsyncArriveOn(&ctl->full[s]);
             }
+            asm volatile("cp.async.wait_all;" ::: "memory"); // nothing in flight when leaving
         }
         else
         {
@@ -125,22 +153,45 @@ namespace
             for(uint32_t kb = 0; kb < numKB; ++kb)
             {
                 const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
-                if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
-                    break;
-                T const*       tile = reinterpret_cast<T const*>(tiles + s * TILE_BYTES);
-                const uint32_t h0   = kb * COLS;
-                if(h0 + COLS <= k)
+                const uint32_t h0 = kb * COLS;
+                T xv[COLS];
+                if(!xStaged)
                 {
 #pragma unroll
                     for(uint32_t j = 0; j < COLS; ++j)
-                        acc = addRn(acc, mulRn(tile[j * ROWS + r], __ldg(x + h0 + j)));
+                        xv[j] = (h0 + j < k) ? __ldg(x + h0 + j) : T(0);
                 }
-                else
+                if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
+                    break;
+                if(xStaged)
                 {
-                    for(uint32_t j = 0; h0 + j < k; ++j)
-                        acc = addRn(acc, mulRn(tile[j * ROWS + r], __ldg(x + h0 + j)));
+                    Vec<T, XV> const* xs
+                        = reinterpret_cast<Vec<T, XV> const*>(tiles + s * SLOT_BYTES + TILE_BYTES);
+#pragma unroll
+                    for(uint32_t j = 0; j < COLS; j += XV)
+                    {
+                        const Vec<T, XV> q = xs[j / XV]; // same address in every lane: broadcast
+#pragma unroll
+                        for(uint32_t e = 0; e < XV; ++e)
+                            xv[j + e] = q.v[e];
+                    }
                 }
-                mbar_arrive(&ctl->empty[s]);
+                T const* tile = reinterpret_cast<T const*>(tiles + s * SLOT_BYTES);
+                // the row's element of every column first (independent loads) ...
+                T av[COLS];
+#pragma unroll
+                for(uint32_t j = 0; j < COLS; ++j)
+                    av[j] = tile[j * ROWS + r];
+                __syncwarp();
+                if((threadIdx.x & 31u) == 0u)
+                    mbar_arrive(&ctl->empty[s]); // slot is in registers: one arrival per warp
+                // ... then the ordered sum.  Columns beyond k hold zeros and must not enter
+                // it (adding +0 could turn a -0 into +0).
+                const uint32_t valid = (k - h0) < COLS ? (k - h0) : COLS;
+#pragma unroll
+                for(uint32_t j = 0; j < COLS; ++j)
+                    if(j < valid)
+                        acc = addRn(acc, mulRn(av[j], xv[j]));
             }
             if(row0 + r < m && ctl->abort.flag == 0u)
                 yOut[row0 + r] = addRn(mulRn(alpha, acc), mulRn(beta, yIn[row0 + r]));
@@ -168,93 +219,33 @@ namespace
         yOut[i] = addRn(mulRn(alpha, acc), mulRn(beta, yIn[i]));
     }
 
-    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    EncodeFn encoder()
-    {
-        static EncodeFn       fn = nullptr;
-        static std::once_flag once;
-        std::call_once(once, [] {
-            void*                           sym = nullptr;
-            cudaDriverEntryPointQueryResult q;
-            if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q)
-                   == cudaSuccess
-               && q == cudaDriverEntryPointSuccess)
-                fn = reinterpret_cast<EncodeFn>(sym);
-            else
-                (void)cudaGetLastError();
-        });
-        return fn;
-    }
-
-    template <typename T, uint32_t ROWS, uint32_t STAGES>
-    int runTma(uint32_t m, uint32_t k, T const* a, T const* x, T const* yIn, T* yOut, T alpha,
-               T beta, uint32_t lda, cudaStream_t stream)
-    {
-        static_assert(STAGES <= MAX_STAGES, "ring deeper than the control block");
-        EncodeFn fn = encoder();
-        if(!fn)
-            return B200WMMA_ERR_CUDA;
-        constexpr uint32_t COLS       = TILE_BYTES / (ROWS * sizeof(T));
-        constexpr uint32_t SMEM_BYTES = smemBytes(STAGES);
-        constexpr uint32_t THREADS    = ROWS + 32;
-        CUtensorMap        map;
-        cuuint64_t         dims[2]    = {m, k};
-        cuuint64_t         strides[1] = {cuuint64_t(lda) * sizeof(T)};
-        cuuint32_t         box[2]     = {ROWS, COLS};
-        cuuint32_t         estr[2]    = {1, 1};
-        const CUtensorMapDataType dt
-            = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT64;
-        if(fn(&map, dt, 2, const_cast<T*>(a), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
-           != CUDA_SUCCESS)
-            return B200WMMA_ERR_CUDA;
-
-        static bool attrDone[64] = {};
-        int         dev          = 0;
-        B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
-        if(dev < 0 || dev >= 64 || !attrDone[dev])
-        {
-            B200WMMA_CUDA_TRY(cudaFuncSetAttribute(gemvTmaKernel<T, ROWS, STAGES>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   int(SMEM_BYTES)));
-            if(dev >= 0 && dev < 64)
-                attrDone[dev] = true;
-        }
-        gemvTmaKernel<T, ROWS, STAGES><<<(m + ROWS - 1) / ROWS, THREADS, SMEM_BYTES, stream>>>(
-            map, m, k, x, yIn, yOut, alpha, beta, b200wmma::deviceStatusWord());
-        return b200wmma::cudaToStatus(cudaGetLastError());
-    }
-
     template <typename T>
     int run(uint32_t m, uint32_t k, T const* a, T const* x, T const* yIn, T* yOut, T alpha, T beta,
             uint32_t lda, cudaStream_t stream)
     {
-        const bool tmaOK = (reinterpret_cast<uintptr_t>(a) % 16 == 0)
-                           && ((size_t(lda) * sizeof(T)) % 16 == 0) && m >= 64;
-        if(!tmaOK)
+        // 16-byte asynchronous copies need 16-byte aligned columns
+        const bool streamOK = (reinterpret_cast<uintptr_t>(a) % 16 == 0)
+                              && ((size_t(lda) * sizeof(T)) % 16 == 0);
+        if(!streamOK)
         {
             gemvPlainKernel<T><<<(m + 127) / 128, 128, 0, stream>>>(m, k, a, x, yIn, yOut, alpha,
                                                                   beta, lda);
             return b200wmma::cudaToStatus(cudaGetLastError());
         }
-        // Rows per block: B200WMMA_GEMV_ROWS overrides (tuning only).
-        static const int forced = [] {
-            const char* e = getenv("B200WMMA_GEMV_ROWS");
-            return e ? atoi(e) : 0;
-        }();
-        const int sms  = b200wmma::smCount();
-        uint32_t  rows = forced ? uint32_t(forced) : 128u;
-        if(!forced && m / 128u < uint32_t(sms > 0 ? sms : 1) / 2u)
-            rows = 64u; // small problems: more, shorter blocks
-        if(rows >= 256u && m >= 256u)
-            return runTma<T, 256, 24>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
-        if(rows >= 128u && m >= 128u)
-            return runTma<T, 128, 12>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
-        return runTma<T, 64, 10>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
+        static bool attrDone[64] = {};
+        int         dev          = 0;
+        B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
+        if(dev < 0 || dev >= 64 || !attrDone[dev])
+        {
+            B200WMMA_CUDA_TRY(cudaFuncSetAttribute(gemvStreamKernel<T>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   int(SMEM_BYTES)));
+            if(dev >= 0 && dev < 64)
+                attrDone[dev] = true;
+        }
+        gemvStreamKernel<T><<<(m + ROWS - 1) / ROWS, THREADS, SMEM_BYTES, stream>>>(
+            m, k, a, x, yIn, yOut, alpha, beta, lda, b200wmma::deviceStatusWord());
+        return b200wmma::cudaToStatus(cudaGetLastError());
     }
 } // namespace
 
