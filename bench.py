@@ -293,7 +293,7 @@ def main():
     kernel_tflops = 2.0 * m_local * N * K / (ms_per_step * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
                 "frac": kernel_tflops / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                "peak_source": peak_src, "kernel": "gemm_tcgen05_kernel<half,half,float>",
+                "peak_source": peak_src, "kernel": "gemm_tcgen05_pair_kernel<half,half,float>",
                 "algorithmic_flops_per_launch": 2.0 * m_local * N * K}
 
     # ---- CPU baseline (rank 0, N = 1 only) + parity of the same rows ----

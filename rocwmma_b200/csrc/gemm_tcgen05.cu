@@ -71,6 +71,7 @@ namespace
         uint32_t*   status;
         uint32_t    chunkKB; // k-blocks per accumulation chain; 0 = all of K in one chain
         uint32_t    wide; // 1: rows of C and D are 32-byte aligned (256-bit accesses)
+        uint32_t    bn; // tile width (columns of D per tile): 256, or less for the pair kernel
     };
 
     template <typename T>
@@ -315,6 +316,7 @@ namespace
     {
         constexpr bool CAN_CHUNK
             = std::is_same<OutT, float>::value && std::is_same<CompT, float>::value;
+        const uint32_t groups = p.bn / 32u; // 32-column groups in this tile
         if constexpr(CAN_CHUNK)
         {
             if(mode == EPI_MIDDLE || mode == EPI_LAST)
@@ -333,6 +335,8 @@ namespace
 #pragma unroll
                 for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
                 {
+                    if(chunk >= groups)
+                        break;
                     if(chunk + AHEAD < BN / 32)
                         loadRunningSum(dq[(chunk + AHEAD) % (AHEAD + 1)], dRow,
                                        colBase + (chunk + AHEAD) * 32u, p.n, rowValid,
@@ -354,7 +358,7 @@ namespace
             return false;
         tc_fence_after_sync();
 #pragma unroll 1
-        for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+        for(uint32_t chunk = 0; chunk < groups; ++chunk)
         {
             uint32_t raw[32];
             __syncwarp(); // rows masked off below rejoin before the warp-wide load
@@ -609,8 +613,12 @@ namespace
     {
         constexpr uint32_t BK     = ROW_BYTES / sizeof(InT);
         constexpr uint32_t UMMA_K = 32 / sizeof(InT);
-        constexpr uint32_t IDESC  = make_instr_desc(KindOf<InT>::acc, KindOf<InT>::fmt,
-                                                   KindOf<InT>::fmt, P_TILE_M, BN);
+        // The tile width is chosen per launch (a multiple of 32 up to 256) so that the tile
+        // count divides evenly over the pairs; it is the N of the MMA instruction.
+        const uint32_t bn    = p.bn;
+        const uint32_t IDESC = make_instr_desc(KindOf<InT>::acc, KindOf<InT>::fmt,
+                                               KindOf<InT>::fmt, P_TILE_M, bn);
+        const uint32_t bHalfBytes = (bn / 2u) * ROW_BYTES; // this block's rows of the B tile
 
         extern __shared__ uint8_t smemRaw[];
         const uint32_t            rawAddr = smem_addr(smemRaw);
@@ -624,7 +632,7 @@ namespace
         const uint32_t nPairs = gridDim.x / 2;
 
         const uint32_t tilesM   = (p.m + P_TILE_M - 1) / P_TILE_M;
-        const uint32_t tilesN   = (p.n + BN - 1) / BN;
+        const uint32_t tilesN   = (p.n + bn - 1) / bn;
         const uint32_t numTiles = tilesM * tilesN;
         const uint32_t numKB    = (p.k + BK - 1) / BK;
         const uint32_t chunkKB  = p.chunkKB != 0u ? p.chunkKB : numKB; // K blocks per chain
@@ -671,7 +679,7 @@ namespace
                     uint32_t tm, tn;
                     tileCoord(t, tilesM, tilesN, tm, tn);
                     const int32_t rowA = int32_t(tm * P_TILE_M + rank * 128u);
-                    const int32_t rowB = int32_t(tn * BN + rank * 128u);
+                    const int32_t rowB = int32_t(tn * bn + rank * (bn / 2u));
                     for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
                     {
                         const uint32_t s  = it % P_STAGES;
@@ -683,7 +691,7 @@ namespace
                         }
                         uint8_t* slot = tiles + s * P_STAGE_BYTES;
                         if(rank == 0)
-                            mbar_expect_tx(&ctl->full[s], 2u * P_STAGE_BYTES); // both blocks' bytes
+                            mbar_expect_tx(&ctl->full[s], 2u * (P_A_BYTES + bHalfBytes)); // both blocks
                         const uint32_t leaderFull = map_to_cta(smem_addr(&ctl->full[s]), 0);
                         tma_load_2d_pair(slot, &tmapA, leaderFull, int32_t(kb * BK), rowA);
                         tma_load_2d_pair(slot + P_A_BYTES, &tmapB, leaderFull, int32_t(kb * BK),
@@ -767,7 +775,7 @@ namespace
                     if(!drainAccumulator<OutT, CompT>(
                            &ctl->accFull[buf], accPh, &ctl->abort,
                            tmemBase + ((quad * 32u) << 16) + buf * BN, p, alpha, beta, useC, row,
-                           tn * BN, mode))
+                           tn * bn, mode))
                     {
                         ok = false;
                         break;
@@ -895,15 +903,35 @@ namespace
                                           || aligned32(c, ldc, sizeof(OutT)))
                                   ? 1u
                                   : 0u;
-        GemmParams  p{m, n, k, c, d, ldc, ldd, alpha, beta, status, chunkKB, wide};
+        GemmParams  p{m, n, k, c, d, ldc, ldd, alpha, beta, status, chunkKB, wide, BN};
         CUtensorMap mapA, mapB;
 
         if(pairEnabled() && m > BM && sms >= 2)
         {
+            // Tile width: the candidate that needs the least time by a simple model --
+            // waves of tiles over the pairs, each wave costing the tile width (plus a small
+            // fixed part).  8192^2 on one GPU keeps 256; the 2048- and 1024-row shards of a
+            // 4- or 8-GPU run come out at 224, which turns 3.46 resp. 1.73 waves into 4 resp. 2
+            // full ones of narrower tiles.
+            const uint32_t pairsMax = uint32_t(sms / 2);
+            const uint32_t tilesM   = (m + P_TILE_M - 1) / P_TILE_M;
+            uint32_t       bn = BN, bestCost = 0xffffffffu;
+            for(uint32_t cand = 256; cand >= 128; cand -= 32)
+            {
+                const uint32_t tiles = tilesM * ((n + cand - 1) / cand);
+                const uint32_t waves = (tiles + pairsMax - 1) / pairsMax;
+                const uint32_t cost  = waves * (cand + 8u);
+                if(cost < bestCost)
+                {
+                    bestCost = cost;
+                    bn       = cand;
+                }
+            }
+            p.bn   = bn;
             int rc = makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, 128);
             if(rc != B200WMMA_OK)
                 return rc;
-            rc = makeOperandMap(&mapB, dt, sizeof(InT), b, n, k, ldb, 128);
+            rc = makeOperandMap(&mapB, dt, sizeof(InT), b, n, k, ldb, bn / 2);
             if(rc != B200WMMA_OK)
                 return rc;
             auto        kernel = gemm_tcgen05_pair_kernel<InT, OutT, CompT>;
@@ -911,8 +939,8 @@ namespace
             rc = optInSharedMemory(kernel, P_SMEM_BYTES, done);
             if(rc != B200WMMA_OK)
                 return rc;
-            const uint32_t tiles = ((m + P_TILE_M - 1) / P_TILE_M) * ((n + BN - 1) / BN);
-            const uint32_t pairs = tiles < uint32_t(sms / 2) ? tiles : uint32_t(sms / 2);
+            const uint32_t tiles = tilesM * ((n + bn - 1) / bn);
+            const uint32_t pairs = tiles < pairsMax ? tiles : pairsMax;
             kernel<<<2 * pairs, NUM_THREADS, P_SMEM_BYTES, stream>>>(mapA, mapB, p);
             return b200wmma::cudaToStatus(cudaGetLastError());
         }

@@ -268,3 +268,13 @@ def test_host_buffer_entry_point(m, beta):
         api.gemm_host(O.F16, O.F16, m, n, k, ta, tb, tc if beta != 0 else None, td, 1.5, beta)
         assert 0 <= O.max_rel_err(O.F16, td.numpy(), want) <= 2e-3
     api.check_device()
+
+
+@pytest.mark.parametrize("m", [1024, 2048])
+def test_multi_gpu_shard_shapes(m):
+    """The row shards of an 8- and 4-GPU run of the 8192^3 problem (reduced K): the launcher
+    narrows the tile to 224 columns for these so the tiles fill whole waves."""
+    case = dict(in_t=O.F16, out_t=O.F16, m=m, n=8192, k=256, la=ROW, lb=COL, alpha=1.0, beta=0.0,
+                seed=75)
+    got, want = _run(case, with_c=False)
+    assert 0 <= O.max_rel_err(O.F16, got, want) <= 2e-3
