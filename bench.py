@@ -42,7 +42,7 @@ METRIC = "hgemm 8192^3 TFLOP/s"
 FALLBACK_PEAK_TFLOPS = 1590.0
 # dram bytes per launch of the GEMM kernel from the ncu capture summarised under profiles/
 # (None until a capture exists for the current kernel)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.408e9  # 8192-row launch: 1.279 GB read + 0.129 GB written
 
 
 def measured_peaks():
@@ -292,7 +292,8 @@ def main():
     peak, peak_src, _ = measured_peaks()
     kernel_tflops = 2.0 * m_local * N * K / (ms_per_step * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
-                "frac": kernel_tflops / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "frac": kernel_tflops / peak,
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
                 "peak_source": peak_src, "kernel": "gemm_tcgen05_pair_kernel<half,half,float>",
                 "algorithmic_flops_per_launch": 2.0 * m_local * N * K}
 

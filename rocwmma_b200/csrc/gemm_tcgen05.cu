@@ -72,6 +72,7 @@ namespace
         uint32_t    chunkKB; // k-blocks per accumulation chain; 0 = all of K in one chain
         uint32_t    wide; // 1: rows of C and D are 32-byte aligned (256-bit accesses)
         uint32_t    bn; // tile width (columns of D per tile): 256, or less for the pair kernel
+        uint32_t    band; // tile rows per raster band (tiles of a band share their rows of A in L2)
     };
 
     template <typename T>
@@ -107,13 +108,13 @@ namespace
         static constexpr uint32_t fmt = FMT_E4M3, acc = ACC_F32;
     };
 
-    __device__ inline void tileCoord(uint32_t t, uint32_t tilesM, uint32_t tilesN, uint32_t& tm,
-                                     uint32_t& tn)
+    __device__ inline void tileCoord(uint32_t t, uint32_t tilesM, uint32_t tilesN, uint32_t band,
+                                     uint32_t& tm, uint32_t& tn)
     {
-        const uint32_t perGroup = GROUP_M * tilesN;
+        const uint32_t perGroup = band * tilesN;
         const uint32_t group    = t / perGroup;
-        const uint32_t firstM   = group * GROUP_M;
-        const uint32_t rows     = min(tilesM - firstM, GROUP_M);
+        const uint32_t firstM   = group * band;
+        const uint32_t rows     = min(tilesM - firstM, band);
         const uint32_t r        = t % perGroup;
         tm                      = firstM + r % rows;
         tn                      = r / rows;
@@ -436,7 +437,7 @@ namespace
                 for(uint32_t t = blockIdx.x; ok && t < numTiles; t += gridDim.x)
                 {
                     uint32_t tm, tn;
-                    tileCoord(t, tilesM, tilesN, tm, tn);
+                    tileCoord(t, tilesM, tilesN, p.band, tm, tn);
                     for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
                     {
                         const uint32_t s  = it % STAGES;
@@ -535,7 +536,7 @@ namespace
             for(uint32_t t = blockIdx.x; ok && t < numTiles; t += gridDim.x)
             {
                 uint32_t tm, tn;
-                tileCoord(t, tilesM, tilesN, tm, tn);
+                tileCoord(t, tilesM, tilesN, p.band, tm, tn);
                 const uint32_t row = tm * BM + quad * 32 + lane;
                 for(uint32_t ch = 0; ch < numChunks; ++ch, ++accIter)
                 {
@@ -677,7 +678,7 @@ namespace
                 for(uint32_t t = pairId; ok && t < numTiles; t += nPairs)
                 {
                     uint32_t tm, tn;
-                    tileCoord(t, tilesM, tilesN, tm, tn);
+                    tileCoord(t, tilesM, tilesN, p.band, tm, tn);
                     const int32_t rowA = int32_t(tm * P_TILE_M + rank * 128u);
                     const int32_t rowB = int32_t(tn * bn + rank * (bn / 2u));
                     for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
@@ -762,7 +763,7 @@ namespace
             for(uint32_t t = pairId; ok && t < numTiles; t += nPairs)
             {
                 uint32_t tm, tn;
-                tileCoord(t, tilesM, tilesN, tm, tn);
+                tileCoord(t, tilesM, tilesN, p.band, tm, tn);
                 const uint32_t row = tm * P_TILE_M + rank * 128u + quad * 32u + lane;
                 for(uint32_t ch = 0; ch < numChunks; ++ch, ++accIter)
                 {
@@ -903,7 +904,13 @@ namespace
                                           || aligned32(c, ldc, sizeof(OutT)))
                                   ? 1u
                                   : 0u;
-        GemmParams  p{m, n, k, c, d, ldc, ldd, alpha, beta, status, chunkKB, wide, BN};
+        // B200WMMA_GEMM_BAND overrides the raster band height (tuning only)
+        static const uint32_t bandEnv = [] {
+            const char* e = getenv("B200WMMA_GEMM_BAND");
+            return e ? uint32_t(atoi(e)) : 0u;
+        }();
+        GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
+                     status, chunkKB, wide, BN, bandEnv ? bandEnv : GROUP_M};
         CUtensorMap mapA, mapB;
 
         if(pairEnabled() && m > BM && sms >= 2)

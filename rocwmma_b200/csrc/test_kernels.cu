@@ -1,0 +1,277 @@
+// Device-side unit-test kernels for the fragment API (built into libb200wmma_test.so,
+// used only by tests/).  They mirror the reference's API-level unit tests:
+//   * load -> store round trip per warp     (test/unit/load_store_matrix_sync_test/device/
+//                                            load_store_matrix_sync.hpp:38-135)
+//   * cooperative load -> store round trip  (test/unit/load_store_matrix_coop_sync_test/device/
+//                                            load_store_matrix_coop_sync.hpp:39-250)
+//   * fill_fragment -> store                (test/unit/fill_fragment_test/device/
+//                                            fill_fragment.hpp:37-120)
+//   * MappingUtil coordinates               (test/unit/map_util_test)
+// Contamination (writes outside the tile) is checked on the host side by padding the
+// buffers, as the reference does (test/unit/contamination_test).
+#include <cstdint>
+#include <cuda_runtime.h>
+#include <rocwmma/rocwmma.hpp>
+#include <rocwmma/rocwmma_block.hpp>
+#include <rocwmma/rocwmma_coop.hpp>
+
+using namespace rocwmma;
+
+#define TEST_API extern "C" __attribute__((visibility("default")))
+
+namespace
+{
+    template <typename Layout>
+    __device__ inline uint32_t tileOrigin(uint32_t tr, uint32_t tc, uint32_t h, uint32_t w,
+                                          uint32_t ld)
+    {
+        return std::is_same<Layout, row_major>::value ? tr * h * ld + tc * w
+                                                      : tc * w * ld + tr * h;
+    }
+
+    // mode 0: every warp moves its own tile with load/store_matrix_sync
+    // mode W > 0: the W warps of a block move ONE tile with the cooperative calls
+    // mode -1: fill_fragment(value read from in[0]) then store_matrix_sync
+    template <typename MatrixT, uint32_t BM, uint32_t BN, uint32_t BK, typename DataT,
+              typename Layout>
+    __global__ void roundTrip(DataT const* in, DataT* out, uint32_t ld, uint32_t tilesR,
+                              uint32_t tilesC, int mode)
+    {
+        using Frag = fragment<MatrixT, BM, BN, BK, DataT, Layout>;
+        Frag           frag;
+        const uint32_t h = Frag::height(), w = Frag::width();
+        const uint32_t warpInBlock = threadIdx.x / Constants::AMDGCN_WAVE_SIZE;
+        const uint32_t warpsPerBlk = blockDim.x / Constants::AMDGCN_WAVE_SIZE;
+        if(mode > 0)
+        {
+            const uint32_t tile = blockIdx.x;
+            if(tile >= tilesR * tilesC)
+                return;
+            const uint32_t off = tileOrigin<Layout>(tile / tilesC, tile % tilesC, h, w, ld);
+            load_matrix_coop_sync(frag, in + off, ld, warpInBlock, warpsPerBlk);
+            store_matrix_coop_sync(out + off, frag, ld, warpInBlock, warpsPerBlk);
+            return;
+        }
+        const uint32_t tile = blockIdx.x * warpsPerBlk + warpInBlock;
+        if(tile >= tilesR * tilesC)
+            return;
+        const uint32_t off = tileOrigin<Layout>(tile / tilesC, tile % tilesC, h, w, ld);
+        if(mode == 0)
+            load_matrix_sync(frag, in + off, ld);
+        else
+            fill_fragment(frag, in[0]);
+        store_matrix_sync(out + off, frag, ld);
+    }
+
+    template <typename MatrixT, uint32_t BM, uint32_t BN, uint32_t BK, typename DataT,
+              typename Layout>
+    int launchRT(void const* in, void* out, uint32_t ld, uint32_t tilesR, uint32_t tilesC, int mode,
+                 int warps, cudaStream_t s)
+    {
+        const uint32_t tiles  = tilesR * tilesC;
+        const uint32_t blocks = mode > 0 ? tiles : (tiles + warps - 1) / warps;
+        roundTrip<MatrixT, BM, BN, BK, DataT, Layout><<<blocks, warps * 32, 0, s>>>(
+            static_cast<DataT const*>(in), static_cast<DataT*>(out), ld, tilesR, tilesC, mode);
+        return cudaGetLastError() == cudaSuccess ? 0 : -4;
+    }
+
+    template <typename MatrixT, uint32_t BM, uint32_t BN, uint32_t BK, typename DataT>
+    int byLayout(int layout, void const* in, void* out, uint32_t ld, uint32_t tr, uint32_t tc,
+                 int mode, int warps, cudaStream_t s)
+    {
+        return layout == 0
+                   ? launchRT<MatrixT, BM, BN, BK, DataT, row_major>(in, out, ld, tr, tc, mode,
+                                                                     warps, s)
+                   : launchRT<MatrixT, BM, BN, BK, DataT, col_major>(in, out, ld, tr, tc, mode,
+                                                                     warps, s);
+    }
+
+    template <uint32_t BM, uint32_t BN, uint32_t BK, typename DataT>
+    int byMatrix(int matrix, int layout, void const* in, void* out, uint32_t ld, uint32_t tr,
+                 uint32_t tc, int mode, int warps, cudaStream_t s)
+    {
+        switch(matrix)
+        {
+        case 0:
+            return byLayout<matrix_a, BM, BN, BK, DataT>(layout, in, out, ld, tr, tc, mode, warps,
+                                                         s);
+        case 1:
+            return byLayout<matrix_b, BM, BN, BK, DataT>(layout, in, out, ld, tr, tc, mode, warps,
+                                                         s);
+        case 2:
+            return byLayout<accumulator, BM, BN, BK, DataT>(layout, in, out, ld, tr, tc, mode,
+                                                            warps, s);
+        }
+        return -1;
+    }
+
+    template <typename DataT>
+    int byShape(int shape, int matrix, int layout, void const* in, void* out, uint32_t ld,
+                uint32_t tr, uint32_t tc, int mode, int warps, cudaStream_t s)
+    {
+        switch(shape)
+        {
+        case 0:
+            return byMatrix<16, 16, 16, DataT>(matrix, layout, in, out, ld, tr, tc, mode, warps, s);
+        case 1:
+            return byMatrix<32, 32, 32, DataT>(matrix, layout, in, out, ld, tr, tc, mode, warps, s);
+        case 2:
+            return byMatrix<64, 16, 32, DataT>(matrix, layout, in, out, ld, tr, tc, mode, warps, s);
+        }
+        return -1;
+    }
+
+    __global__ void mappingKernel(uint32_t* out, uint32_t ldm)
+    {
+        using Map = MappingUtil<16, 32, float, row_major>;
+        using MapC = MappingUtil<16, 32, float, col_major>;
+        if((threadIdx.x % Constants::AMDGCN_WAVE_SIZE) != 0)
+            return;
+        const uint32_t warpsX = blockDim.x / Constants::AMDGCN_WAVE_SIZE;
+        const uint32_t warp   = ((blockIdx.y * gridDim.x + blockIdx.x) * blockDim.y + threadIdx.y)
+                                  * warpsX
+                              + threadIdx.x / Constants::AMDGCN_WAVE_SIZE;
+        uint32_t* o = out + warp * 12;
+        auto      wc = Map::waveCoord();
+        auto      bc = Map::blockCoord();
+        auto      mc = Map::matrixCoord();
+        auto      wg = Map::workgroupDim();
+        o[0] = get<0>(wc), o[1] = get<1>(wc);
+        o[2] = get<0>(bc), o[3] = get<1>(bc);
+        o[4] = get<0>(mc), o[5] = get<1>(mc);
+        o[6] = get<0>(wg), o[7] = get<1>(wg);
+        o[8]  = Map::dataOffset(mc, ldm);
+        o[9]  = MapC::dataOffset(mc, ldm);
+        o[10] = get<0>(Map::matrixCoordN(7)) * 1000 + get<1>(Map::matrixCoordN(7));
+        o[11] = Map::laneId() + get<1>(Map::blockCoordM(5)) * 100 + get<0>(Map::blockCoordM(5));
+    }
+
+    // A wait that nothing will ever satisfy: the barrier expects one arrival and gets none.
+    // The bounded wait must give up after `limitCycles`, raise the block's abort flag and
+    // let the kernel finish normally; out[0] = 1 if it returned false, out[1] = wait code,
+    // out[2] = 1 if a second waiter in the block saw the abort flag and left too.
+    __global__ void boundedWaitKernel(uint32_t* out, long long limitCycles)
+    {
+        __shared__ uint64_t                    bar;
+        __shared__ rocwmma::block::AbortState abortState;
+        if(threadIdx.x == 0)
+        {
+            rocwmma::block::mbar_init(&bar, 1);
+            abortState.flag = 0;
+            abortState.code = 0;
+            rocwmma::block::mbar_init_fence();
+        }
+        __syncthreads();
+        if(threadIdx.x == 0)
+        {
+            const bool ok = rocwmma::block::mbar_wait(&bar, 0, &abortState,
+                                                      rocwmma::block::WAIT_STAGE_FULL, limitCycles);
+            out[0] = ok ? 0u : 1u;
+            out[1] = abortState.code;
+        }
+        else if(threadIdx.x == 32)
+        {
+            // much longer limit: this one must leave because of the flag, not its own clock
+            const bool ok = rocwmma::block::mbar_wait(&bar, 0, &abortState,
+                                                      rocwmma::block::WAIT_ACC_FULL,
+                                                      limitCycles * 1000);
+            out[2] = ok ? 0u : 1u;
+        }
+        __syncthreads();
+        out[3] = abortState.flag;
+    }
+} // namespace
+
+// Runs the never-satisfied wait with a limit of `limit_cycles` SM cycles (keep it around a
+// millisecond); the kernel always terminates by itself.
+TEST_API int b200wmma_test_bounded_wait(uint32_t* out4, long long limit_cycles, void* stream)
+{
+    if(limit_cycles <= 0 || limit_cycles > 20000000ll)
+        return -1;
+    boundedWaitKernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(out4, limit_cycles);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// elem_bytes 1/2/4/8 -> int8_t / float16_t / float32_t / float64_t; matrix 0/1/2 = a/b/acc;
+// layout 0 row, 1 col; shape 0 = 16x16x16, 1 = 32x32x32, 2 = 64x16x32; mode see roundTrip.
+TEST_API int b200wmma_test_round_trip(int elem_bytes, int matrix, int layout, int shape,
+                                      const void* in, void* out, uint32_t ld, uint32_t tiles_r,
+                                      uint32_t tiles_c, int mode, int warps, void* stream)
+{
+    auto s = static_cast<cudaStream_t>(stream);
+    if(warps < 1 || warps > 8)
+        return -1;
+    switch(elem_bytes)
+    {
+    case 1:
+        return byShape<int8_t>(shape, matrix, layout, in, out, ld, tiles_r, tiles_c, mode, warps,
+                               s);
+    case 2:
+        return byShape<float16_t>(shape, matrix, layout, in, out, ld, tiles_r, tiles_c, mode,
+                                  warps, s);
+    case 4:
+        return byShape<float32_t>(shape, matrix, layout, in, out, ld, tiles_r, tiles_c, mode,
+                                  warps, s);
+    case 8:
+        return byShape<float64_t>(shape, matrix, layout, in, out, ld, tiles_r, tiles_c, mode,
+                                  warps, s);
+    }
+    return -1;
+}
+
+// Fragment geometry as the device sees it: out[0..3] = height, width, num_elements, kDim.
+TEST_API int b200wmma_test_geometry(int elem_bytes, int matrix, int shape, uint32_t* out4)
+{
+#define GEOM(T, M, BM, BN, BK)                                   \
+    {                                                            \
+        using F = fragment<M, BM, BN, BK, T, row_major>;         \
+        out4[0] = F::height();                                   \
+        out4[1] = F::width();                                    \
+        out4[2] = F::num_elements;                               \
+        out4[3] = F::kDim();                                     \
+        return 0;                                                \
+    }
+#define GEOM_SHAPE(T, M)                 \
+    switch(shape)                        \
+    {                                    \
+    case 0:                              \
+        GEOM(T, M, 16, 16, 16)           \
+    case 1:                              \
+        GEOM(T, M, 32, 32, 32)           \
+    case 2:                              \
+        GEOM(T, M, 64, 16, 32)           \
+    }                                    \
+    return -1;
+#define GEOM_MATRIX(T)                   \
+    switch(matrix)                       \
+    {                                    \
+    case 0:                              \
+        GEOM_SHAPE(T, matrix_a)          \
+    case 1:                              \
+        GEOM_SHAPE(T, matrix_b)          \
+    case 2:                              \
+        GEOM_SHAPE(T, accumulator)       \
+    }                                    \
+    return -1;
+    switch(elem_bytes)
+    {
+    case 1:
+        GEOM_MATRIX(int8_t)
+    case 2:
+        GEOM_MATRIX(float16_t)
+    case 4:
+        GEOM_MATRIX(float32_t)
+    case 8:
+        GEOM_MATRIX(float64_t)
+    }
+    return -1;
+}
+
+// Launches grid (gx, gy) of blocks (32 * wx, wy); out holds 12 words per warp.
+TEST_API int b200wmma_test_mapping(uint32_t* out, uint32_t gx, uint32_t gy, uint32_t wx,
+                                   uint32_t wy, uint32_t ldm, void* stream)
+{
+    mappingKernel<<<dim3(gx, gy), dim3(32 * wx, wy), 0, static_cast<cudaStream_t>(stream)>>>(out,
+                                                                                            ldm);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
