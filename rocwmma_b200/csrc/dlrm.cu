@@ -25,6 +25,7 @@
 //
 // Limits: fp16, m <= 32, k a multiple of 16 and <= 256, pointers 16-byte aligned.
 #include "common.cuh"
+#include "runtime.cuh"
 #include <cstdlib>
 #include <cuda_fp16.h>
 
@@ -83,11 +84,51 @@ namespace
         uint32_t numGroups; // ceil(batch / 8)
     };
 
-    // Sample `q` of this warp's sequence: groups are dealt round-robin to warps.
-    __device__ inline uint32_t sampleOf(uint32_t q, uint32_t warpGlobal, uint32_t totalWarps)
+    // Work distribution: groups of 8 samples are handed out through one global counter, so
+    // a warp that finishes early simply takes the next group (a fixed round-robin deal left
+    // the slowest warp one group -- up to 8 % of the run -- behind the rest).  A warp walks
+    // its samples as a sequence q = 0, 1, 2, ...; the feed knows the group of the current
+    // eight and of the next eight, which is as far ahead as the prefetch looks.
+    struct GroupFeed
     {
-        return (warpGlobal + (q / GROUP) * totalWarps) * GROUP + (q % GROUP);
-    }
+        unsigned int* counter;
+        uint32_t      numGroups;
+        uint32_t      g0, g1; // groups of q in [base, base + 8) and [base + 8, base + 16)
+        uint32_t      base;
+
+        __device__ inline uint32_t fetch(uint32_t lane)
+        {
+            uint32_t v = 0;
+            if(lane == 0)
+                v = atomicAdd(counter, 1u);
+            return __shfl_sync(0xffffffffu, v, 0);
+        }
+        __device__ inline void init(unsigned int* c, uint32_t groups, uint32_t lane)
+        {
+            counter   = c;
+            numGroups = groups;
+            base      = 0;
+            g0        = fetch(lane);
+            g1        = g0 < numGroups ? fetch(lane) : numGroups;
+        }
+        // Called with q == base + 8: the next eight become the current eight.
+        __device__ inline void advance(uint32_t lane)
+        {
+            g0 = g1;
+            g1 = g0 < numGroups ? fetch(lane) : numGroups;
+            base += GROUP;
+        }
+        __device__ inline bool done() const
+        {
+            return g0 >= numGroups;
+        }
+        // Sample index of sequence position q (base <= q < base + 16), or ~0u past the end.
+        __device__ inline uint32_t sample(uint32_t q) const
+        {
+            const uint32_t grp = (q - base) < GROUP ? g0 : g1;
+            return grp < numGroups ? grp * GROUP + (q % GROUP) : 0xffffffffu;
+        }
+    };
 
     // Copies one sample (m rows of k halves, contiguous in global memory) into a ring slot.
     __device__ inline void issueSample(uint32_t slotAddr, __half const* sample, Shape const& sh,
@@ -108,7 +149,8 @@ namespace
     // =====================================================================================
     template <uint32_t NSTAGES>
     __global__ void __launch_bounds__(MAX_WARPS * 32, 1)
-        dlrmFwdKernel(__half const* __restrict__ input, __half* __restrict__ output, Shape sh)
+        dlrmFwdKernel(__half const* __restrict__ input, __half* __restrict__ output, Shape sh,
+                      unsigned int* counter)
     {
         extern __shared__ __align__(16) uint8_t smem[];
         const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -127,26 +169,17 @@ namespace
             reinterpret_cast<uint32_t*>(zeroRow)[i] = 0u;
         __syncthreads();
 
-        const uint32_t nWarps     = blockDim.x / 32;
-        const uint32_t totalWarps = gridDim.x * nWarps;
-        const uint32_t warpGlobal = blockIdx.x * nWarps + warp;
-        const uint32_t myGroups
-            = warpGlobal < sh.numGroups ? (sh.numGroups - warpGlobal + totalWarps - 1) / totalWarps
-                                        : 0;
-        const uint32_t numQ = myGroups * GROUP;
-        const bool     twoM = sh.m > 16;
+        const bool twoM = sh.m > 16;
+        GroupFeed  feed;
+        feed.init(counter, sh.numGroups, lane);
 
         // prologue
 #pragma unroll
         for(uint32_t q = 0; q < NSTAGES - 1; ++q)
         {
-            if(q < numQ)
-            {
-                const uint32_t s = sampleOf(q, warpGlobal, totalWarps);
-                if(s < sh.batch)
-                    issueSample(ringAddr + q * sh.stageBytes, input + size_t(s) * sh.m * sh.k, sh,
-                                lane);
-            }
+            const uint32_t s = feed.sample(q);
+            if(s < sh.batch)
+                issueSample(ringAddr + q * sh.stageBytes, input + size_t(s) * sh.m * sh.k, sh, lane);
             cpAsyncCommit();
         }
 
@@ -155,23 +188,24 @@ namespace
         const uint32_t lmRow = ((lane >> 3) & 1u) * 8u + (lane & 7u);
         const uint32_t lmCol = (lane >> 4) * 8u;
 
-        for(uint32_t q = 0; q < numQ; ++q)
+        for(uint32_t q = 0;; ++q)
         {
+            if(q - feed.base == GROUP)
+                feed.advance(lane);
+            if(feed.done())
+                break;
             cpAsyncWait<NSTAGES - 2>();
             __syncwarp();
             {
                 const uint32_t qn = q + NSTAGES - 1;
-                if(qn < numQ)
-                {
-                    const uint32_t s = sampleOf(qn, warpGlobal, totalWarps);
-                    if(s < sh.batch)
-                        issueSample(ringAddr + (qn % NSTAGES) * sh.stageBytes,
-                                    input + size_t(s) * sh.m * sh.k, sh, lane);
-                }
+                const uint32_t s  = feed.sample(qn);
+                if(s < sh.batch)
+                    issueSample(ringAddr + (qn % NSTAGES) * sh.stageBytes,
+                                input + size_t(s) * sh.m * sh.k, sh, lane);
                 cpAsyncCommit();
             }
 
-            const uint32_t sample = sampleOf(q, warpGlobal, totalWarps);
+            const uint32_t sample = feed.sample(q);
             const uint32_t slot   = q % GROUP;
             if(sample < sh.batch)
             {
@@ -229,7 +263,7 @@ namespace
             if(slot == GROUP - 1)
             {
                 __syncwarp();
-                const uint32_t first = sampleOf(q - (GROUP - 1), warpGlobal, totalWarps);
+                const uint32_t first = feed.g0 * GROUP;
                 const uint32_t cnt   = min(GROUP, sh.batch - first);
                 __half*        gout  = output + size_t(first) * sh.outLen;
                 if(cnt == GROUP)
@@ -255,7 +289,8 @@ namespace
     template <uint32_t NSTAGES>
     __global__ void __launch_bounds__(MAX_WARPS * 32, 1)
         dlrmBwdKernel(__half const* __restrict__ input, __half const* __restrict__ upstream,
-                      __half* __restrict__ grad, __half* __restrict__ mlpGrad, Shape sh)
+                      __half* __restrict__ grad, __half* __restrict__ mlpGrad, Shape sh,
+                      unsigned int* counter)
     {
         extern __shared__ __align__(16) uint8_t smem[];
         const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -284,17 +319,12 @@ namespace
             reinterpret_cast<uint32_t*>(gTile)[i] = 0u; // diagonal and padding stay zero
         __syncthreads();
 
-        const uint32_t nWarps     = blockDim.x / 32;
-        const uint32_t totalWarps = gridDim.x * nWarps;
-        const uint32_t warpGlobal = blockIdx.x * nWarps + warp;
-        const uint32_t myGroups
-            = warpGlobal < sh.numGroups ? (sh.numGroups - warpGlobal + totalWarps - 1) / totalWarps
-                                        : 0;
-        const uint32_t numQ = myGroups * GROUP;
-        const bool     twoM = sh.m > 16;
+        const bool twoM = sh.m > 16;
+        GroupFeed  feed;
+        feed.init(counter, sh.numGroups, lane);
 
         auto issue = [&](uint32_t q) {
-            const uint32_t s = sampleOf(q, warpGlobal, totalWarps);
+            const uint32_t s = feed.sample(q);
             if(s < sh.batch)
                 issueSample(ringAddr + (q % NSTAGES) * sh.stageBytes,
                             input + size_t(s) * sh.m * sh.k, sh, lane);
@@ -307,7 +337,7 @@ namespace
         constexpr uint32_t TRI_REGS = 16; // ceil(496 / 32) for m = 32
         __half             triNext[TRI_REGS];
         auto prefetchTriangle = [&](uint32_t q) {
-            const uint32_t s = q < numQ ? sampleOf(q, warpGlobal, totalWarps) : sh.batch;
+            const uint32_t s = feed.sample(q);
             if(s < sh.batch)
             {
                 __half const* src = upstream + size_t(s) * sh.outLen + sh.k;
@@ -324,8 +354,7 @@ namespace
 #pragma unroll
         for(uint32_t q = 0; q < NSTAGES - 1; ++q)
         {
-            if(q < numQ)
-                issue(q);
+            issue(q);
             cpAsyncCommit();
         }
         prefetchTriangle(0);
@@ -333,17 +362,20 @@ namespace
         const uint32_t lmRow = ((lane >> 3) & 1u) * 8u + (lane & 7u);
         const uint32_t lmCol = (lane >> 4) * 8u;
 
-        for(uint32_t q = 0; q < numQ; ++q)
+        for(uint32_t q = 0;; ++q)
         {
+            if(q - feed.base == GROUP)
+                feed.advance(lane);
+            if(feed.done())
+                break;
             cpAsyncWait<NSTAGES - 2>();
             __syncwarp();
-            if(q + NSTAGES - 1 < numQ)
-                issue(q + NSTAGES - 1);
+            issue(q + NSTAGES - 1);
             cpAsyncCommit();
 
-            const uint32_t sample = sampleOf(q, warpGlobal, totalWarps);
+            const uint32_t sample = feed.sample(q);
             if(sample >= sh.batch)
-                continue; // only the padding of the last group; nothing follows it
+                continue; // padding of the batch's last group
             uint8_t*       slotPtr  = mine + (q % NSTAGES) * sh.stageBytes;
             const uint32_t slotAddr = ringAddr + (q % NSTAGES) * sh.stageBytes;
 
@@ -565,17 +597,21 @@ extern "C" int b200wmma_dlrm_fwd(int dtype, const void* input, void* output, uin
     auto           s      = static_cast<cudaStream_t>(stream);
     auto           in     = static_cast<__half const*>(input);
     auto           out    = static_cast<__half*>(output);
+    unsigned int*  ctr    = b200wmma::launchCounter();
+    if(!ctr)
+        return B200WMMA_ERR_CUDA;
+    B200WMMA_CUDA_TRY(cudaMemsetAsync(ctr, 0, sizeof(unsigned int), s));
     if(plan.stages == 3)
     {
         if((rc = prepare(dlrmFwdKernel<3>)) != B200WMMA_OK)
             return rc;
-        dlrmFwdKernel<3><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, out, sh);
+        dlrmFwdKernel<3><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, out, sh, ctr);
     }
     else
     {
         if((rc = prepare(dlrmFwdKernel<2>)) != B200WMMA_OK)
             return rc;
-        dlrmFwdKernel<2><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, out, sh);
+        dlrmFwdKernel<2><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, out, sh, ctr);
     }
     return b200wmma::cudaToStatus(cudaGetLastError());
 }
@@ -606,17 +642,21 @@ extern "C" int b200wmma_dlrm_bwd(int dtype, const void* input, const void* upstr
     auto           up     = static_cast<__half const*>(upstream);
     auto           g      = static_cast<__half*>(grad);
     auto           mg     = static_cast<__half*>(mlp_grad);
+    unsigned int*  ctr    = b200wmma::launchCounter();
+    if(!ctr)
+        return B200WMMA_ERR_CUDA;
+    B200WMMA_CUDA_TRY(cudaMemsetAsync(ctr, 0, sizeof(unsigned int), s));
     if(plan.stages == 3)
     {
         if((rc = prepare(dlrmBwdKernel<3>)) != B200WMMA_OK)
             return rc;
-        dlrmBwdKernel<3><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, up, g, mg, sh);
+        dlrmBwdKernel<3><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, up, g, mg, sh, ctr);
     }
     else
     {
         if((rc = prepare(dlrmBwdKernel<2>)) != B200WMMA_OK)
             return rc;
-        dlrmBwdKernel<2><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, up, g, mg, sh);
+        dlrmBwdKernel<2><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, up, g, mg, sh, ctr);
     }
     return b200wmma::cudaToStatus(cudaGetLastError());
 }

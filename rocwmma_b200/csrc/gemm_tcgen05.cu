@@ -934,6 +934,13 @@ namespace
                     bn       = cand;
                 }
             }
+            // B200WMMA_GEMM_BN overrides the tile width (tuning only)
+            static const uint32_t bnEnv = [] {
+                const char* e = getenv("B200WMMA_GEMM_BN");
+                return e ? uint32_t(atoi(e)) : 0u;
+            }();
+            if(bnEnv >= 128 && bnEnv <= 256 && bnEnv % 32 == 0)
+                bn = bnEnv;
             p.bn   = bn;
             int rc = makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, 128);
             if(rc != B200WMMA_OK)

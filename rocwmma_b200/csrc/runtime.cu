@@ -20,6 +20,8 @@ namespace b200wmma
             void*     stage[4]      = {nullptr, nullptr, nullptr, nullptr}; // A, B, C, D staging
             size_t    stageBytes[4] = {0, 0, 0, 0};
             HostPipe  pipe;
+            unsigned int* counters    = nullptr; // ring of 64 launch counters, 32 bytes apart
+            unsigned int  nextCounter = 0;
         };
 
         std::mutex  g_mutex;
@@ -117,6 +119,26 @@ namespace b200wmma
         return st->stage[slot];
     }
 
+    unsigned int* launchCounter()
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceState*                st = current();
+        if(!st)
+            return nullptr;
+        if(!st->counters)
+        {
+            if(cudaMalloc(&st->counters, 64 * 32) != cudaSuccess)
+            {
+                (void)cudaGetLastError();
+                st->counters = nullptr;
+                return nullptr;
+            }
+        }
+        unsigned int* c = st->counters + (st->nextCounter % 64u) * 8u;
+        st->nextCounter++;
+        return c;
+    }
+
     HostPipe* hostPipe()
     {
         std::lock_guard<std::mutex> lock(g_mutex);
@@ -204,7 +226,7 @@ int b200wmma_shutdown(void)
     {
         DeviceState& st = g_dev[d];
         bool any = st.status || st.scratch || st.stage[0] || st.stage[1] || st.stage[2]
-                   || st.stage[3] || st.pipe.ok;
+                   || st.stage[3] || st.pipe.ok || st.counters;
         if(!any)
             continue;
         if(cudaSetDevice(d) != cudaSuccess)
@@ -216,6 +238,8 @@ int b200wmma_shutdown(void)
             (void)cudaFree(st.status);
         if(st.scratch)
             (void)cudaFree(st.scratch);
+        if(st.counters)
+            (void)cudaFree(st.counters);
         for(void*& p : st.stage)
             if(p)
                 (void)cudaFree(p);

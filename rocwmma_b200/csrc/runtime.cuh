@@ -12,6 +12,11 @@ namespace b200wmma
     // Staging buffers for the host-buffer GEMM entry point; slot 0..3 = A, B, C, D.
     void* stagingBuffer(int slot, size_t bytes);
 
+    // A 4-byte device counter for one kernel launch (work distribution).  Counters come from
+    // a per-device ring of 64, so up to 64 launches may be in flight; the caller zeroes the
+    // counter on its stream before the launch.  nullptr on failure.
+    unsigned int* launchCounter();
+
     // Copy streams and events for the host-buffer GEMM entry point (created on first use,
     // one set per device, destroyed by b200wmma_shutdown).
     constexpr int HOST_PIPE_MAX_CHUNKS = 16;

@@ -14,6 +14,7 @@
 #include <rocwmma/rocwmma.hpp>
 #include <rocwmma/rocwmma_block.hpp>
 #include <rocwmma/rocwmma_coop.hpp>
+#include <rocwmma/rocwmma_transforms.hpp>
 
 using namespace rocwmma;
 
@@ -29,6 +30,9 @@ namespace
                                                       : tc * w * ld + tr * h;
     }
 
+    // mode -2: load, applyTranspose, store the transposed fragment in the orthogonal layout
+    //          (same memory image) -- matrix_a and matrix_b only
+    // mode -3: load, applyDataLayout to the other layout and back, store
     // mode 0: every warp moves its own tile with load/store_matrix_sync
     // mode W > 0: the W warps of a block move ONE tile with the cooperative calls
     // mode -1: fill_fragment(value read from in[0]) then store_matrix_sync
@@ -56,6 +60,26 @@ namespace
         if(tile >= tilesR * tilesC)
             return;
         const uint32_t off = tileOrigin<Layout>(tile / tilesC, tile % tilesC, h, w, ld);
+        if(mode == -2)
+        {
+            if constexpr(!std::is_same<MatrixT, accumulator>::value && BN % 16u == 0u)
+            {
+                load_matrix_sync(frag, in + off, ld);
+                auto t = applyTranspose(frag);
+                // the transpose in the orthogonal layout addresses memory exactly like frag
+                store_matrix_sync(out + off, t, ld);
+            }
+            return;
+        }
+        if(mode == -3)
+        {
+            using Other = typename detail::OrthogonalLayout<Layout>::type;
+            load_matrix_sync(frag, in + off, ld);
+            auto const& o = applyDataLayout<Other>(frag);
+            auto const& back = applyDataLayout<Layout>(o);
+            store_matrix_sync(out + off, back, ld);
+            return;
+        }
         if(mode == 0)
             load_matrix_sync(frag, in + off, ld);
         else

@@ -162,3 +162,24 @@ def test_bounded_wait_gives_up_and_reports():
     assert gave_up == 1 and code == 2 and follower_left == 1 and flag == 1
     # the device is still healthy
     assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("eb", [1, 2, 4, 8])
+@pytest.mark.parametrize("matrix", [0, 1])
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("shape", [0, 1, 2])
+def test_apply_transpose(eb, matrix, layout, shape):
+    """applyTranspose(A row-major) is B col-major of the same memory (and so on): storing the
+    transposed fragment with its own, orthogonal, layout must reproduce the input image
+    (rocwmma_transforms_impl.hpp:58-172)."""
+    src, out, major, minor = _run_round_trip(eb, matrix, layout, shape, mode=-2, warps=2)
+    assert np.array_equal(out[:major, :minor], src[:major, :minor])
+    assert (out[:major, minor:] == 77).all() and (out[major:] == 77).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("matrix,layout", [(0, 0), (1, 1), (2, 0)])
+def test_apply_data_layout_is_a_recast(matrix, layout):
+    src, out, major, minor = _run_round_trip(2, matrix, layout, 1, mode=-3, warps=2)
+    assert np.array_equal(out[:major, :minor], src[:major, :minor])
