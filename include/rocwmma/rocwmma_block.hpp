@@ -155,6 +155,68 @@ namespace rocwmma
                          : "memory");
         }
 
+        // ---- TMA stores (shared -> global), bulk-group completion ----------------------------
+        // Generic-proxy writes to shared memory must be fenced before the async proxy reads them.
+        ROCWMMA_DEVICE inline void fence_async_shared()
+        {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        // Writes the box at (x, y) of `tensorMap` from shared memory; parts of the box outside
+        // the tensor are dropped.  x * element size must be a multiple of 16 bytes, x, y >= 0.
+        ROCWMMA_DEVICE inline void tma_store_2d(void const* tensorMap, void const* src, int32_t x,
+                                                int32_t y)
+        {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::
+                             "l"(reinterpret_cast<uint64_t>(tensorMap)),
+                         "r"(smem_addr(src)), "r"(x), "r"(y)
+                         : "memory");
+        }
+        // Same, but adds the box to global memory (element type of the tensor map; the adds
+        // are performed by the L2, round to nearest for fp32).
+        ROCWMMA_DEVICE inline void tma_reduce_add_2d(void const* tensorMap, void const* src,
+                                                     int32_t x, int32_t y)
+        {
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];" ::
+                             "l"(reinterpret_cast<uint64_t>(tensorMap)),
+                         "r"(smem_addr(src)), "r"(x), "r"(y)
+                         : "memory");
+        }
+        ROCWMMA_DEVICE inline void tma_store_commit()
+        {
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        // Waits until at most N of this thread's bulk groups have not yet READ their shared
+        // memory source (the source may then be overwritten).
+        template <int N>
+        ROCWMMA_DEVICE inline void tma_store_wait_read()
+        {
+            asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+        }
+        // Waits until at most N of this thread's bulk groups are still incomplete (their global
+        // writes performed).
+        template <int N>
+        ROCWMMA_DEVICE inline void tma_store_wait_all()
+        {
+            asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+        }
+        // Barrier among `count` threads that also ANDs a predicate over them: every
+        // participant gets true only if all passed true.
+        ROCWMMA_DEVICE inline bool named_barrier_all(uint32_t id, uint32_t count, bool pred)
+        {
+            uint32_t r;
+            asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %3, 0;\n\t"
+                         "bar.red.and.pred p, %1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(r)
+                         : "r"(id), "r"(count), "r"(uint32_t(pred))
+                         : "memory");
+            return r != 0u;
+        }
+        // Barrier among `count` threads of the block (id 1..15; 0 is __syncthreads).
+        ROCWMMA_DEVICE inline void named_barrier(uint32_t id, uint32_t count)
+        {
+            asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+        }
+
         // ---- tensor memory ----------------------------------------------------------
         // One full warp allocates `columns` (power of two, 32..512) TMEM columns; the
         // base address is written to *slot in shared memory.

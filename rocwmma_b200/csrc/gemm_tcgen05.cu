@@ -58,7 +58,10 @@ namespace
         uint32_t   tmemBase;
         AbortState abort;
     };
-    constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/
+    // Epilogue staging: two buffers of 128 rows x 32 columns (16 KiB for 4-byte outputs),
+    // written by the epilogue threads, read by TMA stores.
+    constexpr uint32_t STG_BYTES  = 128 * 128;
+    constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 2 * STG_BYTES + 1024 /*alignment slack*/
                                     + sizeof(SharedControl) + 64;
 
     struct GemmParams
@@ -73,6 +76,7 @@ namespace
         uint32_t    wide; // 1: rows of C and D are 32-byte aligned (256-bit accesses)
         uint32_t    bn; // tile width (columns of D per tile): 256, or less for the pair kernel
         uint32_t    band; // tile rows per raster band (tiles of a band share their rows of A in L2)
+        uint32_t    tmaStore; // 1: D leaves through shared memory and TMA stores
     };
 
     template <typename T>
@@ -373,10 +377,115 @@ namespace
         return true;
     }
 
+    // ---- epilogue through shared memory and TMA ------------------------------------------
+    // One TMEM lane is one output row, so a thread that stores its row straight to global
+    // memory touches 32 different cache lines per warp instruction.  Here the 128 epilogue
+    // threads instead lay each 32-column group of the tile out in shared memory (in the
+    // swizzled order the TMA expects, which also keeps the 16-byte shared stores free of
+    // bank conflicts) and one thread hands the 128 x 32 box to a TMA store; rows and columns
+    // beyond m and n are clipped by the TMA.  With chunked K accumulation the first chunk is
+    // stored and every later chunk is ADDED by a TMA reduction (fp32 adds in L2, round to
+    // nearest), so the running sum is never read back.
+    template <uint32_t ROW_B>
+    __device__ inline uint32_t stagingOffset(uint32_t row, uint32_t chunk)
+    {
+        if constexpr(ROW_B == 128) // 128-byte swizzle: chunk index ^ (row % 8)
+            return row * 128u + ((chunk ^ (row & 7u)) << 4);
+        else // 64-byte rows, 64-byte swizzle: chunk index ^ ((row / 2) % 4)
+            return row * 64u + ((chunk ^ ((row >> 1) & 3u)) << 4);
+    }
+
+    template <typename OutT, typename CompT>
+    __device__ inline bool drainAccumulatorTma(uint64_t* accFullBar, uint32_t accPh,
+                                               AbortState* abort, uint32_t taddrRowBase,
+                                               GemmParams const& p, CUtensorMap const* tmapD,
+                                               uint8_t* staging, uint32_t& stagedGroups,
+                                               CompT alpha, CompT beta, bool useC,
+                                               uint32_t rowInTile, uint32_t tileRow0,
+                                               uint32_t colBase, uint32_t mode, bool leader)
+    {
+        constexpr uint32_t ROW_B  = 32 * sizeof(OutT); // bytes of one staged row (128 or 64)
+        constexpr uint32_t VEC    = 16 / sizeof(OutT); // elements per 16-byte chunk
+        constexpr uint32_t CHUNKS = ROW_B / 16;
+        const uint32_t     groups = p.bn / 32u;
+        const uint32_t     row    = tileRow0 + rowInTile;
+        const bool         adds   = (mode == EPI_MIDDLE || mode == EPI_LAST);
+        const bool         readC  = useC && !adds && row < p.m;
+        OutT const*        cRow   = static_cast<OutT const*>(p.c) + size_t(row) * p.ldc;
+
+        // all 128 epilogue threads must take the same way out: the barriers below have no
+        // time limit of their own
+        const bool ready = mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL);
+        if(!named_barrier_all(1, EPI_THREADS, ready))
+            return false;
+        tc_fence_after_sync();
+        if(adds && leader)
+            tma_store_wait_all<0>(); // the previous chunk's stores have been performed
+#pragma unroll 1
+        for(uint32_t g = 0; g < groups; ++g, ++stagedGroups)
+        {
+            uint8_t* buf = staging + (stagedGroups & 1u) * STG_BYTES;
+            if(leader)
+                tma_store_wait_read<1>(); // the store that last used this buffer has read it
+            named_barrier(1, EPI_THREADS);
+            uint32_t raw[32];
+            tmem_load_32x32b_x32(taddrRowBase + g * 32u, raw);
+            tmem_load_wait();
+            const uint32_t col0 = colBase + g * 32u;
+#pragma unroll
+            for(uint32_t ch = 0; ch < CHUNKS; ++ch)
+            {
+                alignas(16) OutT out[VEC];
+                alignas(16) OutT cin[VEC];
+                const uint32_t   col = col0 + ch * VEC;
+                if(readC)
+                {
+                    if(col + VEC <= p.n)
+                        ldVec<16>(cin, cRow + col);
+                    else
+                        for(uint32_t e = 0; e < VEC; ++e)
+                            cin[e] = (col + e < p.n) ? cRow[col + e] : OutT(0);
+                }
+#pragma unroll
+                for(uint32_t e = 0; e < VEC; ++e)
+                {
+                    CompT acc;
+                    if constexpr(std::is_same<CompT, float>::value)
+                        acc = __uint_as_float(raw[ch * VEC + e]);
+                    else
+                        acc = int32_t(raw[ch * VEC + e]);
+                    CompT r;
+                    if(readC)
+                        r = scaleAdd(alpha, acc, beta, CompT(toCompute(cin[e])));
+                    else if constexpr(std::is_same<CompT, float>::value)
+                        r = CompT(__fmul_rn(float(alpha), float(acc)));
+                    else
+                        r = CompT(alpha * acc);
+                    out[e] = fromCompute<OutT, CompT>(r);
+                }
+                *reinterpret_cast<uint4*>(buf + stagingOffset<ROW_B>(rowInTile, ch))
+                    = *reinterpret_cast<uint4 const*>(out);
+            }
+            fence_async_shared();
+            named_barrier(1, EPI_THREADS);
+            if(leader)
+            {
+                if(adds)
+                    tma_reduce_add_2d(tmapD, buf, int32_t(col0), int32_t(tileRow0));
+                else
+                    tma_store_2d(tmapD, buf, int32_t(col0), int32_t(tileRow0));
+                tma_store_commit();
+            }
+        }
+        tc_fence_before_sync();
+        return true;
+    }
+
     template <typename InT, typename OutT, typename CompT>
     __global__ void __launch_bounds__(NUM_THREADS, 1)
         gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmapA,
                             const __grid_constant__ CUtensorMap tmapB,
+                            const __grid_constant__ CUtensorMap tmapD,
                             const GemmParams                    p)
     {
         constexpr uint32_t BK     = ROW_BYTES / sizeof(InT); // K elements per ring slot
@@ -387,7 +496,9 @@ namespace
         extern __shared__ uint8_t smemRaw[];
         const uint32_t            rawAddr = smem_addr(smemRaw);
         uint8_t*       tiles = smemRaw + ((1024u - (rawAddr & 1023u)) & 1023u); // 1024-aligned
-        SharedControl* ctl   = reinterpret_cast<SharedControl*>(tiles + STAGES * STAGE_BYTES);
+        uint8_t*       staging = tiles + STAGES * STAGE_BYTES; // 1024-aligned: tiles are
+        SharedControl* ctl
+            = reinterpret_cast<SharedControl*>(tiles + STAGES * STAGE_BYTES + 2 * STG_BYTES);
 
         const uint32_t warp = threadIdx.x / 32;
         const uint32_t lane = threadIdx.x % 32;
@@ -416,6 +527,7 @@ namespace
             mbar_init_fence();
             tma_prefetch_descriptor(&tmapA);
             tma_prefetch_descriptor(&tmapB);
+            tma_prefetch_descriptor(&tmapD);
         }
         if(warp == 1)
         {
@@ -531,7 +643,7 @@ namespace
             const CompT    alpha = CompT(p.alpha);
             const CompT    beta  = CompT(p.beta);
             const bool     useC  = (p.beta != 0.0) && (p.c != nullptr);
-            uint32_t       accIter = 0;
+            uint32_t       accIter = 0, stagedGroups = 0;
             bool           ok      = true;
             for(uint32_t t = blockIdx.x; ok && t < numTiles; t += gridDim.x)
             {
@@ -546,10 +658,17 @@ namespace
                                           : ch == 0u            ? EPI_FIRST
                                           : ch + 1u < numChunks ? EPI_MIDDLE
                                                                 : EPI_LAST;
-                    if(!drainAccumulator<OutT, CompT>(
-                           &ctl->accFull[buf], accPh, &ctl->abort,
-                           tmemBase + ((quad * 32u) << 16) + buf * BN, p, alpha, beta, useC, row,
-                           tn * BN, mode))
+                    const uint32_t taddr = tmemBase + ((quad * 32u) << 16) + buf * BN;
+                    const bool     drained
+                        = p.tmaStore
+                              ? drainAccumulatorTma<OutT, CompT>(
+                                  &ctl->accFull[buf], accPh, &ctl->abort, taddr, p, &tmapD, staging,
+                                  stagedGroups, alpha, beta, useC, quad * 32u + lane, tm * BM,
+                                  tn * BN, mode, threadIdx.x == 64u)
+                              : drainAccumulator<OutT, CompT>(&ctl->accFull[buf], accPh,
+                                                              &ctl->abort, taddr, p, alpha, beta,
+                                                              useC, row, tn * BN, mode);
+                    if(!drained)
                     {
                         ok = false;
                         break;
@@ -557,6 +676,8 @@ namespace
                     mbar_arrive(&ctl->accEmpty[buf]);
                 }
             }
+            if(threadIdx.x == 64u)
+                tma_store_wait_all<0>(); // every TMA store of this block has been performed
         }
 
         // ---------------- teardown ----------------
@@ -604,12 +725,14 @@ namespace
         uint32_t   tmemBase;
         AbortState abort;
     };
-    constexpr uint32_t P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + sizeof(PairControl) + 64;
+    constexpr uint32_t P_SMEM_BYTES
+        = P_STAGES * P_STAGE_BYTES + 2 * STG_BYTES + 1024 + sizeof(PairControl) + 64;
 
     template <typename InT, typename OutT, typename CompT>
     __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
         gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmapA,
                                  const __grid_constant__ CUtensorMap tmapB,
+                                 const __grid_constant__ CUtensorMap tmapD,
                                  const GemmParams                    p)
     {
         constexpr uint32_t BK     = ROW_BYTES / sizeof(InT);
@@ -624,7 +747,9 @@ namespace
         extern __shared__ uint8_t smemRaw[];
         const uint32_t            rawAddr = smem_addr(smemRaw);
         uint8_t*     tiles = smemRaw + ((1024u - (rawAddr & 1023u)) & 1023u);
-        PairControl* ctl   = reinterpret_cast<PairControl*>(tiles + P_STAGES * P_STAGE_BYTES);
+        uint8_t*     staging = tiles + P_STAGES * P_STAGE_BYTES;
+        PairControl* ctl
+            = reinterpret_cast<PairControl*>(tiles + P_STAGES * P_STAGE_BYTES + 2 * STG_BYTES);
 
         const uint32_t warp   = threadIdx.x / 32;
         const uint32_t lane   = threadIdx.x % 32;
@@ -656,6 +781,7 @@ namespace
             mbar_init_fence();
             tma_prefetch_descriptor(&tmapA);
             tma_prefetch_descriptor(&tmapB);
+            tma_prefetch_descriptor(&tmapD);
         }
         if(warp == 1)
         {
@@ -758,7 +884,7 @@ namespace
             const CompT    alpha = CompT(p.alpha);
             const CompT    beta  = CompT(p.beta);
             const bool     useC  = (p.beta != 0.0) && (p.c != nullptr);
-            uint32_t       accIter = 0;
+            uint32_t       accIter = 0, stagedGroups = 0;
             bool           ok      = true;
             for(uint32_t t = pairId; ok && t < numTiles; t += nPairs)
             {
@@ -773,10 +899,17 @@ namespace
                                           : ch == 0u            ? EPI_FIRST
                                           : ch + 1u < numChunks ? EPI_MIDDLE
                                                                 : EPI_LAST;
-                    if(!drainAccumulator<OutT, CompT>(
-                           &ctl->accFull[buf], accPh, &ctl->abort,
-                           tmemBase + ((quad * 32u) << 16) + buf * BN, p, alpha, beta, useC, row,
-                           tn * bn, mode))
+                    const uint32_t taddr = tmemBase + ((quad * 32u) << 16) + buf * BN;
+                    const bool     drained
+                        = p.tmaStore
+                              ? drainAccumulatorTma<OutT, CompT>(
+                                  &ctl->accFull[buf], accPh, &ctl->abort, taddr, p, &tmapD, staging,
+                                  stagedGroups, alpha, beta, useC, quad * 32u + lane,
+                                  tm * P_TILE_M + rank * 128u, tn * bn, mode, threadIdx.x == 64u)
+                              : drainAccumulator<OutT, CompT>(&ctl->accFull[buf], accPh,
+                                                              &ctl->abort, taddr, p, alpha, beta,
+                                                              useC, row, tn * bn, mode);
+                    if(!drained)
                     {
                         ok = false;
                         break;
@@ -784,6 +917,8 @@ namespace
                     mbar_arrive_cluster(map_to_cta(smem_addr(&ctl->accEmpty[buf]), 0));
                 }
             }
+            if(threadIdx.x == 64u)
+                tma_store_wait_all<0>(); // every TMA store of this block has been performed
         }
 
         // ---------------- teardown ----------------
@@ -824,6 +959,36 @@ namespace
                 (void)cudaGetLastError();
         });
         return fn;
+    }
+
+    // Tensor map of the row-major output: rows x cols elements, `ld` apart; box = 32 columns
+    // (128 or 64 bytes, swizzled accordingly) x 128 rows.
+    int makeOutputMap(CUtensorMap* map, CUtensorMapDataType dt, size_t elemBytes, void* base,
+                      uint32_t rows, uint32_t cols, uint32_t ld)
+    {
+        EncodeFn fn = encoder();
+        if(!fn)
+            return B200WMMA_ERR_CUDA;
+        cuuint64_t dims[2]    = {cols, rows};
+        cuuint64_t strides[1] = {cuuint64_t(ld) * elemBytes};
+        cuuint32_t box[2]     = {32, 128};
+        cuuint32_t estr[2]    = {1, 1};
+        CUresult   r = fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        elemBytes == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS ? B200WMMA_OK : B200WMMA_ERR_CUDA;
+    }
+
+    template <typename OutT>
+    CUtensorMapDataType outputMapType()
+    {
+        if(std::is_same<OutT, __half>::value)
+            return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        if(std::is_same<OutT, __nv_bfloat16>::value)
+            return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        if(std::is_same<OutT, int32_t>::value)
+            return CU_TENSOR_MAP_DATA_TYPE_INT32;
+        return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     }
 
     // Tensor map of a K-major operand: `rows` rows of `k` elements, `ld` elements apart;
@@ -909,9 +1074,33 @@ namespace
             const char* e = getenv("B200WMMA_GEMM_BAND");
             return e ? uint32_t(atoi(e)) : 0u;
         }();
+        // Two epilogues.  "rows": every thread stores its own output row (256-bit accesses).
+        // "tma": the tile goes through shared memory and leaves by TMA stores / reduce-adds.
+        // Measured on 8192^3 fp16 they are equal (the epilogue hides behind the next tile's
+        // MMAs either way); with chunked accumulation, where the epilogue runs once per 512
+        // elements of K, the TMA form is 1.4x faster because the running sum is added in L2
+        // instead of being read back.  TMA stores write whole 16-byte pieces, so they are
+        // only used when a row of D ends on a 16-byte boundary (otherwise bytes between n
+        // and ldd could be touched).  B200WMMA_GEMM_EPILOGUE=rows|tma forces one (tuning).
+        static const int epilogueEnv = [] {
+            const char* e = getenv("B200WMMA_GEMM_EPILOGUE");
+            return !e ? 0 : (e[0] == 'r' ? 1 : (e[0] == 't' ? 2 : 0));
+        }();
+        const bool tmaSafe = (size_t(n) * sizeof(OutT)) % 16 == 0;
+        bool       useTma  = chunkKB != 0u;
+        if(epilogueEnv == 1)
+            useTma = false;
+        if(epilogueEnv == 2)
+            useTma = true;
+        useTma = useTma && tmaSafe;
         GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
-                     status, chunkKB, wide, BN, bandEnv ? bandEnv : GROUP_M};
-        CUtensorMap mapA, mapB;
+                     status, chunkKB, wide, BN, bandEnv ? bandEnv : GROUP_M, useTma ? 1u : 0u};
+        CUtensorMap mapA, mapB, mapD;
+        {
+            int rcD = makeOutputMap(&mapD, outputMapType<OutT>(), sizeof(OutT), d, m, n, ldd);
+            if(rcD != B200WMMA_OK)
+                return rcD;
+        }
 
         if(pairEnabled() && m > BM && sms >= 2)
         {
@@ -955,7 +1144,7 @@ namespace
                 return rc;
             const uint32_t tiles = tilesM * ((n + bn - 1) / bn);
             const uint32_t pairs = tiles < pairsMax ? tiles : pairsMax;
-            kernel<<<2 * pairs, NUM_THREADS, P_SMEM_BYTES, stream>>>(mapA, mapB, p);
+            kernel<<<2 * pairs, NUM_THREADS, P_SMEM_BYTES, stream>>>(mapA, mapB, mapD, p);
             return b200wmma::cudaToStatus(cudaGetLastError());
         }
 
@@ -972,7 +1161,7 @@ namespace
             return rc;
         const uint32_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
         const uint32_t grid  = tiles < uint32_t(sms) ? tiles : uint32_t(sms);
-        kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(mapA, mapB, p);
+        kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(mapA, mapB, mapD, p);
         return b200wmma::cudaToStatus(cudaGetLastError());
     }
 
