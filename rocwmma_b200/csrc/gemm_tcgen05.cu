@@ -1104,25 +1104,29 @@ namespace
 
         if(pairEnabled() && m > BM && sms >= 2)
         {
-            // Tile width: the candidate that needs the least time by a simple model --
-            // waves of tiles over the pairs, each wave costing the tile width (plus a small
-            // fixed part).  8192^2 on one GPU keeps 256; the 2048- and 1024-row shards of a
-            // 4- or 8-GPU run come out at 224, which turns 3.46 resp. 1.73 waves into 4 resp. 2
-            // full ones of narrower tiles.
+            // Tile width: 256, 224 or 192 columns, whichever needs the least time by a simple
+            // model -- waves of tiles over the pairs, each wave costing the tile width plus a
+            // fixed part (A is loaded per tile whatever its width, so narrow tiles pay more
+            // L2 traffic per flop; measured: 128-wide tiles lose at 4096^3).  8192^2 and 4096^2
+            // keep 256; the 2048- and 1024-row shards of a 4- or 8-GPU run of 8192^3 come out
+            // at 224, which turns 3.46 resp. 1.73 waves into 4 resp. 2 full ones.
             const uint32_t pairsMax = uint32_t(sms / 2);
             const uint32_t tilesM   = (m + P_TILE_M - 1) / P_TILE_M;
             uint32_t       bn = BN, bestCost = 0xffffffffu;
-            for(uint32_t cand = 256; cand >= 128; cand -= 32)
+            for(uint32_t cand = 256; cand >= 192; cand -= 32)
             {
                 const uint32_t tiles = tilesM * ((n + cand - 1) / cand);
                 const uint32_t waves = (tiles + pairsMax - 1) / pairsMax;
-                const uint32_t cost  = waves * (cand + 8u);
+                const uint32_t cost  = waves * (cand + 64u);
                 if(cost < bestCost)
                 {
                     bestCost = cost;
                     bn       = cand;
                 }
             }
+            // problems narrower than a tile: no wider than needed (multiples of 32)
+            if(n < bn)
+                bn = n <= 128u ? 128u : (n + 31u) / 32u * 32u;
             // B200WMMA_GEMM_BN overrides the tile width (tuning only)
             static const uint32_t bnEnv = [] {
                 const char* e = getenv("B200WMMA_GEMM_BN");
