@@ -263,6 +263,23 @@ namespace rocwmma
             return d;
         }
 
+        // Descriptor for an MN-major operand tile (the M or N index is contiguous in memory:
+        // a column-major A or a row-major B) written by TMA with the 128-byte swizzle as
+        // blocks of [K rows][128 bytes of M/N]: 8 K rows form a 1024-byte group, consecutive
+        // groups follow each other, and `mnAtomStride` bytes separate the blocks that hold
+        // the next 128 bytes of M/N.  `addr` is the tile base plus the K groups already
+        // consumed.
+        ROCWMMA_DEVICE inline uint64_t smem_desc_mnmajor_sw128(uint32_t addr, uint32_t mnAtomStride)
+        {
+            uint64_t d = 0;
+            d |= uint64_t((addr & 0x3ffffu) >> 4);
+            d |= uint64_t((mnAtomStride >> 4) & 0x3fffu) << 16; // leading-dimension byte offset
+            d |= uint64_t(1024u >> 4) << 32; // stride between 8-row K groups
+            d |= uint64_t(1) << 46;
+            d |= uint64_t(2) << 61;
+            return d;
+        }
+
         enum class MmaKind : uint32_t
         {
             F16, // fp16 or bf16 inputs, fp32 accumulate
@@ -276,13 +293,14 @@ namespace rocwmma
         constexpr uint32_t FMT_U8 = 0, FMT_S8 = 1;
         constexpr uint32_t ACC_F16 = 0, ACC_F32 = 1, ACC_S32 = 2;
 
-        // 32-bit instruction descriptor: accumulator format, A/B formats, both
-        // operands K-major, tile M x N.
+        // 32-bit instruction descriptor: accumulator format, A/B formats, operand majors
+        // (0 = K-major, 1 = MN-major), tile M x N.
         ROCWMMA_HOST_DEVICE constexpr uint32_t
-            make_instr_desc(uint32_t accFmt, uint32_t aFmt, uint32_t bFmt, uint32_t m, uint32_t n)
+            make_instr_desc(uint32_t accFmt, uint32_t aFmt, uint32_t bFmt, uint32_t m, uint32_t n,
+                            uint32_t aMnMajor = 0, uint32_t bMnMajor = 0)
         {
-            return (accFmt << 4) | (aFmt << 7) | (bFmt << 10) | (0u << 15) | (0u << 16)
-                   | ((n >> 3) << 17) | ((m >> 4) << 24);
+            return (accFmt << 4) | (aFmt << 7) | (bFmt << 10) | (aMnMajor << 15)
+                   | (bMnMajor << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
         }
 
         // D[tmem] (+)= A[smem] * B[smem].  Issued by ONE thread.

@@ -94,10 +94,12 @@ B200WMMA_API int b200wmma_gemm_simple(int in_dtype, int out_dtype, uint32_t m, u
  * double-precision tensor path with a shared-memory pipeline.
  * Requirements: a, b, c, d 16-byte aligned; lda, ldb, ldc, ldd times the element
  * size multiples of 16 bytes.  Any m, n, k >= 1 (edge tiles are zero-filled on
- * load and masked on store).  A row-major with B column-major is the native
- * operand form; any other layout is first transposed into a per-device scratch
- * buffer that is allocated on first use and grown on demand, so such calls on
- * different streams of one device must not overlap.
+ * load and masked on store).  Every layout combination of A and B is read in
+ * place (row-major A / column-major B as K-major tensor-core operands,
+ * column-major A / row-major B as MN-major ones), except for 32- and 64-bit
+ * inputs (XF32, F64): those transpose column-major A / row-major B into a
+ * per-device scratch buffer first (allocated on first use, grown on demand; such
+ * calls on different streams of one device must not overlap).  The first call on a device allocates a few bytes of status memory.
  */
 B200WMMA_API int b200wmma_gemm(int in_dtype, int out_dtype, uint32_t m, uint32_t n, uint32_t k, const void* a,
                   const void* b, const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
@@ -124,10 +126,11 @@ B200WMMA_API int b200wmma_gemm_host(int in_dtype, int out_dtype, uint32_t m, uin
  * inference server or a training framework with a caching pool), where a cudaMalloc
  * issued behind its back can fail or push it over its budget; and code on a latency
  * budget, since cudaFree (and, depending on the driver, cudaMalloc) waits for the whole
- * device and so stalls every stream that is running.  b200wmma_gemm gets the scratch it needs for non-native
- * operand layouts (A column-major, B row-major are first transposed) from cudaMalloc on
- * first use; this variant keeps that scratch in a fixed array inside the library image
- * instead and calls neither cudaMalloc, cudaFree nor any other allocating routine.
+ * device and so stalls every stream that is running.  b200wmma_gemm calls cudaMalloc on
+ * its first use on a device (for the word its kernels report abandoned waits in); this
+ * variant calls neither cudaMalloc, cudaFree nor any other allocating routine.  It brings
+ * column-major A / row-major B into the K-major form with a transposition pass of its
+ * own, whose scratch is a fixed array inside the library image.
  *
  * Same arguments, same arithmetic and same results as b200wmma_gemm, for the same type
  * pairs except F64.  Differences:

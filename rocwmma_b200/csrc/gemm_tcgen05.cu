@@ -77,7 +77,56 @@ namespace
         uint32_t    bn; // tile width (columns of D per tile): 256, or less for the pair kernel
         uint32_t    band; // tile rows per raster band (tiles of a band share their rows of A in L2)
         uint32_t    tmaStore; // 1: D leaves through shared memory and TMA stores
+        uint32_t    aMN, bMN; // 1: operand is MN-major in memory (A column-major, B row-major)
     };
+
+    // One operand tile for one K block.  K-major: one TMA box of `rows` rows x 128 bytes of
+    // K.  MN-major: boxes of BK K-rows x 128 bytes of M/N, one per 128 bytes of the tile's
+    // M/N extent, stacked in shared memory.  Returns the bytes that will arrive.
+    template <typename InT, bool PAIR>
+    __device__ inline uint32_t loadOperandTile(uint8_t* dst, void const* tmap, uint64_t* bar,
+                                               uint32_t barClusterAddr, bool mnMajor,
+                                               uint32_t mnOrigin, uint32_t rows, uint32_t k0)
+    {
+        constexpr uint32_t BK = ROW_BYTES / sizeof(InT); // K elements per ring slot
+        constexpr uint32_t W  = ROW_BYTES / sizeof(InT); // M/N elements per 128 bytes
+        if(!mnMajor)
+        {
+            if constexpr(PAIR)
+                tma_load_2d_pair(dst, tmap, barClusterAddr, int32_t(k0), int32_t(mnOrigin));
+            else
+                tma_load_2d(dst, tmap, bar, int32_t(k0), int32_t(mnOrigin));
+            return rows * ROW_BYTES;
+        }
+        const uint32_t atoms = (rows + W - 1) / W;
+        for(uint32_t a = 0; a < atoms; ++a)
+        {
+            uint8_t* d = dst + a * (BK * ROW_BYTES);
+            if constexpr(PAIR)
+                tma_load_2d_pair(d, tmap, barClusterAddr, int32_t(mnOrigin + a * W), int32_t(k0));
+            else
+                tma_load_2d(d, tmap, bar, int32_t(mnOrigin + a * W), int32_t(k0));
+        }
+        return atoms * BK * ROW_BYTES;
+    }
+    template <typename InT>
+    __device__ inline uint32_t operandTileBytes(bool mnMajor, uint32_t rows)
+    {
+        constexpr uint32_t W  = ROW_BYTES / sizeof(InT); // M/N elements per 128 bytes
+        constexpr uint32_t BK = ROW_BYTES / sizeof(InT); // K rows per ring slot
+        return mnMajor ? ((rows + W - 1) / W) * BK * ROW_BYTES : rows * ROW_BYTES;
+    }
+    // Shared-memory descriptor of an operand tile at K step `ks` of its ring slot.
+    template <typename InT>
+    __device__ inline uint64_t operandDesc(uint32_t tileAddr, bool mnMajor, uint32_t ks)
+    {
+        constexpr uint32_t BK     = ROW_BYTES / sizeof(InT);
+        constexpr uint32_t UMMA_K = 32 / sizeof(InT);
+        if(!mnMajor)
+            return smem_desc_kmajor_sw128(tileAddr + ks * 32u);
+        return smem_desc_mnmajor_sw128(tileAddr + ks * (UMMA_K / 8u) * 1024u, BK * ROW_BYTES);
+    }
+
 
     template <typename T>
     struct KindOf;
@@ -490,8 +539,8 @@ namespace
     {
         constexpr uint32_t BK     = ROW_BYTES / sizeof(InT); // K elements per ring slot
         constexpr uint32_t UMMA_K = 32 / sizeof(InT); // K elements per tcgen05.mma
-        constexpr uint32_t IDESC
-            = make_instr_desc(KindOf<InT>::acc, KindOf<InT>::fmt, KindOf<InT>::fmt, BM, BN);
+        const uint32_t IDESC = make_instr_desc(KindOf<InT>::acc, KindOf<InT>::fmt,
+                                               KindOf<InT>::fmt, BM, BN, p.aMN, p.bMN);
 
         extern __shared__ uint8_t smemRaw[];
         const uint32_t            rawAddr = smem_addr(smemRaw);
@@ -560,11 +609,12 @@ namespace
                             break;
                         }
                         uint8_t* slot = tiles + s * STAGE_BYTES;
-                        mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
-                        tma_load_2d(slot, &tmapA, &ctl->full[s], int32_t(kb * BK),
-                                    int32_t(tm * BM));
-                        tma_load_2d(slot + A_BYTES, &tmapB, &ctl->full[s], int32_t(kb * BK),
-                                    int32_t(tn * BN));
+                        mbar_expect_tx(&ctl->full[s], operandTileBytes<InT>(p.aMN != 0u, BM)
+                                                          + operandTileBytes<InT>(p.bMN != 0u, BN));
+                        loadOperandTile<InT, false>(slot, &tmapA, &ctl->full[s], 0u, p.aMN != 0u,
+                                                    tm * BM, BM, kb * BK);
+                        loadOperandTile<InT, false>(slot + A_BYTES, &tmapB, &ctl->full[s], 0u,
+                                                    p.bMN != 0u, tn * BN, BN, kb * BK);
                     }
                 }
                 if(!ok)
@@ -623,8 +673,8 @@ namespace
 #pragma unroll
                             for(uint32_t ks = 0; ks < BK / UMMA_K; ++ks)
                             {
-                                const uint64_t da = smem_desc_kmajor_sw128(aAddr + ks * 32u);
-                                const uint64_t db = smem_desc_kmajor_sw128(bAddr + ks * 32u);
+                                const uint64_t da = operandDesc<InT>(aAddr, p.aMN != 0u, ks);
+                                const uint64_t db = operandDesc<InT>(bAddr, p.bMN != 0u, ks);
                                 mma_ss<KindOf<InT>::kind>(dTmem, da, db, IDESC,
                                                           (kb > kb0 || ks > 0u) ? 1u : 0u);
                             }
@@ -741,8 +791,10 @@ namespace
         // count divides evenly over the pairs; it is the N of the MMA instruction.
         const uint32_t bn    = p.bn;
         const uint32_t IDESC = make_instr_desc(KindOf<InT>::acc, KindOf<InT>::fmt,
-                                               KindOf<InT>::fmt, P_TILE_M, bn);
-        const uint32_t bHalfBytes = (bn / 2u) * ROW_BYTES; // this block's rows of the B tile
+                                               KindOf<InT>::fmt, P_TILE_M, bn, p.aMN, p.bMN);
+        // bytes per K block and block: its 128 rows of A and its half of the B tile
+        const uint32_t pairSlotBytes = operandTileBytes<InT>(p.aMN != 0u, 128u)
+                                       + operandTileBytes<InT>(p.bMN != 0u, bn / 2u);
 
         extern __shared__ uint8_t smemRaw[];
         const uint32_t            rawAddr = smem_addr(smemRaw);
@@ -818,11 +870,12 @@ namespace
                         }
                         uint8_t* slot = tiles + s * P_STAGE_BYTES;
                         if(rank == 0)
-                            mbar_expect_tx(&ctl->full[s], 2u * (P_A_BYTES + bHalfBytes)); // both blocks
+                            mbar_expect_tx(&ctl->full[s], 2u * pairSlotBytes); // both blocks
                         const uint32_t leaderFull = map_to_cta(smem_addr(&ctl->full[s]), 0);
-                        tma_load_2d_pair(slot, &tmapA, leaderFull, int32_t(kb * BK), rowA);
-                        tma_load_2d_pair(slot + P_A_BYTES, &tmapB, leaderFull, int32_t(kb * BK),
-                                         rowB);
+                        loadOperandTile<InT, true>(slot, &tmapA, nullptr, leaderFull, p.aMN != 0u,
+                                                   uint32_t(rowA), 128u, kb * BK);
+                        loadOperandTile<InT, true>(slot + P_A_BYTES, &tmapB, nullptr, leaderFull,
+                                                   p.bMN != 0u, uint32_t(rowB), bn / 2u, kb * BK);
                     }
                 }
             }
@@ -864,8 +917,8 @@ namespace
 #pragma unroll
                             for(uint32_t ks = 0; ks < BK / UMMA_K; ++ks)
                             {
-                                const uint64_t da = smem_desc_kmajor_sw128(aAddr + ks * 32u);
-                                const uint64_t db = smem_desc_kmajor_sw128(bAddr + ks * 32u);
+                                const uint64_t da = operandDesc<InT>(aAddr, p.aMN != 0u, ks);
+                                const uint64_t db = operandDesc<InT>(bAddr, p.bMN != 0u, ks);
                                 mma_ss_pair<KindOf<InT>::kind>(dTmem, da, db, IDESC,
                                                                (kb > kb0 || ks > 0u) ? 1u : 0u);
                             }
@@ -1009,6 +1062,24 @@ namespace
         return r == CUDA_SUCCESS ? B200WMMA_OK : B200WMMA_ERR_CUDA;
     }
 
+    // Tensor map of an MN-major operand (column-major A or row-major B): `k` rows of `mn`
+    // contiguous elements, `ld` apart; box = 128 bytes of M/N x one ring slot of K rows.
+    int makeOperandMapMN(CUtensorMap* map, CUtensorMapDataType dt, size_t elemBytes,
+                         void const* base, uint32_t mn, uint32_t k, uint32_t ld)
+    {
+        EncodeFn fn = encoder();
+        if(!fn)
+            return B200WMMA_ERR_CUDA;
+        cuuint64_t dims[2]    = {mn, k};
+        cuuint64_t strides[1] = {cuuint64_t(ld) * elemBytes};
+        cuuint32_t box[2]     = {cuuint32_t(ROW_BYTES / elemBytes), cuuint32_t(ROW_BYTES / elemBytes)};
+        cuuint32_t estr[2]    = {1, 1};
+        CUresult   r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS ? B200WMMA_OK : B200WMMA_ERR_CUDA;
+    }
+
     // The pair kernel is the default whenever a 256-row tile makes sense; the environment
     // variable B200WMMA_GEMM_PAIR=0 selects the single-block kernel (for comparison).
     bool pairEnabled()
@@ -1043,7 +1114,8 @@ namespace
     int launchWithStatus(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k,
                          void const* a, void const* b, void const* c, void* d, uint32_t lda,
                          uint32_t ldb, uint32_t ldc, uint32_t ldd, double alpha, double beta,
-                         cudaStream_t stream, uint32_t* status)
+                         cudaStream_t stream, uint32_t* status, bool aMN = false,
+                         bool bMN = false)
     {
         const int sms = b200wmma::smCount();
         if(sms <= 0)
@@ -1094,7 +1166,8 @@ namespace
             useTma = true;
         useTma = useTma && tmaSafe;
         GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
-                     status, chunkKB, wide, BN, bandEnv ? bandEnv : GROUP_M, useTma ? 1u : 0u};
+                     status, chunkKB, wide, BN, bandEnv ? bandEnv : GROUP_M, useTma ? 1u : 0u,
+                     aMN ? 1u : 0u,      bMN ? 1u : 0u};
         CUtensorMap mapA, mapB, mapD;
         {
             int rcD = makeOutputMap(&mapD, outputMapType<OutT>(), sizeof(OutT), d, m, n, ldd);
@@ -1135,10 +1208,12 @@ namespace
             if(bnEnv >= 128 && bnEnv <= 256 && bnEnv % 32 == 0)
                 bn = bnEnv;
             p.bn   = bn;
-            int rc = makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, 128);
+            int rc = aMN ? makeOperandMapMN(&mapA, dt, sizeof(InT), a, m, k, lda)
+                         : makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, 128);
             if(rc != B200WMMA_OK)
                 return rc;
-            rc = makeOperandMap(&mapB, dt, sizeof(InT), b, n, k, ldb, bn / 2);
+            rc = bMN ? makeOperandMapMN(&mapB, dt, sizeof(InT), b, n, k, ldb)
+                     : makeOperandMap(&mapB, dt, sizeof(InT), b, n, k, ldb, bn / 2);
             if(rc != B200WMMA_OK)
                 return rc;
             auto        kernel = gemm_tcgen05_pair_kernel<InT, OutT, CompT>;
@@ -1152,10 +1227,12 @@ namespace
             return b200wmma::cudaToStatus(cudaGetLastError());
         }
 
-        int rc = makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, BM);
+        int rc = aMN ? makeOperandMapMN(&mapA, dt, sizeof(InT), a, m, k, lda)
+                     : makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, BM);
         if(rc != B200WMMA_OK)
             return rc;
-        rc = makeOperandMap(&mapB, dt, sizeof(InT), b, n, k, ldb, BN);
+        rc = bMN ? makeOperandMapMN(&mapB, dt, sizeof(InT), b, n, k, ldb)
+                 : makeOperandMap(&mapB, dt, sizeof(InT), b, n, k, ldb, BN);
         if(rc != B200WMMA_OK)
             return rc;
         auto        kernel = gemm_tcgen05_kernel<InT, OutT, CompT>;
@@ -1172,11 +1249,11 @@ namespace
     template <typename InT, typename OutT, typename CompT>
     int launch(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k, void const* a,
                void const* b, void const* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
-               uint32_t ldd, double alpha, double beta, cudaStream_t stream)
+               uint32_t ldd, double alpha, double beta, cudaStream_t stream, bool aMN, bool bMN)
     {
         return launchWithStatus<InT, OutT, CompT>(dt, m, n, k, a, b, c, d, lda, ldb, ldc, ldd,
                                                   alpha, beta, stream,
-                                                  b200wmma::deviceStatusWord());
+                                                  b200wmma::deviceStatusWord(), aMN, bMN);
     }
 
     // out[c][r] = in[r][c]: turns an MN-major operand into the K-major form the
@@ -1217,42 +1294,57 @@ namespace
         return (v + m - 1) / m * m;
     }
 
+    // Every layout combination is read in place: a row-major A / column-major B tile is
+    // K-major for the tensor core, a column-major A / row-major B tile MN-major; the TMA box
+    // shape and the shared-memory and instruction descriptors follow the layout.
     template <typename InT, typename OutT, typename CompT>
     int run(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k, void const* a,
             void const* b, void const* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
             uint32_t ldd, double alpha, double beta, int layoutA, int layoutB, cudaStream_t stream)
     {
-        constexpr uint32_t E16 = 16 / sizeof(InT); // elements per 16 bytes
-        // A column-major / B row-major: bring them to K-major in scratch first.
-        if(layoutA == B200WMMA_COL_MAJOR || layoutB == B200WMMA_ROW_MAJOR)
+        bool aMN = layoutA == B200WMMA_COL_MAJOR;
+        bool bMN = layoutB == B200WMMA_ROW_MAJOR;
+        if constexpr(sizeof(InT) == 4)
         {
-            const uint32_t kPad   = roundUp(k, E16);
-            const size_t   aBytes = layoutA == B200WMMA_COL_MAJOR ? size_t(m) * kPad * sizeof(InT) : 0;
-            const size_t   bBytes = layoutB == B200WMMA_ROW_MAJOR ? size_t(n) * kPad * sizeof(InT) : 0;
-            const size_t   aPad   = (aBytes + 255) / 256 * 256;
-            uint8_t* scratch = static_cast<uint8_t*>(b200wmma::deviceScratch(aPad + bBytes));
-            if(!scratch)
-                return B200WMMA_ERR_CUDA;
-            if(layoutA == B200WMMA_COL_MAJOR)
+            // 32-bit (tf32) operands are fed K-major only: with the MN-major descriptors that
+            // work for 8- and 16-bit types the tensor core returned zeros for kind::tf32
+            // (it wants a different swizzle atom for 32-bit transposes).  Column-major A /
+            // row-major B are therefore transposed into a per-device scratch buffer first.
+            if(aMN || bMN)
             {
-                // stored as k rows of m (ld = lda); wanted: m rows of k
-                int rc = transposeInto(static_cast<InT const*>(a),
-                                       reinterpret_cast<InT*>(scratch), k, m, lda, kPad, stream);
-                if(rc != B200WMMA_OK)
-                    return rc;
-                a   = scratch;
-                lda = kPad;
-            }
-            if(layoutB == B200WMMA_ROW_MAJOR)
-            {
-                // stored as k rows of n (ld = ldb); wanted: n rows of k
-                int rc = transposeInto(static_cast<InT const*>(b),
-                                       reinterpret_cast<InT*>(scratch + aPad), k, n, ldb, kPad,
-                                       stream);
-                if(rc != B200WMMA_OK)
-                    return rc;
-                b   = scratch + aPad;
-                ldb = kPad;
+                constexpr uint32_t E16    = 16 / sizeof(InT);
+                const uint32_t     kPad   = roundUp(k, E16);
+                const size_t       aBytes = aMN ? size_t(m) * kPad * sizeof(InT) : 0;
+                const size_t       bBytes = bMN ? size_t(n) * kPad * sizeof(InT) : 0;
+                const size_t       aPad   = (aBytes + 255) / 256 * 256;
+                uint8_t* scratch = static_cast<uint8_t*>(b200wmma::deviceScratch(aPad + bBytes));
+                if(!scratch)
+                    return B200WMMA_ERR_CUDA;
+                if(aMN)
+                {
+                    if(lda < m)
+                        return B200WMMA_ERR_INVALID_ARG;
+                    int rc = transposeInto(static_cast<InT const*>(a),
+                                           reinterpret_cast<InT*>(scratch), k, m, lda, kPad, stream);
+                    if(rc != B200WMMA_OK)
+                        return rc;
+                    a   = scratch;
+                    lda = kPad;
+                    aMN = false;
+                }
+                if(bMN)
+                {
+                    if(ldb < n)
+                        return B200WMMA_ERR_INVALID_ARG;
+                    int rc = transposeInto(static_cast<InT const*>(b),
+                                           reinterpret_cast<InT*>(scratch + aPad), k, n, ldb, kPad,
+                                           stream);
+                    if(rc != B200WMMA_OK)
+                        return rc;
+                    b   = scratch + aPad;
+                    ldb = kPad;
+                    bMN = false;
+                }
             }
         }
         auto misaligned = [](void const* ptr, uint32_t ld, size_t elem) {
@@ -1261,10 +1353,10 @@ namespace
         if(misaligned(a, lda, sizeof(InT)) || misaligned(b, ldb, sizeof(InT))
            || misaligned(d, ldd, sizeof(OutT)) || (beta != 0.0 && misaligned(c, ldc, sizeof(OutT))))
             return B200WMMA_ERR_ALIGNMENT;
-        if(lda < k || ldb < k || ldd < n || (beta != 0.0 && ldc < n))
+        if(lda < (aMN ? m : k) || ldb < (bMN ? n : k) || ldd < n || (beta != 0.0 && ldc < n))
             return B200WMMA_ERR_INVALID_ARG;
         return launch<InT, OutT, CompT>(dt, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
-                                        stream);
+                                        stream, aMN, bMN);
     }
 } // namespace
 

@@ -86,15 +86,18 @@ def test_block_gemm_ragged_edges(in_t, out_t, m, n, k):
     assert 0 <= err <= tolerance(in_t, out_t), err
 
 
-@pytest.mark.parametrize("in_t,out_t", [(O.F16, O.F16), (O.I8, O.I32), (O.XF32, O.F32),
-                                        (O.F64, O.F64)])
+@pytest.mark.parametrize("in_t,out_t", BLOCK_PAIRS)
 @pytest.mark.parametrize("la,lb", [(COL, ROW), (ROW, ROW), (COL, COL)])
-def test_block_gemm_other_layouts(in_t, out_t, la, lb):
+@pytest.mark.parametrize("m,n,k", [(256, 256, 192), (300, 520, 264), (1024, 2048, 160),
+                                   (100, 72, 40)])
+def test_block_gemm_other_layouts(in_t, out_t, la, lb, m, n, k):
+    """Column-major A and row-major B are read in place as MN-major tensor-core operands
+    (the layout of the reference's perf samples, samples/perf_hgemm.cpp:268-271)."""
     al, be = _ab(in_t)
-    case = dict(in_t=in_t, out_t=out_t, m=256, n=256, k=192, la=la, lb=lb, alpha=al, beta=be,
+    case = dict(in_t=in_t, out_t=out_t, m=m, n=n, k=k, la=la, lb=lb, alpha=al, beta=be,
                 seed=60 + in_t)
     got, want = _run(case)
-    assert 0 <= O.max_rel_err(out_t, got, want) <= TOLERANCE[in_t]
+    assert 0 <= O.max_rel_err(out_t, got, want) <= tolerance(in_t, out_t)
 
 
 def test_beta_zero_never_reads_c():
