@@ -5,8 +5,34 @@
 #ifndef ROCWMMA_B200_CONFIG_HPP
 #define ROCWMMA_B200_CONFIG_HPP
 
+// Under run-time compilation (NVRTC defines __CUDACC_RTC__) no host headers exist: the
+// fixed-width integers and the type traits come from libcu++ instead, which ships with the
+// toolkit and works in both modes.  rocWMMA makes the same promise for hipRTC
+// (docs/conceptual/programmers-guide.rst:28-34).
+#if defined(__CUDACC_RTC__)
+#include <cuda/std/cstdint>
+#include <cuda/std/type_traits>
+using cuda::std::int16_t;
+using cuda::std::int32_t;
+using cuda::std::int64_t;
+using cuda::std::int8_t;
+using cuda::std::uint16_t;
+using cuda::std::uint32_t;
+using cuda::std::uint64_t;
+using cuda::std::uint8_t;
+using cuda::std::uintptr_t;
+namespace rocwmma
+{
+    namespace stdx = ::cuda::std;
+}
+#else
 #include <cstdint>
 #include <cuda_runtime.h>
+namespace rocwmma
+{
+    namespace stdx = ::std;
+}
+#endif
 
 #define ROCWMMA_DEVICE __device__
 #define ROCWMMA_HOST __host__

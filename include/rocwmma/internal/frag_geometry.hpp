@@ -27,7 +27,6 @@
 #include "constants.hpp"
 #include "coord.hpp"
 #include "types.hpp"
-#include <type_traits>
 
 namespace rocwmma
 {
@@ -72,9 +71,9 @@ namespace rocwmma
                   typename DataT>
         struct FragGeom
         {
-            static constexpr bool IsA   = std::is_same<MatrixT, matrix_a>::value;
-            static constexpr bool IsB   = std::is_same<MatrixT, matrix_b>::value;
-            static constexpr bool IsAcc = std::is_same<MatrixT, accumulator>::value;
+            static constexpr bool IsA   = stdx::is_same<MatrixT, matrix_a>::value;
+            static constexpr bool IsB   = stdx::is_same<MatrixT, matrix_b>::value;
+            static constexpr bool IsAcc = stdx::is_same<MatrixT, accumulator>::value;
             static_assert(IsA || IsB || IsAcc, "MatrixT must be matrix_a, matrix_b or accumulator");
 
             static constexpr uint32_t KA = kAtom<DataT, BlockK>();

@@ -27,7 +27,7 @@ namespace rocwmma
         template <typename Geom, typename DataLayoutT>
         struct UnitIO
         {
-            static constexpr bool RowMajor   = std::is_same<DataLayoutT, row_major>::value;
+            static constexpr bool RowMajor   = stdx::is_same<DataLayoutT, row_major>::value;
             static constexpr bool Contiguous = (Geom::UnitAlongCols == RowMajor);
             static constexpr uint32_t US     = Geom::UnitSize;
 

@@ -119,7 +119,7 @@ namespace rocwmma
                          const DataT*                                                   data,
                          uint32_t                                                       ldm)
     {
-        static_assert(!std::is_same<DataLayoutT, void>::value,
+        static_assert(!stdx::is_same<DataLayoutT, void>::value,
                       "Must provide layout information. Either statically assign data layout in "
                       "fragment declaration or use the run-time function overload.");
         using Geom = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>::Geom;
@@ -152,7 +152,7 @@ namespace rocwmma
                           fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT> const& frag,
                           uint32_t                                                             ldm)
     {
-        static_assert(!std::is_same<DataLayoutT, void>::value,
+        static_assert(!stdx::is_same<DataLayoutT, void>::value,
                       "Must provide data layout. Either statically assign data layout in "
                       "fragment declaration or use the run-time function overload.");
         using Geom = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>::Geom;
@@ -190,7 +190,7 @@ namespace rocwmma
             const __nv_fp8x2_storage_t two
                 = __nv_fp8x2_storage_t(hiPair ? (packed >> 16) : (packed & 0xffffu));
             const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(
-                two, std::is_same<Fp8T, __nv_fp8_e4m3>::value ? __NV_E4M3 : __NV_E5M2);
+                two, stdx::is_same<Fp8T, __nv_fp8_e4m3>::value ? __NV_E4M3 : __NV_E5M2);
             return uint32_t(h.x) | (uint32_t(h.y) << 16);
         }
     } // namespace detail
@@ -211,7 +211,7 @@ namespace rocwmma
                  fragment<matrix_b, BlockM, BlockN, BlockK, InputTB, LayoutB> const&     b,
                  fragment<accumulator, BlockM, BlockN, BlockK, ComputeT, LayoutC> const& c)
     {
-        static_assert(std::is_same<InputTA, InputTB>::value,
+        static_assert(stdx::is_same<InputTA, InputTB>::value,
                       "A and B fragments must hold the same data type");
         using InT   = InputTA;
         using GeomA = detail::FragGeom<matrix_a, BlockM, BlockN, BlockK, InT>;
@@ -223,14 +223,14 @@ namespace rocwmma
         constexpr uint32_t RA = GeomA::UnitsPerAtom; // 32-bit (or 64-bit) registers per A atom
         constexpr uint32_t RB = GeomB::UnitsPerAtom;
 
-        constexpr bool Is16   = std::is_same<InT, float16_t>::value
-                              || std::is_same<InT, bfloat16_t>::value;
-        constexpr bool IsFp8  = std::is_same<InT, float8_t>::value
-                               || std::is_same<InT, bfloat8_t>::value;
-        constexpr bool IsI8   = std::is_same<InT, int8_t>::value;
-        constexpr bool IsF32  = std::is_same<InT, float32_t>::value;
-        constexpr bool IsXF32 = std::is_same<InT, xfloat32_t>::value;
-        constexpr bool IsF64  = std::is_same<InT, float64_t>::value;
+        constexpr bool Is16   = stdx::is_same<InT, float16_t>::value
+                              || stdx::is_same<InT, bfloat16_t>::value;
+        constexpr bool IsFp8  = stdx::is_same<InT, float8_t>::value
+                               || stdx::is_same<InT, bfloat8_t>::value;
+        constexpr bool IsI8   = stdx::is_same<InT, int8_t>::value;
+        constexpr bool IsF32  = stdx::is_same<InT, float32_t>::value;
+        constexpr bool IsXF32 = stdx::is_same<InT, xfloat32_t>::value;
+        constexpr bool IsF64  = stdx::is_same<InT, float64_t>::value;
         static_assert(Is16 || IsFp8 || IsI8 || IsF32 || IsXF32 || IsF64,
                       "unsupported input type for mma_sync");
 
@@ -244,7 +244,7 @@ namespace rocwmma
 
                 if constexpr(IsF64)
                 {
-                    static_assert(std::is_same<ComputeT, float64_t>::value,
+                    static_assert(stdx::is_same<ComputeT, float64_t>::value,
                                   "float64_t inputs accumulate in float64_t");
                     double acc[4] = {c.x[ci], c.x[ci + 1], c.x[ci + 2], c.x[ci + 3]};
                     ROCWMMA_UNROLL
@@ -262,7 +262,7 @@ namespace rocwmma
                 }
                 else if constexpr(IsI8)
                 {
-                    static_assert(std::is_same<ComputeT, int32_t>::value,
+                    static_assert(stdx::is_same<ComputeT, int32_t>::value,
                                   "int8_t inputs accumulate in int32_t");
                     int32_t acc[4] = {c.x[ci], c.x[ci + 1], c.x[ci + 2], c.x[ci + 3]};
                     ROCWMMA_UNROLL
@@ -288,8 +288,8 @@ namespace rocwmma
                     for(uint32_t e = 0; e < 4; ++e)
                         d.x[ci + e] = acc[e];
                 }
-                else if constexpr(Is16 && std::is_same<ComputeT, float16_t>::value
-                                  && std::is_same<InT, float16_t>::value)
+                else if constexpr(Is16 && stdx::is_same<ComputeT, float16_t>::value
+                                  && stdx::is_same<InT, float16_t>::value)
                 {
                     // 16-bit accumulation requested: the tensor core accumulates in fp16.
                     uint32_t acc[2] = {c.mStorage[ci / 2u], c.mStorage[ci / 2u + 1u]};

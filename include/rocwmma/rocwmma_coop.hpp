@@ -33,7 +33,7 @@ namespace rocwmma
                               uint32_t waveIndex,
                               uint32_t waveCount)
     {
-        static_assert(!std::is_same<DataLayoutT, void>::value,
+        static_assert(!stdx::is_same<DataLayoutT, void>::value,
                       "Must provide layout information. Either statically assign data layout in "
                       "fragment declaration or use the run-time function overload.");
         using Geom = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>::Geom;
@@ -98,7 +98,7 @@ namespace rocwmma
         uint32_t                                                             waveIndex,
         uint32_t                                                             waveCount)
     {
-        static_assert(!std::is_same<DataLayoutT, void>::value,
+        static_assert(!stdx::is_same<DataLayoutT, void>::value,
                       "Must provide data layout. Either statically assign data layout in "
                       "fragment declaration or use the run-time function overload.");
         using Geom = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>::Geom;

@@ -138,29 +138,29 @@ namespace rocwmma
     } // namespace detail
 
     template <typename FragT>
-    using ApplyTranspose_t = typename detail::ApplyTranspose<std::decay_t<FragT>>::Type;
+    using ApplyTranspose_t = typename detail::ApplyTranspose<stdx::decay_t<FragT>>::Type;
 
     template <typename FragT, typename NewDataLayoutT>
     using ApplyDataLayout_t =
-        typename detail::ApplyDataLayout<std::decay_t<FragT>, NewDataLayoutT>::Type;
+        typename detail::ApplyDataLayout<stdx::decay_t<FragT>, NewDataLayoutT>::Type;
 
     template <typename FragT>
     ROCWMMA_DEVICE static inline decltype(auto) applyTranspose(FragT&& frag)
     {
-        return detail::ApplyTranspose<std::decay_t<FragT>>::exec(frag);
+        return detail::ApplyTranspose<stdx::decay_t<FragT>>::exec(frag);
     }
 
     template <typename DataLayoutT, uint32_t WaveCount = 1, typename FragT>
     ROCWMMA_DEVICE static inline decltype(auto) applyDataLayout(FragT&& frag)
     {
-        return detail::ApplyDataLayout<std::decay_t<FragT>, DataLayoutT>::exec(frag);
+        return detail::ApplyDataLayout<stdx::decay_t<FragT>, DataLayoutT>::exec(frag);
     }
 
     // Fragment property accessors used by kernels (rocWMMA internal/accessors.hpp:33-91).
     template <typename FragT>
     struct GetIOShape
     {
-        using F = std::decay_t<FragT>;
+        using F = stdx::decay_t<FragT>;
         static constexpr uint32_t BlockHeight = F::height();
         static constexpr uint32_t BlockWidth  = F::width();
         static constexpr uint32_t BlockDim    = F::blockDim();
@@ -170,7 +170,7 @@ namespace rocwmma
     using GetIOShape_t = GetIOShape<FragT>;
 
     template <typename FragT>
-    using GetDataType_t = typename std::decay_t<FragT>::element_type;
+    using GetDataType_t = typename stdx::decay_t<FragT>::element_type;
 } // namespace rocwmma
 
 #endif // ROCWMMA_B200_TRANSFORMS_API_HPP
