@@ -82,6 +82,7 @@ namespace
         uint32_t rowStride; // bytes per staged sample row: 2k + 16
         uint32_t stageBytes; // m * rowStride
         uint32_t numGroups; // ceil(batch / 8)
+        uint32_t chunks; // 16-byte pieces in a sample: m * k / 8
     };
 
     // Work distribution: groups of 8 samples are handed out through one global counter, so
@@ -130,18 +131,42 @@ namespace
         }
     };
 
-    // Copies one sample (m rows of k halves, contiguous in global memory) into a ring slot.
-    __device__ inline void issueSample(uint32_t slotAddr, __half const* sample, Shape const& sh,
-                                       uint32_t lane)
+    // Bytes of the backward pass's triangle table: 4 per entry, rounded up to 16.
+    __host__ __device__ inline uint32_t triTableBytes(uint32_t m)
     {
-        const uint32_t chunksPerRow = sh.k / 8;
-        const uint32_t total        = sh.m * chunksPerRow;
-        for(uint32_t c = lane; c < total; c += 32)
+        return (m * (m - 1) / 2 * 4 + 15) / 16 * 16;
+    }
+
+    // A sample is m rows of k halves, contiguous in global memory; in a ring slot its rows
+    // are rowStride bytes apart.  ChunkMap gives the slot offset of the sample's c-th
+    // 16-byte piece without a division: c / chunksPerRow == (c * magic) >> 16 for every
+    // c < 2048 and chunksPerRow <= 32 (magic = ceil(65536 / chunksPerRow)), and a sample
+    // has at most 32 * 256 / 8 = 1024 pieces.
+    struct ChunkMap
+    {
+        uint32_t chunksPerRow, magic, rowStride, total;
+
+        __device__ inline void init(Shape const& sh)
         {
-            const uint32_t row = c / chunksPerRow, cc = c % chunksPerRow;
-            cpAsync16(slotAddr + row * sh.rowStride + cc * 16,
-                      reinterpret_cast<uint8_t const*>(sample) + size_t(c) * 16);
+            chunksPerRow = sh.k / 8;
+            magic        = (65536u + chunksPerRow - 1u) / chunksPerRow;
+            rowStride    = sh.rowStride;
+            total        = sh.chunks;
         }
+        __device__ inline uint32_t offset(uint32_t c) const
+        {
+            const uint32_t row = (c * magic) >> 16;
+            return row * rowStride + (c - row * chunksPerRow) * 16u;
+        }
+    };
+
+    // Copies one sample into a ring slot.
+    __device__ inline void issueSample(uint32_t slotAddr, __half const* sample,
+                                       ChunkMap const& map, uint32_t lane)
+    {
+        uint8_t const* src = reinterpret_cast<uint8_t const*>(sample);
+        for(uint32_t c = lane; c < map.total; c += 32)
+            cpAsync16(slotAddr + map.offset(c), src + size_t(c) * 16);
     }
 
     // =====================================================================================
@@ -172,6 +197,30 @@ namespace
         const bool twoM = sh.m > 16;
         GroupFeed  feed;
         feed.init(counter, sh.numGroups, lane);
+        ChunkMap map;
+        map.init(sh);
+
+        // Where this lane's accumulator elements go in a packed output row.  Element pair h
+        // of block i sits at row r = 16 mt + g + 8 h, columns c and c + 1 (c = 8 nt + 2 t);
+        // only c < r < m is part of the strict lower triangle.  Bits 0-15: index of (r, c)
+        // in the row, bit 16 / 17: (r, c) / (r, c + 1) is stored.
+        uint32_t triSlot[6][2];
+#pragma unroll
+        for(uint32_t i = 0; i < 6; ++i)
+#pragma unroll
+            for(uint32_t h = 0; h < 2; ++h)
+            {
+                const uint32_t mt = i < 2 ? 0u : 1u;
+                const uint32_t nt = i < 2 ? i : i - 2u;
+                const uint32_t r  = mt * 16u + g + 8u * h;
+                const uint32_t c  = nt * 8u + 2u * t;
+                uint32_t       v  = sh.k + r * (r - 1u) / 2u + c;
+                if(r < sh.m && c < r)
+                    v |= 1u << 16;
+                if(r < sh.m && c + 1u < r)
+                    v |= 1u << 17;
+                triSlot[i][h] = v;
+            }
 
         // prologue
 #pragma unroll
@@ -179,7 +228,8 @@ namespace
         {
             const uint32_t s = feed.sample(q);
             if(s < sh.batch)
-                issueSample(ringAddr + q * sh.stageBytes, input + size_t(s) * sh.m * sh.k, sh, lane);
+                issueSample(ringAddr + q * sh.stageBytes, input + size_t(s) * sh.m * sh.k,
+                            map, lane);
             cpAsyncCommit();
         }
 
@@ -201,7 +251,7 @@ namespace
                 const uint32_t s  = feed.sample(qn);
                 if(s < sh.batch)
                     issueSample(ringAddr + (qn % NSTAGES) * sh.stageBytes,
-                                input + size_t(s) * sh.m * sh.k, sh, lane);
+                                input + size_t(s) * sh.m * sh.k, map, lane);
                 cpAsyncCommit();
             }
 
@@ -245,18 +295,15 @@ namespace
                     dst[j] = row0p[j];
 #pragma unroll
                 for(uint32_t i = 0; i < 6; ++i)
-                {
-                    const uint32_t mt = i < 2 ? 0u : 1u;
-                    const uint32_t nt = i < 2 ? i : i - 2u;
 #pragma unroll
-                    for(uint32_t e = 0; e < 4; ++e)
+                    for(uint32_t h = 0; h < 2; ++h)
                     {
-                        const uint32_t r = mt * 16u + g + 8u * (e >> 1);
-                        const uint32_t c = nt * 8u + 2u * t + (e & 1u);
-                        if(c < r && r < sh.m)
-                            dst[sh.k + r * (r - 1u) / 2u + c] = __float2half_rn(acc[i][e]);
+                        const uint32_t v = triSlot[i][h], idx = v & 0xffffu;
+                        if(v & (1u << 16))
+                            dst[idx] = __float2half_rn(acc[i][2 * h]);
+                        if(v & (1u << 17))
+                            dst[idx + 1] = __float2half_rn(acc[i][2 * h + 1]);
                     }
-                }
             }
 
             // end of a group: flush its packed rows with 128-bit stores
@@ -296,13 +343,13 @@ namespace
         const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
         const uint32_t g = lane >> 2, t = lane & 3;
 
-        // layout: [zero row][triangle index table][warp 0: ring, G][warp 1: ...]
+        // layout: [zero row][triangle table][warp 0: ring, G][warp 1: ...]
         const uint32_t triCount   = sh.m * (sh.m - 1) / 2;
-        const uint32_t triBytes   = (triCount * 2 + 15) / 16 * 16;
+        const uint32_t triBytes   = triTableBytes(sh.m);
         const uint32_t gBytes     = 32 * G_LD * 2;
         const uint32_t perWarp    = NSTAGES * sh.stageBytes + gBytes;
         uint8_t*       zeroRow    = smem;
-        uint16_t*      tri        = reinterpret_cast<uint16_t*>(smem + ZERO_BYTES);
+        uint32_t*      tri        = reinterpret_cast<uint32_t*>(smem + ZERO_BYTES);
         uint8_t*       mine       = smem + ZERO_BYTES + triBytes + warp * perWarp;
         __half*        gTile      = reinterpret_cast<__half*>(mine + NSTAGES * sh.stageBytes);
         const uint32_t ringAddr   = smemAddr(mine);
@@ -311,10 +358,11 @@ namespace
 
         for(uint32_t i = threadIdx.x; i < ZERO_BYTES / 4; i += blockDim.x)
             reinterpret_cast<uint32_t*>(zeroRow)[i] = 0u;
-        // (r, c) of packed triangle entry idx, row-major over r, c < r
+        // Packed triangle entry idx is G(r, c), c < r, row-major over r: its two places in
+        // the G tile, (r, c) in the low and (c, r) in the high 16 bits.
         for(uint32_t r = threadIdx.x; r < sh.m; r += blockDim.x)
             for(uint32_t c = 0; c < r; ++c)
-                tri[r * (r - 1) / 2 + c] = uint16_t((r << 8) | c);
+                tri[r * (r - 1) / 2 + c] = (r * G_LD + c) | ((c * G_LD + r) << 16);
         for(uint32_t i = lane; i < 32 * G_LD / 2; i += 32)
             reinterpret_cast<uint32_t*>(gTile)[i] = 0u; // diagonal and padding stay zero
         __syncthreads();
@@ -322,12 +370,14 @@ namespace
         const bool twoM = sh.m > 16;
         GroupFeed  feed;
         feed.init(counter, sh.numGroups, lane);
+        ChunkMap map;
+        map.init(sh);
 
         auto issue = [&](uint32_t q) {
             const uint32_t s = feed.sample(q);
             if(s < sh.batch)
                 issueSample(ringAddr + (q % NSTAGES) * sh.stageBytes,
-                            input + size_t(s) * sh.m * sh.k, sh, lane);
+                            input + size_t(s) * sh.m * sh.k, map, lane);
         };
 
         // The packed upstream row of a sample is only 2-byte aligned, and each value is used
@@ -401,9 +451,9 @@ namespace
                 const uint32_t idx = i * 32u + lane;
                 if(idx < triCount)
                 {
-                    const uint32_t rc = tri[idx], r = rc >> 8, c = rc & 0xffu;
-                    gTile[r * G_LD + c] = triCur[i];
-                    gTile[c * G_LD + r] = triCur[i];
+                    const uint32_t at = tri[idx];
+                    gTile[at & 0xffffu] = triCur[i];
+                    gTile[at >> 16]     = triCur[i];
                 }
             }
             __syncwarp();
@@ -490,13 +540,9 @@ namespace
 
             // rows of the result leave with 128-bit stores (the sample is contiguous in grad)
             {
-                const uint32_t chunksPerRow = sh.k / 8, total = sh.m * chunksPerRow;
-                uint4*         gdst = reinterpret_cast<uint4*>(grad + size_t(sample) * sh.m * sh.k);
-                for(uint32_t c = lane; c < total; c += 32)
-                {
-                    const uint32_t row = c / chunksPerRow, cc = c % chunksPerRow;
-                    gdst[c] = *reinterpret_cast<uint4 const*>(slotPtr + row * sh.rowStride + cc * 16);
-                }
+                uint4* gdst = reinterpret_cast<uint4*>(grad + size_t(sample) * sh.m * sh.k);
+                for(uint32_t c = lane; c < map.total; c += 32)
+                    gdst[c] = *reinterpret_cast<uint4 const*>(slotPtr + map.offset(c));
             }
             __syncwarp();
         }
@@ -519,6 +565,7 @@ namespace
         sh->rowStride  = 2 * k + 16;
         sh->stageBytes = m * sh->rowStride;
         sh->numGroups  = (batch + GROUP - 1) / GROUP;
+        sh->chunks     = m * k / 8;
         return B200WMMA_OK;
     }
 
@@ -628,8 +675,7 @@ extern "C" int b200wmma_dlrm_bwd(int dtype, const void* input, const void* upstr
         return B200WMMA_ERR_INVALID_ARG;
     if(!aligned16(input) || !aligned16(upstream) || !aligned16(grad) || !aligned16(mlp_grad))
         return B200WMMA_ERR_ALIGNMENT;
-    const uint32_t triBytes = (m * (m - 1) / 2 * 2 + 15) / 16 * 16;
-    const Plan     plan     = choosePlan(ZERO_BYTES + triBytes, sh.stageBytes, 32 * G_LD * 2);
+    const Plan plan = choosePlan(ZERO_BYTES + triTableBytes(m), sh.stageBytes, 32 * G_LD * 2);
     if(plan.warps == 0)
         return B200WMMA_ERR_UNSUPPORTED;
     const int sms = b200wmma::smCount();
