@@ -155,6 +155,35 @@ namespace rocwmma
                          : "memory");
         }
 
+        // ---- untiled bulk copies (cp.async.bulk): contiguous bytes, no tensor map ----------
+        // Both addresses 16-byte aligned, `bytes` a multiple of 16.
+        // Global -> this block's shared memory; `bar` receives complete_tx(bytes).
+        ROCWMMA_DEVICE inline void bulk_load(uint32_t dstSmemAddr, void const* src, uint32_t bytes,
+                                             uint32_t barSmemAddr)
+        {
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes"
+                         " [%0], [%1], %2, [%3];" ::"r"(dstSmemAddr),
+                         "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(barSmemAddr)
+                         : "memory");
+        }
+        // Shared -> global, completion tracked by the issuing thread's bulk groups
+        // (tma_store_commit / tma_store_wait_read / tma_store_wait_all below).
+        ROCWMMA_DEVICE inline void bulk_store(void* dst, uint32_t srcSmemAddr, uint32_t bytes)
+        {
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                             reinterpret_cast<uint64_t>(dst)),
+                         "r"(srcSmemAddr), "r"(bytes)
+                         : "memory");
+        }
+        // One arrival on `bar` that also announces `bytes` of complete_tx still to come
+        // (bytes may be 0).  Address form of mbar_expect_tx.
+        ROCWMMA_DEVICE inline void mbar_arrive_expect_tx(uint32_t barSmemAddr, uint32_t bytes)
+        {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(barSmemAddr),
+                         "r"(bytes)
+                         : "memory");
+        }
+
         // ---- TMA stores (shared -> global), bulk-group completion ----------------------------
         // Generic-proxy writes to shared memory must be fenced before the async proxy reads them.
         ROCWMMA_DEVICE inline void fence_async_shared()

@@ -11,30 +11,38 @@
 //
 //   * a warp owns whole samples; eight consecutive samples form a group so that the
 //     packed [k + m(m-1)/2]-wide rows, which are only 2-byte aligned one by one, start
-//     on a 16-byte boundary as a group and move with 128-bit accesses;
-//   * samples stream through a per-warp cp.async ring (padded rows, conflict-free
-//     ldmatrix); the m x m (forward) and m x k (backward) products run on warp-level
-//     tensor-core instructions (mma.sync m16n8k16, fp32 accumulate) with m padded to
-//     32 by a shared row of zeros; nothing is written to global scratch;
+//     on a 16-byte boundary as a group;
+//   * samples stream through a per-warp cp.async ring in shared memory (16-byte pieces into
+//     rows padded by 16 bytes, so that ldmatrix is conflict-free).  A finished group of
+//     packed forward rows leaves as ONE bulk copy (cp.async.bulk shared -> global, 16 x
+//     outLen bytes).  Bulk copies per 256-byte row, for the loads or for the gradient,
+//     were slower than 16-byte cp.async / 128-bit stores: the copy engine took about 17
+//     cycles per request.
+//   * the m x m (forward) and m x k (backward) products run on warp-level tensor-core
+//     instructions (mma.sync m16n8k16, fp32 accumulate) with m padded to 32 by a shared
+//     row of zeros; nothing is written to global scratch;
 //   * forward: X X^T needs only A fragments -- the B operand of block (i, j) is a
 //     re-labelling of the A registers of block j; only blocks on or below the diagonal
 //     are computed;
 //   * backward: the symmetric matrix G is rebuilt in shared memory (stored in fp16 as
 //     the host routine does), G X overwrites the sample's own ring slot column block
-//     by column block and leaves with 128-bit row stores.
+//     by column block.
 //
 // Limits: fp16, m <= 32, k a multiple of 16 and <= 256, pointers 16-byte aligned.
 #include "common.cuh"
+#include "rocwmma/rocwmma_block.hpp"
 #include "runtime.cuh"
 #include <cstdlib>
 #include <cuda_fp16.h>
 
 namespace
 {
-    constexpr uint32_t GROUP   = 8; // samples per aligned group
-    constexpr uint32_t MAX_K   = 256;
-    constexpr uint32_t G_LD    = 40; // halves per row of the 32x32 G tile (80 bytes)
-    constexpr uint32_t MAX_WARPS = 12;
+    namespace blk = rocwmma::block;
+
+    constexpr uint32_t GROUP      = 8; // samples per aligned group
+    constexpr uint32_t MAX_K      = 256;
+    constexpr uint32_t G_LD       = 40; // halves per row of the 32x32 G tile (80 bytes)
+    constexpr uint32_t MAX_WARPS  = 12;
     constexpr uint32_t ZERO_BYTES = MAX_K * 2 + 16;
 
     __device__ inline uint32_t smemAddr(void const* p)
@@ -58,22 +66,67 @@ namespace
     {
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                     : "r"(addr));
+                     : "r"(addr)
+                     : "memory");
     }
     __device__ inline void ldmatrixX4Trans(uint32_t (&r)[4], uint32_t addr)
     {
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                     : "r"(addr));
+                     : "r"(addr)
+                     : "memory");
     }
     __device__ inline void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                     uint32_t a3, uint32_t b0, uint32_t b1)
     {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
-                     "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+            "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
     }
+    // The same with a zero accumulator on input: the first product of a chain needs no
+    // cleared registers.
+    __device__ inline void mma16816z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                     uint32_t a3, uint32_t b0, uint32_t b1)
+    {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+            "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+    }
+    template <bool FIRST>
+    __device__ inline void mmaStep(float (&d)[4], uint32_t const (&a)[4], uint32_t b0, uint32_t b1)
+    {
+        if constexpr(FIRST)
+            mma16816z(d, a[0], a[1], a[2], a[3], b0, b1);
+        else
+            mma16816(d, a[0], a[1], a[2], a[3], b0, b1);
+    }
+
+    // Predicated shared-memory stores.  Written as predicated instructions on purpose: as
+    // `if(p) *ptr = v` the compiler at times emitted a divergent branch with a reconvergence
+    // point around every store of an unrolled epilogue, a third more instructions overall.
+    __device__ inline void stSharedIf(uint32_t addr, uint32_t v, bool p)
+    {
+        asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %2, 0;\n\t@q st.shared.b32 [%0], %1;\n\t}"
+                     ::"r"(addr), "r"(v), "r"(uint32_t(p))
+                     : "memory");
+    }
+    __device__ inline void stSharedIf(uint32_t addr, __half v, bool p)
+    {
+        asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %2, 0;\n\t@q st.shared.b16 [%0], %1;\n\t}"
+                     ::"r"(addr), "h"(__half_as_ushort(v)), "r"(uint32_t(p))
+                     : "memory");
+    }
+
+    struct TrueT
+    {
+        static constexpr bool value = true;
+    };
+    struct FalseT
+    {
+        static constexpr bool value = false;
+    };
 
     struct Shape
     {
@@ -82,7 +135,6 @@ namespace
         uint32_t rowStride; // bytes per staged sample row: 2k + 16
         uint32_t stageBytes; // m * rowStride
         uint32_t numGroups; // ceil(batch / 8)
-        uint32_t chunks; // 16-byte pieces in a sample: m * k / 8
     };
 
     // Work distribution: groups of 8 samples are handed out through one global counter, so
@@ -137,37 +189,53 @@ namespace
         return (m * (m - 1) / 2 * 4 + 15) / 16 * 16;
     }
 
-    // A sample is m rows of k halves, contiguous in global memory; in a ring slot its rows
-    // are rowStride bytes apart.  ChunkMap gives the slot offset of the sample's c-th
-    // 16-byte piece without a division: c / chunksPerRow == (c * magic) >> 16 for every
-    // c < 2048 and chunksPerRow <= 32 (magic = ceil(65536 / chunksPerRow)), and a sample
-    // has at most 32 * 256 / 8 = 1024 pieces.
-    struct ChunkMap
+    // One warp's ring of staged samples.  A sample is m rows of k halves, contiguous in
+    // global memory; in a slot its rows are rowStride bytes apart.  A lane moves the 16-byte
+    // pieces lane, lane + 32, ...; the slot offset of piece c needs c / chunksPerRow, which
+    // is (c * magic) >> 16 -- exact for c < 2048 and chunksPerRow <= 32 with
+    // magic = ceil(65536 / chunksPerRow); a sample has at most 32 * 256 / 8 = 1024 pieces.
+    // Every fill is one cp.async group (an empty one past the end of the batch), so that
+    // "all but the newest NSTAGES - 2 groups have landed" always means "the oldest slot is
+    // full".
+    template <uint32_t NSTAGES>
+    struct Ring
     {
-        uint32_t chunksPerRow, magic, rowStride, total;
+        uint32_t slot0, stageBytes;
+        uint32_t chunksPerRow, magic, rowStride, chunks;
 
-        __device__ inline void init(Shape const& sh)
+        __device__ inline void init(uint32_t ringAddr, Shape const& sh)
         {
+            slot0        = ringAddr;
+            stageBytes   = sh.stageBytes;
             chunksPerRow = sh.k / 8;
             magic        = (65536u + chunksPerRow - 1u) / chunksPerRow;
             rowStride    = sh.rowStride;
-            total        = sh.chunks;
+            chunks       = sh.m * chunksPerRow;
         }
+        __device__ inline uint32_t slotAddr(uint32_t s) const
+        {
+            return slot0 + s * stageBytes;
+        }
+        // Slot offset of a sample's c-th 16-byte piece.
         __device__ inline uint32_t offset(uint32_t c) const
         {
             const uint32_t row = (c * magic) >> 16;
             return row * rowStride + (c - row * chunksPerRow) * 16u;
         }
+        __device__ inline void fill(uint32_t s, __half const* sample, uint32_t lane) const
+        {
+            uint8_t const* src = reinterpret_cast<uint8_t const*>(sample);
+            const uint32_t dst = slotAddr(s);
+            for(uint32_t c = lane; c < chunks; c += 32)
+                cpAsync16(dst + offset(c), src + size_t(c) * 16);
+        }
+        // The oldest fill still outstanding has landed, for every lane of the warp.
+        __device__ inline void waitOldest() const
+        {
+            cpAsyncWait<NSTAGES - 2>();
+            __syncwarp();
+        }
     };
-
-    // Copies one sample into a ring slot.
-    __device__ inline void issueSample(uint32_t slotAddr, __half const* sample,
-                                       ChunkMap const& map, uint32_t lane)
-    {
-        uint8_t const* src = reinterpret_cast<uint8_t const*>(sample);
-        for(uint32_t c = lane; c < map.total; c += 32)
-            cpAsync16(slotAddr + map.offset(c), src + size_t(c) * 16);
-    }
 
     // =====================================================================================
     // forward
@@ -187,18 +255,17 @@ namespace
         uint8_t*       zeroRow       = smem;
         uint8_t*       mine          = smem + ZERO_BYTES + warp * perWarp;
         __half*        outStage      = reinterpret_cast<__half*>(mine + NSTAGES * sh.stageBytes);
-        const uint32_t ringAddr      = smemAddr(mine);
         const uint32_t zeroAddr      = smemAddr(zeroRow);
 
         for(uint32_t i = threadIdx.x; i < ZERO_BYTES / 4; i += blockDim.x)
             reinterpret_cast<uint32_t*>(zeroRow)[i] = 0u;
+        Ring<NSTAGES> ring;
+        ring.init(smemAddr(mine), sh);
         __syncthreads();
 
         const bool twoM = sh.m > 16;
         GroupFeed  feed;
         feed.init(counter, sh.numGroups, lane);
-        ChunkMap map;
-        map.init(sh);
 
         // Where this lane's accumulator elements go in a packed output row.  Element pair h
         // of block i sits at row r = 16 mt + g + 8 h, columns c and c + 1 (c = 8 nt + 2 t);
@@ -222,16 +289,15 @@ namespace
                 triSlot[i][h] = v;
             }
 
-        // prologue
-#pragma unroll
-        for(uint32_t q = 0; q < NSTAGES - 1; ++q)
-        {
+        auto fill = [&](uint32_t q) {
             const uint32_t s = feed.sample(q);
             if(s < sh.batch)
-                issueSample(ringAddr + q * sh.stageBytes, input + size_t(s) * sh.m * sh.k,
-                            map, lane);
+                ring.fill(q % NSTAGES, input + size_t(s) * sh.m * sh.k, lane);
             cpAsyncCommit();
-        }
+        };
+#pragma unroll
+        for(uint32_t q = 0; q < NSTAGES - 1; ++q)
+            fill(q);
 
         // ldmatrix row addresses of this lane inside a slot: matrix (lane / 8) of the x4 group
         // is rows (lane/8 & 1) * 8 ..., column block (lane / 16) * 8; rows >= m read zeros.
@@ -244,90 +310,93 @@ namespace
                 feed.advance(lane);
             if(feed.done())
                 break;
-            cpAsyncWait<NSTAGES - 2>();
-            __syncwarp();
-            {
-                const uint32_t qn = q + NSTAGES - 1;
-                const uint32_t s  = feed.sample(qn);
-                if(s < sh.batch)
-                    issueSample(ringAddr + (qn % NSTAGES) * sh.stageBytes,
-                                input + size_t(s) * sh.m * sh.k, map, lane);
-                cpAsyncCommit();
-            }
+            // sample q has landed, and every lane is done with the slot the next fill overwrites
+            ring.waitOldest();
+            fill(q + NSTAGES - 1);
 
             const uint32_t sample = feed.sample(q);
             const uint32_t slot   = q % GROUP;
             if(sample < sh.batch)
             {
-                const uint32_t slotAddr = ringAddr + (q % NSTAGES) * sh.stageBytes;
+                const uint32_t slotAddr = ring.slotAddr(q % NSTAGES);
                 float          acc[6][4];
-#pragma unroll
-                for(uint32_t i = 0; i < 6; ++i)
-#pragma unroll
-                    for(uint32_t e = 0; e < 4; ++e)
-                        acc[i][e] = 0.0f;
-
                 const uint32_t row0 = lmRow, row1 = 16u + lmRow;
                 const uint32_t base0 = row0 < sh.m ? slotAddr + row0 * sh.rowStride : zeroAddr;
                 const uint32_t base1 = row1 < sh.m ? slotAddr + row1 * sh.rowStride : zeroAddr;
-                for(uint32_t kk = 0; kk < sh.k; kk += 16)
-                {
-                    uint32_t a[4], b[4];
+                auto kStep = [&](auto first, uint32_t kk) {
+                    constexpr bool FIRST = decltype(first)::value;
+                    uint32_t       a[4], b[4];
                     ldmatrixX4(a, base0 + (kk + lmCol) * 2);
                     // blocks (0,0) and (0,1): B operands are A's own registers
-                    mma16816(acc[0], a[0], a[1], a[2], a[3], a[0], a[2]);
-                    mma16816(acc[1], a[0], a[1], a[2], a[3], a[1], a[3]);
+                    mmaStep<FIRST>(acc[0], a, a[0], a[2]);
+                    mmaStep<FIRST>(acc[1], a, a[1], a[3]);
                     if(twoM)
                     {
                         ldmatrixX4(b, base1 + (kk + lmCol) * 2);
-                        mma16816(acc[2], b[0], b[1], b[2], b[3], a[0], a[2]);
-                        mma16816(acc[3], b[0], b[1], b[2], b[3], a[1], a[3]);
-                        mma16816(acc[4], b[0], b[1], b[2], b[3], b[0], b[2]);
-                        mma16816(acc[5], b[0], b[1], b[2], b[3], b[1], b[3]);
+                        mmaStep<FIRST>(acc[2], b, a[0], a[2]);
+                        mmaStep<FIRST>(acc[3], b, a[1], a[3]);
+                        mmaStep<FIRST>(acc[4], b, b[0], b[2]);
+                        mmaStep<FIRST>(acc[5], b, b[1], b[3]);
                     }
-                }
+                };
+                kStep(TrueT{}, 0u);
+                for(uint32_t kk = 16; kk < sh.k; kk += 16)
+                    kStep(FalseT{}, kk);
 
+                // The staging rows of the previous group may still be on their way out.
+                if(slot == 0)
+                {
+                    if(lane == 0)
+                        blk::tma_store_wait_read<0>();
+                    __syncwarp();
+                }
                 // row 0 of the sample, then the strict lower triangle
-                __half*       dst  = outStage + slot * sh.outLen;
+                __half*       dst   = outStage + slot * sh.outLen;
                 __half const* row0p = reinterpret_cast<__half const*>(
                     mine + (q % NSTAGES) * sh.stageBytes);
                 for(uint32_t j = lane; j < sh.k; j += 32)
                     dst[j] = row0p[j];
+                const uint32_t dstAddr = smemAddr(dst);
 #pragma unroll
                 for(uint32_t i = 0; i < 6; ++i)
 #pragma unroll
                     for(uint32_t h = 0; h < 2; ++h)
                     {
-                        const uint32_t v = triSlot[i][h], idx = v & 0xffffu;
-                        if(v & (1u << 16))
-                            dst[idx] = __float2half_rn(acc[i][2 * h]);
-                        if(v & (1u << 17))
-                            dst[idx + 1] = __float2half_rn(acc[i][2 * h + 1]);
+                        const uint32_t v = triSlot[i][h], at = dstAddr + (v & 0xffffu) * 2u;
+                        stSharedIf(at, __float2half_rn(acc[i][2 * h]), (v >> 16) & 1u);
+                        stSharedIf(at + 2u, __float2half_rn(acc[i][2 * h + 1]), (v >> 17) & 1u);
                     }
             }
 
-            // end of a group: flush its packed rows with 128-bit stores
+            // end of a group: its packed rows are contiguous in the output and start on a
+            // 16-byte boundary -- one bulk copy when the group is complete
             if(slot == GROUP - 1)
             {
-                __syncwarp();
                 const uint32_t first = feed.g0 * GROUP;
                 const uint32_t cnt   = min(GROUP, sh.batch - first);
                 __half*        gout  = output + size_t(first) * sh.outLen;
                 if(cnt == GROUP)
                 {
-                    for(uint32_t i = lane; i < sh.outLen; i += 32)
-                        reinterpret_cast<uint4*>(gout)[i]
-                            = reinterpret_cast<uint4 const*>(outStage)[i];
+                    blk::fence_async_shared();
+                    __syncwarp();
+                    if(lane == 0)
+                    {
+                        blk::bulk_store(gout, smemAddr(outStage), outStageBytes);
+                        blk::tma_store_commit();
+                    }
                 }
                 else
                 {
+                    __syncwarp();
                     for(uint32_t i = lane; i < cnt * sh.outLen; i += 32)
                         gout[i] = outStage[i];
+                    __syncwarp();
                 }
-                __syncwarp();
             }
         }
         cpAsyncWait<0>();
+        if(lane == 0)
+            blk::tma_store_wait_all<0>();
     }
 
     // =====================================================================================
@@ -344,17 +413,16 @@ namespace
         const uint32_t g = lane >> 2, t = lane & 3;
 
         // layout: [zero row][triangle table][warp 0: ring, G][warp 1: ...]
-        const uint32_t triCount   = sh.m * (sh.m - 1) / 2;
-        const uint32_t triBytes   = triTableBytes(sh.m);
-        const uint32_t gBytes     = 32 * G_LD * 2;
-        const uint32_t perWarp    = NSTAGES * sh.stageBytes + gBytes;
-        uint8_t*       zeroRow    = smem;
-        uint32_t*      tri        = reinterpret_cast<uint32_t*>(smem + ZERO_BYTES);
-        uint8_t*       mine       = smem + ZERO_BYTES + triBytes + warp * perWarp;
-        __half*        gTile      = reinterpret_cast<__half*>(mine + NSTAGES * sh.stageBytes);
-        const uint32_t ringAddr   = smemAddr(mine);
-        const uint32_t zeroAddr   = smemAddr(zeroRow);
-        const uint32_t gAddr      = smemAddr(gTile);
+        const uint32_t triCount = sh.m * (sh.m - 1) / 2;
+        const uint32_t triBytes = triTableBytes(sh.m);
+        const uint32_t gBytes   = 32 * G_LD * 2;
+        const uint32_t perWarp  = NSTAGES * sh.stageBytes + gBytes;
+        uint8_t*       zeroRow  = smem;
+        uint32_t*      tri      = reinterpret_cast<uint32_t*>(smem + ZERO_BYTES);
+        uint8_t*       mine     = smem + ZERO_BYTES + triBytes + warp * perWarp;
+        __half*        gTile    = reinterpret_cast<__half*>(mine + NSTAGES * sh.stageBytes);
+        const uint32_t zeroAddr = smemAddr(zeroRow);
+        const uint32_t gAddr    = smemAddr(gTile);
 
         for(uint32_t i = threadIdx.x; i < ZERO_BYTES / 4; i += blockDim.x)
             reinterpret_cast<uint32_t*>(zeroRow)[i] = 0u;
@@ -365,19 +433,19 @@ namespace
                 tri[r * (r - 1) / 2 + c] = (r * G_LD + c) | ((c * G_LD + r) << 16);
         for(uint32_t i = lane; i < 32 * G_LD / 2; i += 32)
             reinterpret_cast<uint32_t*>(gTile)[i] = 0u; // diagonal and padding stay zero
+        Ring<NSTAGES> ring;
+        ring.init(smemAddr(mine), sh);
         __syncthreads();
 
         const bool twoM = sh.m > 16;
         GroupFeed  feed;
         feed.init(counter, sh.numGroups, lane);
-        ChunkMap map;
-        map.init(sh);
 
-        auto issue = [&](uint32_t q) {
+        auto fill = [&](uint32_t q) {
             const uint32_t s = feed.sample(q);
             if(s < sh.batch)
-                issueSample(ringAddr + (q % NSTAGES) * sh.stageBytes,
-                            input + size_t(s) * sh.m * sh.k, map, lane);
+                ring.fill(q % NSTAGES, input + size_t(s) * sh.m * sh.k, lane);
+            cpAsyncCommit();
         };
 
         // The packed upstream row of a sample is only 2-byte aligned, and each value is used
@@ -403,10 +471,7 @@ namespace
 
 #pragma unroll
         for(uint32_t q = 0; q < NSTAGES - 1; ++q)
-        {
-            issue(q);
-            cpAsyncCommit();
-        }
+            fill(q);
         prefetchTriangle(0);
 
         const uint32_t lmRow = ((lane >> 3) & 1u) * 8u + (lane & 7u);
@@ -418,16 +483,13 @@ namespace
                 feed.advance(lane);
             if(feed.done())
                 break;
-            cpAsyncWait<NSTAGES - 2>();
-            __syncwarp();
-            issue(q + NSTAGES - 1);
-            cpAsyncCommit();
-
             const uint32_t sample = feed.sample(q);
             if(sample >= sh.batch)
-                continue; // padding of the batch's last group
+                continue; // padding of the batch's last group; nothing follows it
+            ring.waitOldest();
+            fill(q + NSTAGES - 1);
             uint8_t*       slotPtr  = mine + (q % NSTAGES) * sh.stageBytes;
-            const uint32_t slotAddr = ringAddr + (q % NSTAGES) * sh.stageBytes;
+            const uint32_t slotAddr = ring.slotAddr(q % NSTAGES);
 
             // this sample's triangle (fetched one iteration ago), then start on the next one's
             __half triCur[TRI_REGS];
@@ -477,40 +539,37 @@ namespace
             {
                 const uint32_t pairs = min(4u, (sh.k - n0) / 16u); // 16 columns per ldmatrix.x4
                 float          acc[2][8][4];
-#pragma unroll
-                for(uint32_t a = 0; a < 2; ++a)
-#pragma unroll
-                    for(uint32_t b = 0; b < 8; ++b)
-#pragma unroll
-                        for(uint32_t e = 0; e < 4; ++e)
-                            acc[a][b][e] = 0.0f;
+                // Two passes over the column block, one per half of the k rows, so that the
+                // two products that add into one accumulator are sixteen instructions apart.
 #pragma unroll
                 for(uint32_t p = 0; p < 4; ++p)
                 {
                     if(p < pairs)
                     {
-                        uint32_t       xb[4];
-                        const uint32_t col = (n0 + p * 16u + lmCol) * 2u;
-                        ldmatrixX4Trans(xb, xb0 + col); // k rows 0..15
-                        mma16816(acc[0][2 * p], ga[0][0][0], ga[0][0][1], ga[0][0][2], ga[0][0][3],
-                                 xb[0], xb[1]);
-                        mma16816(acc[0][2 * p + 1], ga[0][0][0], ga[0][0][1], ga[0][0][2],
-                                 ga[0][0][3], xb[2], xb[3]);
+                        uint32_t xb[4];
+                        ldmatrixX4Trans(xb, xb0 + (n0 + p * 16u + lmCol) * 2u); // k rows 0..15
+                        mmaStep<true>(acc[0][2 * p], ga[0][0], xb[0], xb[1]);
+                        mmaStep<true>(acc[0][2 * p + 1], ga[0][0], xb[2], xb[3]);
                         if(twoM)
                         {
-                            mma16816(acc[1][2 * p], ga[1][0][0], ga[1][0][1], ga[1][0][2],
-                                     ga[1][0][3], xb[0], xb[1]);
-                            mma16816(acc[1][2 * p + 1], ga[1][0][0], ga[1][0][1], ga[1][0][2],
-                                     ga[1][0][3], xb[2], xb[3]);
-                            ldmatrixX4Trans(xb, xb1 + col); // k rows 16..31
-                            mma16816(acc[0][2 * p], ga[0][1][0], ga[0][1][1], ga[0][1][2],
-                                     ga[0][1][3], xb[0], xb[1]);
-                            mma16816(acc[0][2 * p + 1], ga[0][1][0], ga[0][1][1], ga[0][1][2],
-                                     ga[0][1][3], xb[2], xb[3]);
-                            mma16816(acc[1][2 * p], ga[1][1][0], ga[1][1][1], ga[1][1][2],
-                                     ga[1][1][3], xb[0], xb[1]);
-                            mma16816(acc[1][2 * p + 1], ga[1][1][0], ga[1][1][1], ga[1][1][2],
-                                     ga[1][1][3], xb[2], xb[3]);
+                            mmaStep<true>(acc[1][2 * p], ga[1][0], xb[0], xb[1]);
+                            mmaStep<true>(acc[1][2 * p + 1], ga[1][0], xb[2], xb[3]);
+                        }
+                    }
+                }
+                if(twoM)
+                {
+#pragma unroll
+                    for(uint32_t p = 0; p < 4; ++p)
+                    {
+                        if(p < pairs)
+                        {
+                            uint32_t xb[4];
+                            ldmatrixX4Trans(xb, xb1 + (n0 + p * 16u + lmCol) * 2u); // k rows 16..31
+                            mmaStep<false>(acc[0][2 * p], ga[0][1], xb[0], xb[1]);
+                            mmaStep<false>(acc[0][2 * p + 1], ga[0][1], xb[2], xb[3]);
+                            mmaStep<false>(acc[1][2 * p], ga[1][1], xb[0], xb[1]);
+                            mmaStep<false>(acc[1][2 * p + 1], ga[1][1], xb[2], xb[3]);
                         }
                     }
                 }
@@ -518,33 +577,41 @@ namespace
                 __syncwarp();
 #pragma unroll
                 for(uint32_t mt = 0; mt < 2; ++mt)
-#pragma unroll
-                    for(uint32_t nb = 0; nb < 8; ++nb)
+                {
+                    if(mt == 0 || twoM)
                     {
-                        if(nb < 2 * pairs && (mt == 0 || twoM))
-                        {
 #pragma unroll
-                            for(uint32_t h = 0; h < 2; ++h)
+                        for(uint32_t h = 0; h < 2; ++h)
+                        {
+                            const uint32_t r    = mt * 16u + g + 8u * h;
+                            const bool     live = r < sh.m;
+                            const uint32_t at   = slotAddr + r * sh.rowStride + (n0 + 2u * t) * 2u;
+#pragma unroll
+                            for(uint32_t nb = 0; nb < 8; ++nb)
                             {
-                                const uint32_t r = mt * 16u + g + 8u * h;
-                                const uint32_t c = n0 + nb * 8u + 2u * t;
-                                if(r < sh.m)
-                                    *reinterpret_cast<__half2*>(slotPtr + r * sh.rowStride + c * 2)
-                                        = __floats2half2_rn(acc[mt][nb][2 * h],
-                                                            acc[mt][nb][2 * h + 1]);
+                                if(nb < 2 * pairs)
+                                {
+                                    const __half2 v = __floats2half2_rn(acc[mt][nb][2 * h],
+                                                                        acc[mt][nb][2 * h + 1]);
+                                    stSharedIf(at + nb * 16u,
+                                               *reinterpret_cast<uint32_t const*>(&v), live);
+                                }
                             }
                         }
                     }
+                }
             }
+
             __syncwarp();
 
-            // rows of the result leave with 128-bit stores (the sample is contiguous in grad)
+            // The result leaves with 128-bit stores (the sample is contiguous in grad).  One
+            // bulk copy per 256-byte row instead was slower, as it was for the loads.
             {
                 uint4* gdst = reinterpret_cast<uint4*>(grad + size_t(sample) * sh.m * sh.k);
-                for(uint32_t c = lane; c < map.total; c += 32)
-                    gdst[c] = *reinterpret_cast<uint4 const*>(slotPtr + map.offset(c));
+                for(uint32_t c = lane; c < ring.chunks; c += 32)
+                    gdst[c] = *reinterpret_cast<uint4 const*>(slotPtr + ring.offset(c));
             }
-            __syncwarp();
+            // (the next iteration's __syncwarp orders these reads before the slot's refill)
         }
         cpAsyncWait<0>();
     }
@@ -565,7 +632,6 @@ namespace
         sh->rowStride  = 2 * k + 16;
         sh->stageBytes = m * sh->rowStride;
         sh->numGroups  = (batch + GROUP - 1) / GROUP;
-        sh->chunks     = m * k / 8;
         return B200WMMA_OK;
     }
 
