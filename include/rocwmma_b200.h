@@ -42,7 +42,8 @@ enum b200wmma_dtype
     B200WMMA_F32  = 4, /* float32_t, full fp32 products                 */
     B200WMMA_XF32 = 5, /* xfloat32_t: fp32 storage, low 13 bits zero    */
     B200WMMA_F64  = 6, /* float64_t                                     */
-    B200WMMA_I32  = 7  /* int32_t (outputs of int8 GEMM)                */
+    B200WMMA_I32  = 7, /* int32_t (outputs of int8 GEMM)                */
+    B200WMMA_E5M2 = 8  /* bfloat8_t, OCP e5m2                           */
 };
 
 /* Memory layouts (rocwmma.hpp:74-81, 106-110). */
@@ -84,13 +85,33 @@ B200WMMA_API int b200wmma_gemm_simple(int in_dtype, int out_dtype, uint32_t m, u
                          int layout_a, int layout_b, int layout_cd, int block, void* stream);
 
 /*
+ * The same kernel for a full rocWMMA type triple Ti / To / Tc
+ * (docs/api-reference/api-reference-guide.rst:80-153; the reference's test kernels take
+ * the compute type and BlockK as template parameters, test/gemm/gemm_kernel_base.hpp:57-75).
+ * compute_dtype is the type of the accumulator fragment, of alpha and beta and of the
+ * scaling arithmetic; a negative value selects the usual one (F32; I32 for I8; F64 for
+ * F64), which makes the call identical to b200wmma_gemm_simple.  Besides the triples of
+ * b200wmma_gemm_simple: F16/F16/F16 (tensor-core fp16 accumulation), BF16/BF16/BF16
+ * (accumulator fragment rounded to bf16 after every BlockK step, as rocWMMA does for
+ * 16-bit compute types, internal/mfma_impl.hpp:101-156), I8/I8/I32, E5M2/F32/F32.
+ * block_k is the K extent of the A and B fragments: 0 for the usual one (16; 32 for 8-bit
+ * types in 32 x 32 tiles), else 16, 32 or 64 for 8- and 16-bit types, 8 or 32 for
+ * F32 / XF32, 4 or 8 for F64; k must be a multiple of it.
+ */
+B200WMMA_API int b200wmma_gemm_simple_ex(int in_dtype, int out_dtype, int compute_dtype, uint32_t m,
+                            uint32_t n, uint32_t k, const void* a, const void* b, const void* c,
+                            void* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                            double alpha, double beta, int layout_a, int layout_b, int layout_cd,
+                            int block, int block_k, void* stream);
+
+/*
  * D = alpha * A * B + beta * C through the block-cooperative path: TMA-staged
  * shared-memory ring, tcgen05.mma with accumulators in tensor memory, persistent
  * tiles.  Takes the place of the reference's macro-tile GEMM
  * (samples/perf_hgemm.cpp:518-714, perf_sgemm.cpp:472, perf_dgemm.cpp:464; same
  * argument order as above).  C and D are row-major.  When beta == 0, c may be
  * NULL and is never read.  Type pairs: F16->F16, F16->F32, BF16->F32, BF16->BF16,
- * XF32->F32, I8->I32, E4M3->BF16, E4M3->F32; F64->F64 runs on the warp-level
+ * XF32->F32, I8->I32, E4M3->BF16, E4M3->F32, E5M2->BF16, E5M2->F32; F64->F64 runs on the warp-level
  * double-precision tensor path with a shared-memory pipeline.
  * Requirements: a, b, c, d 16-byte aligned; lda, ldb, ldc, ldd times the element
  * size multiples of 16 bytes.  Any m, n, k >= 1 (edge tiles are zero-filled on

@@ -20,11 +20,11 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
 # dtype codes shared with the C ABI of the CUDA library
-F16, BF16, E4M3, I8, F32, XF32, F64, I32 = range(8)
+F16, BF16, E4M3, I8, F32, XF32, F64, I32, E5M2 = range(9)
 ROW, COL = 0, 1
 
 _NP = {F16: np.float16, BF16: np.uint16, E4M3: np.uint8, I8: np.int8,
-       F32: np.float32, XF32: np.float32, F64: np.float64, I32: np.int32}
+       F32: np.float32, XF32: np.float32, F64: np.float64, I32: np.int32, E5M2: np.uint8}
 
 
 def np_dtype(code: int):
@@ -54,11 +54,11 @@ def lib():
     if _lib is None:
         build()
         L = C.CDLL(os.path.join(_HERE, "liboracle.so"))
-        L.oracle_gemm.restype = C.c_int
-        L.oracle_gemm.argtypes = [C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32,
-                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                  C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
-                                  C.c_double, C.c_double, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.oracle_gemm_ex.restype = C.c_int
+        L.oracle_gemm_ex.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_uint32,
+                                     C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                     C.c_double, C.c_double, C.c_int, C.c_int, C.c_int, C.c_int]
         L.oracle_dlrm_fwd.restype = C.c_int
         L.oracle_dlrm_fwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
                                       C.c_uint32]
@@ -70,6 +70,9 @@ def lib():
                                   C.c_void_p, C.c_void_p, C.c_double, C.c_double, C.c_uint32]
         L.oracle_max_rel_err.restype = C.c_double
         L.oracle_max_rel_err.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_uint64]
+        for name in ("oracle_encode_e5m2", "oracle_decode_e5m2"):
+            getattr(L, name).restype = None
+            getattr(L, name).argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
         for name in ("oracle_encode_e4m3", "oracle_decode_e4m3", "oracle_encode_bf16",
                      "oracle_decode_bf16"):
             getattr(L, name).restype = None
@@ -90,10 +93,10 @@ def ref():
             if not os.path.exists(path):
                 return None
         L = C.CDLL(path)
-        L.ref_gemm.restype = C.c_int
-        L.ref_gemm.argtypes = [C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
-                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_double, C.c_double,
-                               C.c_int, C.c_int]
+        L.ref_gemm_ex.restype = C.c_int
+        L.ref_gemm_ex.argtypes = [C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32,
+                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_double,
+                                  C.c_double, C.c_int, C.c_int]
         L.ref_dlrm_fwd.restype = C.c_int
         L.ref_dlrm_fwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
                                    C.c_uint32]
@@ -117,32 +120,35 @@ def _check(a, code, name):
 
 
 def gemm(in_t, out_t, m, n, k, a, b, c, alpha, beta, layout_a=ROW, layout_b=COL,
-         layout_c=ROW, layout_d=ROW, lda=None, ldb=None, ldc=None, ldd=None, literal=False):
+         layout_c=ROW, layout_d=ROW, lda=None, ldb=None, ldc=None, ldd=None, literal=False,
+         comp_t=None):
     """D = alpha*A*B + beta*C.  Arrays are flat storage in the stated layouts;
-    leading dimensions default to the natural ones (test/reference_impl.hpp:53-56)."""
+    leading dimensions default to the natural ones (test/reference_impl.hpp:53-56).
+    comp_t: the compute type (rocWMMA's Tc); None = the usual one for the input type."""
     lda = lda or (k if layout_a == ROW else m)
     ldb = ldb or (n if layout_b == ROW else k)
     ldc = ldc or (n if layout_c == ROW else m)
     ldd = ldd or (n if layout_d == ROW else m)
     _check(a, in_t, "a"), _check(b, in_t, "b"), _check(c, out_t, "c")
     d = np.empty(m * ldd if layout_d == ROW else n * ldd, dtype=_NP[out_t])
-    rc = lib().oracle_gemm(in_t, out_t, int(literal), m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d),
-                           lda, ldb, ldc, ldd, float(alpha), float(beta), layout_a, layout_b,
-                           layout_c, layout_d)
+    rc = lib().oracle_gemm_ex(in_t, out_t, -1 if comp_t is None else comp_t, int(literal), m, n,
+                              k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
+                              float(alpha), float(beta), layout_a, layout_b, layout_c, layout_d)
     if rc != 0:
-        raise ValueError(f"oracle_gemm: unsupported type pair ({in_t},{out_t})")
+        raise ValueError(f"oracle_gemm: unsupported type triple ({in_t},{out_t},{comp_t})")
     return d
 
 
-def ref_gemm(in_t, out_t, m, n, k, a, b, c, alpha, beta, layout_a=ROW, layout_b=COL):
+def ref_gemm(in_t, out_t, m, n, k, a, b, c, alpha, beta, layout_a=ROW, layout_b=COL,
+             comp_t=None):
     """The reference's gemm_CPU (natural leading dimensions, C/D row-major)."""
     R = ref()
     assert R is not None, "oracle/_ref/libref.so was not built"
     d = np.empty(m * n, dtype=_NP[out_t])
-    rc = R.ref_gemm(in_t, out_t, m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), float(alpha),
-                    float(beta), layout_a, layout_b)
+    rc = R.ref_gemm_ex(in_t, out_t, -1 if comp_t is None else comp_t, m, n, k, _ptr(a), _ptr(b),
+                       _ptr(c), _ptr(d), float(alpha), float(beta), layout_a, layout_b)
     if rc != 0:
-        raise ValueError("ref_gemm: unsupported type pair")
+        raise ValueError("ref_gemm: unsupported type triple")
     return d
 
 
@@ -194,6 +200,20 @@ def decode_e4m3(x):
     x = np.ascontiguousarray(x, dtype=np.uint8)
     out = np.empty(x.shape, dtype=np.float32)
     lib().oracle_decode_e4m3(_ptr(x), _ptr(out), x.size)
+    return out
+
+
+def encode_e5m2(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint8)
+    lib().oracle_encode_e5m2(_ptr(x), _ptr(out), x.size)
+    return out
+
+
+def decode_e5m2(x):
+    x = np.ascontiguousarray(x, dtype=np.uint8)
+    out = np.empty(x.shape, dtype=np.float32)
+    lib().oracle_decode_e5m2(_ptr(x), _ptr(out), x.size)
     return out
 
 

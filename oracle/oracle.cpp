@@ -46,6 +46,7 @@ namespace
         DT_XF32 = 5, // fp32 storage whose low 13 mantissa bits are zero
         DT_F64  = 6,
         DT_I32  = 7,
+        DT_E5M2 = 8,
     };
 
     enum Layout : int
@@ -60,6 +61,10 @@ namespace
         uint16_t bits;
     };
     struct e4m3_t
+    {
+        uint8_t bits;
+    };
+    struct e5m2_t
     {
         uint8_t bits;
     };
@@ -93,6 +98,22 @@ namespace
             r = std::ldexp(float(m), -9); // subnormal: m/8 * 2^-6
         else
             r = std::ldexp(1.0f + float(m) / 8.0f, int(e) - 7);
+        return s ? -r : r;
+    }
+
+    // OCP e5m2: bias 15, two mantissa bits, infinities and NaNs as in IEEE -- the upper
+    // byte of a binary16 number.
+    inline float decode(e5m2_t v)
+    {
+        uint32_t s = v.bits >> 7, e = (v.bits >> 2) & 0x1F, m = v.bits & 3;
+        float    r;
+        if(e == 0x1F)
+            r = m ? std::numeric_limits<float>::quiet_NaN()
+                  : std::numeric_limits<float>::infinity();
+        else if(e == 0)
+            r = std::ldexp(float(m), -16); // subnormal: m/4 * 2^-14
+        else
+            r = std::ldexp(1.0f + float(m) / 4.0f, int(e) - 15);
         return s ? -r : r;
     }
 
@@ -136,6 +157,67 @@ namespace
         return e4m3_t{uint8_t(sign | bits)};
     }
 
+    // float -> e5m2, round to nearest even, saturating to +-57344 (no infinities are
+    // produced, like the e4m3 encoder).
+    inline e5m2_t encode_e5m2(float f)
+    {
+        uint32_t u    = float_to_bits(f);
+        uint8_t  sign = uint8_t((u >> 24) & 0x80);
+        float    a    = std::fabs(f);
+        if(std::isnan(f))
+            return e5m2_t{uint8_t(sign | 0x7f)};
+        if(a >= 57344.0f)
+            return e5m2_t{uint8_t(sign | 0x7b)};
+        if(a < std::ldexp(1.0f, -17)) // below half of the smallest subnormal (2^-16)
+            return e5m2_t{sign};
+        int ex;
+        (void)std::frexp(a, &ex);
+        int   e    = std::max(ex - 1, -14);
+        float q    = std::ldexp(a, 2 - e);
+        int   mant = int(std::nearbyint(q));
+        if(mant == 8)
+        {
+            mant = 4;
+            e += 1;
+        }
+        uint8_t bits;
+        if(mant < 4)
+            bits = uint8_t(mant);
+        else
+            bits = uint8_t(((e + 15) << 2) | (mant - 4));
+        return e5m2_t{uint8_t(sign | bits)};
+    }
+
+    // bfloat16 as a COMPUTE type: every operation is carried out in float and rounded back
+    // to bfloat16 (round to nearest even), which is how the host bfloat16 class used by the
+    // reference (hip_bfloat16, outside the reference tree) behaves.
+    struct bf16c_t
+    {
+        bf16_t v;
+        bf16c_t() = default;
+        bf16c_t(float f)
+            : v(encode_bf16(f))
+        {
+        }
+        operator float() const
+        {
+            return decode(v);
+        }
+        bf16c_t& operator+=(bf16c_t o)
+        {
+            *this = bf16c_t(float(*this) + float(o));
+            return *this;
+        }
+    };
+    inline bf16c_t operator*(bf16c_t a, bf16c_t b)
+    {
+        return bf16c_t(float(a) * float(b));
+    }
+    inline bf16c_t operator+(bf16c_t a, bf16c_t b)
+    {
+        return bf16c_t(float(a) + float(b));
+    }
+
     template <typename T>
     struct Conv;
     template <>
@@ -155,6 +237,12 @@ namespace
     {
         static float  up(e4m3_t v) { return decode(v); }
         static e4m3_t down(float v) { return encode_e4m3(v); }
+    };
+    template <>
+    struct Conv<e5m2_t>
+    {
+        static float  up(e5m2_t v) { return decode(v); }
+        static e5m2_t down(float v) { return encode_e5m2(v); }
     };
     template <>
     struct Conv<float>
@@ -204,11 +292,17 @@ namespace
                 CompT acc = CompT(0);
                 for(uint32_t h = 0; h < k; ++h)
                 {
-                    acc += CompT(Conv<InT>::up(a[idx(la, i, h, lda)]))
-                           * CompT(Conv<InT>::up(b[idx(lb, h, j, ldb)]));
+                    // Every operation is rounded to CompT on its own (named temporaries: a
+                    // 16-bit CompT must not keep a wider intermediate).
+                    const CompT p = CompT(Conv<InT>::up(a[idx(la, i, h, lda)]))
+                                    * CompT(Conv<InT>::up(b[idx(lb, h, j, ldb)]));
+                    acc += p;
                 }
-                CompT cv                = CompT(Conv<OutT>::up(c[idx(lc, i, j, ldc)]));
-                d[idx(ldl, i, j, ldd)] = Conv<OutT>::down(alpha * acc + beta * cv);
+                const CompT cv = CompT(Conv<OutT>::up(c[idx(lc, i, j, ldc)]));
+                const CompT t1 = alpha * acc;
+                const CompT t2 = beta * cv;
+                const CompT r  = t1 + t2;
+                d[idx(ldl, i, j, ldd)] = Conv<OutT>::down(r);
             }
         }
     }
@@ -252,13 +346,19 @@ namespace
                         CompT        av = arow[h];
                         CompT const* br = &bw[size_t(h) * n + j0];
                         for(uint32_t jj = 0; jj < jn; ++jj)
-                            acc[jj] += av * br[jj];
+                        {
+                            const CompT p = av * br[jj];
+                            acc[jj] += p;
+                        }
                     }
                     for(uint32_t jj = 0; jj < jn; ++jj)
                     {
                         uint32_t j  = j0 + jj;
-                        CompT    cv = CompT(Conv<OutT>::up(c[idx(lc, i, j, ldc)]));
-                        d[idx(ldl, i, j, ldd)] = Conv<OutT>::down(alpha * acc[jj] + beta * cv);
+                        const CompT cv = CompT(Conv<OutT>::up(c[idx(lc, i, j, ldc)]));
+                        const CompT t1 = alpha * acc[jj];
+                        const CompT t2 = beta * cv;
+                        const CompT r  = t1 + t2;
+                        d[idx(ldl, i, j, ldd)] = Conv<OutT>::down(r);
                     }
                 }
             }
@@ -416,30 +516,49 @@ namespace
 
 extern "C" {
 
-// D = alpha*A*B + beta*C on the host.  Returns 0, or -1 for a type triple the
-// reference's type table does not have.  `literal` != 0 selects the plain
-// triple loop (slow; used to check the blocked form).
+// D = alpha*A*B + beta*C on the host for the type triple (input, output, compute) --
+// rocWMMA's Ti / To / Tc (docs/api-reference/api-reference-guide.rst:80-153).  comp_t < 0
+// selects the triple's usual compute type (float for floating-point inputs up to 32 bits,
+// int32 for int8, double for double).  Returns 0, or -1 for a triple the reference's type
+// table does not have.  `literal` != 0 selects the plain triple loop (slow; used to check
+// the blocked form).
+int oracle_gemm_ex(int in_t, int out_t, int comp_t, int literal, uint32_t m, uint32_t n,
+                   uint32_t k, void const* a, void const* b, void const* c, void* d, uint32_t lda,
+                   uint32_t ldb, uint32_t ldc, uint32_t ldd, double alpha, double beta,
+                   int layoutA, int layoutB, int layoutC, int layoutD)
+{
+    if(comp_t < 0)
+        comp_t = in_t == DT_I8 ? DT_I32 : in_t == DT_F64 ? DT_F64 : DT_F32;
+#define ORACLE_CASE(I, O, C, IT, OT, CT)                                                    \
+    if(in_t == I && out_t == O && comp_t == C)                                              \
+        return gemm_run<IT, OT, CT>(literal, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, \
+                                    beta, layoutA, layoutB, layoutC, layoutD);
+    ORACLE_CASE(DT_F16, DT_F32, DT_F32, _Float16, float, float)
+    ORACLE_CASE(DT_F16, DT_F16, DT_F32, _Float16, _Float16, float)
+    ORACLE_CASE(DT_F16, DT_F16, DT_F16, _Float16, _Float16, _Float16)
+    ORACLE_CASE(DT_BF16, DT_F32, DT_F32, bf16_t, float, float)
+    ORACLE_CASE(DT_BF16, DT_BF16, DT_F32, bf16_t, bf16_t, float)
+    ORACLE_CASE(DT_BF16, DT_BF16, DT_BF16, bf16_t, bf16_t, bf16c_t)
+    ORACLE_CASE(DT_E4M3, DT_F32, DT_F32, e4m3_t, float, float)
+    ORACLE_CASE(DT_E4M3, DT_BF16, DT_F32, e4m3_t, bf16_t, float)
+    ORACLE_CASE(DT_E5M2, DT_F32, DT_F32, e5m2_t, float, float)
+    ORACLE_CASE(DT_E5M2, DT_BF16, DT_F32, e5m2_t, bf16_t, float)
+    ORACLE_CASE(DT_I8, DT_I32, DT_I32, int8_t, int32_t, int32_t)
+    ORACLE_CASE(DT_I8, DT_I8, DT_I32, int8_t, int8_t, int32_t)
+    ORACLE_CASE(DT_F32, DT_F32, DT_F32, float, float, float)
+    ORACLE_CASE(DT_XF32, DT_F32, DT_F32, float, float, float)
+    ORACLE_CASE(DT_F64, DT_F64, DT_F64, double, double, double)
+#undef ORACLE_CASE
+    return -1;
+}
+
 int oracle_gemm(int in_t, int out_t, int literal, uint32_t m, uint32_t n, uint32_t k,
                 void const* a, void const* b, void const* c, void* d, uint32_t lda, uint32_t ldb,
                 uint32_t ldc, uint32_t ldd, double alpha, double beta, int layoutA, int layoutB,
                 int layoutC, int layoutD)
 {
-#define ORACLE_CASE(I, O, IT, OT, CT)                                                       \
-    if(in_t == I && out_t == O)                                                             \
-        return gemm_run<IT, OT, CT>(literal, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, \
-                                    beta, layoutA, layoutB, layoutC, layoutD);
-    ORACLE_CASE(DT_F16, DT_F32, _Float16, float, float)
-    ORACLE_CASE(DT_F16, DT_F16, _Float16, _Float16, float)
-    ORACLE_CASE(DT_BF16, DT_F32, bf16_t, float, float)
-    ORACLE_CASE(DT_BF16, DT_BF16, bf16_t, bf16_t, float)
-    ORACLE_CASE(DT_E4M3, DT_F32, e4m3_t, float, float)
-    ORACLE_CASE(DT_E4M3, DT_BF16, e4m3_t, bf16_t, float)
-    ORACLE_CASE(DT_I8, DT_I32, int8_t, int32_t, int32_t)
-    ORACLE_CASE(DT_F32, DT_F32, float, float, float)
-    ORACLE_CASE(DT_XF32, DT_F32, float, float, float)
-    ORACLE_CASE(DT_F64, DT_F64, double, double, double)
-#undef ORACLE_CASE
-    return -1;
+    return oracle_gemm_ex(in_t, out_t, -1, literal, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha,
+                          beta, layoutA, layoutB, layoutC, layoutD);
 }
 
 int oracle_dlrm_fwd(int dt, void const* input, void* output, uint32_t m, uint32_t k,
@@ -519,6 +638,18 @@ void oracle_decode_e4m3(uint8_t const* src, float* dst, uint64_t n)
 #pragma omp parallel for
     for(int64_t i = 0; i < int64_t(n); ++i)
         dst[i] = decode(e4m3_t{src[i]});
+}
+void oracle_encode_e5m2(float const* src, uint8_t* dst, uint64_t n)
+{
+#pragma omp parallel for
+    for(int64_t i = 0; i < int64_t(n); ++i)
+        dst[i] = encode_e5m2(src[i]).bits;
+}
+void oracle_decode_e5m2(uint8_t const* src, float* dst, uint64_t n)
+{
+#pragma omp parallel for
+    for(int64_t i = 0; i < int64_t(n); ++i)
+        dst[i] = decode(e5m2_t{src[i]});
 }
 void oracle_encode_bf16(float const* src, uint16_t* dst, uint64_t n)
 {

@@ -57,6 +57,39 @@ namespace
         }
     };
 
+    // 8-bit floating-point inputs: storage plus the format-defined (exact) decoding, which
+    // in the reference comes from HIP's fp8 header.  e4m3: bias 7, no infinity, max 448;
+    // e5m2: the upper byte of a binary16 number.
+    struct e4m3_t
+    {
+        uint8_t bits;
+        e4m3_t() = default;
+        explicit operator float() const
+        {
+            const uint32_t e = (bits >> 3) & 0xF, m = bits & 7;
+            float          r;
+            if(e == 0xF && m == 7)
+                r = __builtin_nanf("");
+            else if(e == 0)
+                r = std::ldexp(float(m), -9);
+            else
+                r = std::ldexp(1.0f + float(m) / 8.0f, int(e) - 7);
+            return (bits & 0x80) ? -r : r;
+        }
+    };
+    struct e5m2_t
+    {
+        uint8_t bits;
+        e5m2_t() = default;
+        explicit operator float() const
+        {
+            const uint16_t h = uint16_t(uint16_t(bits) << 8);
+            _Float16       v;
+            __builtin_memcpy(&v, &h, 2);
+            return float(v);
+        }
+    };
+
     template <typename InT, typename OutT, typename CompT, typename LA, typename LB>
     void run(uint32_t m, uint32_t n, uint32_t k, void const* a, void const* b, void const* c,
              void* d, double alpha, double beta)
@@ -83,27 +116,42 @@ namespace
 
 extern "C" {
 
-// gemm_CPU with natural leading dimensions, C and D row-major.  dtype codes:
-// 0 f16, 1 bf16 (inputs only), 3 i8, 4 f32, 6 f64, 7 i32.
+// gemm_CPU with natural leading dimensions, C and D row-major, for the type triple
+// (input, output, compute).  dtype codes: 0 f16, 1 bf16 (inputs only), 2 e4m3 and 8 e5m2
+// (inputs only), 3 i8, 4 f32, 5 xf32 (float storage), 6 f64, 7 i32.  comp_t < 0: the
+// triple's usual compute type.
+int ref_gemm_ex(int in_t, int out_t, int comp_t, uint32_t m, uint32_t n, uint32_t k,
+                void const* a, void const* b, void const* c, void* d, double alpha, double beta,
+                int layoutA, int layoutB)
+{
+    if(comp_t < 0)
+        comp_t = in_t == 3 ? 7 : in_t == 6 ? 6 : 4;
+#define REF_CASE(I, O, C, IT, OT, CT)                                                   \
+    if(in_t == I && out_t == O && comp_t == C)                                          \
+    {                                                                                   \
+        run_layout<IT, OT, CT>(layoutA, layoutB, m, n, k, a, b, c, d, alpha, beta);     \
+        return 0;                                                                       \
+    }
+    REF_CASE(0, 4, 4, _Float16, float, float)
+    REF_CASE(0, 0, 4, _Float16, _Float16, float)
+    REF_CASE(0, 0, 0, _Float16, _Float16, _Float16)
+    REF_CASE(1, 4, 4, bf16_t, float, float)
+    REF_CASE(2, 4, 4, e4m3_t, float, float)
+    REF_CASE(8, 4, 4, e5m2_t, float, float)
+    REF_CASE(3, 7, 7, int8_t, int32_t, int32_t)
+    REF_CASE(3, 3, 7, int8_t, int8_t, int32_t)
+    REF_CASE(4, 4, 4, float, float, float)
+    REF_CASE(5, 4, 4, float, float, float)
+    REF_CASE(6, 6, 6, double, double, double)
+#undef REF_CASE
+    return -1;
+}
+
 int ref_gemm(int in_t, int out_t, uint32_t m, uint32_t n, uint32_t k, void const* a,
              void const* b, void const* c, void* d, double alpha, double beta, int layoutA,
              int layoutB)
 {
-    if(in_t == 0 && out_t == 4)
-        run_layout<_Float16, float, float>(layoutA, layoutB, m, n, k, a, b, c, d, alpha, beta);
-    else if(in_t == 0 && out_t == 0)
-        run_layout<_Float16, _Float16, float>(layoutA, layoutB, m, n, k, a, b, c, d, alpha, beta);
-    else if(in_t == 1 && out_t == 4)
-        run_layout<bf16_t, float, float>(layoutA, layoutB, m, n, k, a, b, c, d, alpha, beta);
-    else if(in_t == 3 && out_t == 7)
-        run_layout<int8_t, int32_t, int32_t>(layoutA, layoutB, m, n, k, a, b, c, d, alpha, beta);
-    else if((in_t == 4 || in_t == 5) && out_t == 4)
-        run_layout<float, float, float>(layoutA, layoutB, m, n, k, a, b, c, d, alpha, beta);
-    else if(in_t == 6 && out_t == 6)
-        run_layout<double, double, double>(layoutA, layoutB, m, n, k, a, b, c, d, alpha, beta);
-    else
-        return -1;
-    return 0;
+    return ref_gemm_ex(in_t, out_t, -1, m, n, k, a, b, c, d, alpha, beta, layoutA, layoutB);
 }
 
 int ref_dlrm_fwd(int dt, void const* input, void* output, uint32_t m, uint32_t k, uint32_t batch)

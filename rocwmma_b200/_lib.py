@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libb200wmma.so")
 TEST_LIB_PATH = os.path.join(_HERE, "lib", "libb200wmma_test.so")
 
 # dtype / layout / status codes (enum b200wmma_dtype etc.)
-F16, BF16, E4M3, I8, F32, XF32, F64, I32 = range(8)
+F16, BF16, E4M3, I8, F32, XF32, F64, I32, E5M2 = range(9)
 ROW_MAJOR, COL_MAJOR = 0, 1
 OK = 0
 ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_CUDA, ERR_DEVICE_WAIT, ERR_TOO_LARGE = (
@@ -29,6 +29,8 @@ SIGNATURES = {
     "b200wmma_status_string": (C.c_char_p, [_i]),
     "b200wmma_gemm_simple": (_i, [_i, _i, _u32, _u32, _u32, _p, _p, _p, _p, _u32, _u32, _u32, _u32,
                                   _d, _d, _i, _i, _i, _i, _p]),
+    "b200wmma_gemm_simple_ex": (_i, [_i, _i, _i, _u32, _u32, _u32, _p, _p, _p, _p, _u32, _u32, _u32,
+                                     _u32, _d, _d, _i, _i, _i, _i, _i, _p]),
     "b200wmma_gemm": (_i, [_i, _i, _u32, _u32, _u32, _p, _p, _p, _p, _u32, _u32, _u32, _u32,
                            _d, _d, _i, _i, _p]),
     "b200wmma_gemm_host": (_i, [_i, _i, _u32, _u32, _u32, _p, _p, _p, _p, _u32, _u32, _u32, _u32,

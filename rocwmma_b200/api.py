@@ -16,11 +16,12 @@ from __future__ import annotations
 import torch
 
 from . import _lib as L
-from ._lib import (BF16, COL_MAJOR, E4M3, F16, F32, F64, I8, I32, ROW_MAJOR, XF32,  # noqa: F401
+from ._lib import (BF16, COL_MAJOR, E4M3, E5M2, F16, F32, F64, I8, I32, ROW_MAJOR, XF32,  # noqa: F401
                    B200WmmaError)
 
 _TORCH = {F16: torch.float16, BF16: torch.bfloat16, E4M3: torch.uint8, I8: torch.int8,
-          F32: torch.float32, XF32: torch.float32, F64: torch.float64, I32: torch.int32}
+          F32: torch.float32, XF32: torch.float32, F64: torch.float64, I32: torch.int32,
+          E5M2: torch.uint8}
 
 
 def torch_dtype(code: int):
@@ -48,8 +49,10 @@ def _natural_ld(layout, rows, cols):
 
 def gemm_simple(in_t, out_t, m, n, k, a, b, c, alpha, beta, layout_a=ROW_MAJOR,
                 layout_b=COL_MAJOR, layout_cd=ROW_MAJOR, block=16, lda=None, ldb=None, ldc=None,
-                ldd=None, out=None, stream=None):
-    """D = alpha*A*B + beta*C, one fragment tile per warp (the simple_*gemm samples)."""
+                ldd=None, out=None, stream=None, compute=None, block_k=0):
+    """D = alpha*A*B + beta*C, one fragment tile per warp (the simple_*gemm samples).
+    compute: rocWMMA's ComputeT as a dtype code (None = the usual one for the input type);
+    block_k: K extent of the fragments (0 = the usual one)."""
     _require_cuda(a, b, c)
     lda = lda or _natural_ld(layout_a, m, k)
     ldb = ldb or _natural_ld(layout_b, k, n)
@@ -57,9 +60,15 @@ def gemm_simple(in_t, out_t, m, n, k, a, b, c, alpha, beta, layout_a=ROW_MAJOR,
     ldd = ldd or _natural_ld(layout_cd, m, n)
     d = out if out is not None else torch.empty(
         (m if layout_cd == ROW_MAJOR else n) * ldd, dtype=_TORCH[out_t], device=a.device)
-    rc = L.lib().b200wmma_gemm_simple(in_t, out_t, m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda,
-                                      ldb, ldc, ldd, float(alpha), float(beta), layout_a, layout_b,
-                                      layout_cd, block, _stream(stream))
+    if compute is None and block_k == 0:
+        rc = L.lib().b200wmma_gemm_simple(in_t, out_t, m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d),
+                                          lda, ldb, ldc, ldd, float(alpha), float(beta), layout_a,
+                                          layout_b, layout_cd, block, _stream(stream))
+    else:
+        rc = L.lib().b200wmma_gemm_simple_ex(in_t, out_t, -1 if compute is None else compute, m, n,
+                                             k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc,
+                                             ldd, float(alpha), float(beta), layout_a, layout_b,
+                                             layout_cd, block, block_k, _stream(stream))
     L.check(rc, "b200wmma_gemm_simple")
     return d
 

@@ -1,6 +1,6 @@
 """Per-configuration throughput of every kernel in the library, one JSON line each.
 
-    python -m rocwmma_b200.bench_all [--only NAME[,NAME...]] [--iters N] [--small]
+    python -m rocwmma_b200.bench_all [--only NAME[,NAME...]] [--iters N] [--small] [--csv FILE]
 
 Covers the configurations the headline benchmark (bench.py at the repository root) does
 not: the simple one-tile-per-warp GEMM, the precision sweep, the quantised GEMMs, GEMV
@@ -9,6 +9,10 @@ bf16 peak scaled per type; GEMV and DLRM report algorithmic bytes / time against
 measured HBM copy bandwidth.  Inputs are random device tensors (timing only; parity is
 the test-suite's job).  Timed with CUDA events over `iters` back-to-back launches after
 3 warm-ups; every working set exceeds the 126 MB L2 except where noted.
+
+--csv FILE also writes the GEMM results as the table rocWMMA's GEMM test programs print
+(header and row format: test/gemm/gemm_kernel_base_impl.hpp:441-523), which its plotting
+script test/bin/GenBenchmarkPlots.py reads.
 """
 from __future__ import annotations
 
@@ -19,7 +23,7 @@ import os
 import torch
 
 from . import api
-from ._lib import BF16, COL_MAJOR, E4M3, F16, F32, F64, I8, I32, ROW_MAJOR, XF32
+from ._lib import BF16, COL_MAJOR, E4M3, E5M2, F16, F32, F64, I8, I32, ROW_MAJOR, XF32
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -61,7 +65,36 @@ def rand(n, code):
     if code == E4M3:
         return (torch.randn(n, device=dev) * 80).clamp(-448, 448).to(torch.float8_e4m3fn).view(
             torch.uint8)
+    if code == E5M2:
+        return (torch.randn(n, device=dev) * 80).to(torch.float8_e5m2).view(torch.uint8)
     raise ValueError(code)
+
+
+# rocWMMA's spellings of the element types in its result tables (dataTypeToString).
+_TYPE_NAME = {F16: "f16", BF16: "bf16", E4M3: "f8", E5M2: "bf8", I8: "i8", I32: "i32",
+              F32: "f32", XF32: "xf32", F64: "f64"}
+_ELEM_BYTES = {F16: 2, BF16: 2, E4M3: 1, E5M2: 1, I8: 1, I32: 4, F32: 4, XF32: 4, F64: 8}
+
+CSV_HEADER = ("TBlkX, TBlkY, BlkM, BlkN, BlkK, MatM, MatN, MatK, alpha, lda, ldb, beta, ldc, ldd, "
+              "LytA_LytB_LytC_LytD, Ti_To_Tc, elapsedMs, Problem Size(GFlops), TFlops/s, "
+              "Efficiency(%), Result")
+
+
+def csv_row(r):
+    g = r["gemm"]
+    comp = I32 if g["in_t"] == I8 else F64 if g["in_t"] == F64 else F32
+    if g["simple"]:
+        tile = (128, 4, 16, 16, 16)       # thread block and fragment of the per-warp kernel
+    elif g["in_t"] == F64:
+        tile = (256, 1, 128, 128, 16)     # block tile of the double-precision kernel
+    else:
+        tile = (192, 1, 256, 256, 128 // _ELEM_BYTES[g["in_t"]])  # CTA-pair tile, one ring slot
+    n = g["size"]
+    fields = [*tile, n, n, n, g["alpha"], n, n, g["beta"], n, n, "row_col_row_row",
+              f"{_TYPE_NAME[g['in_t']]}_{_TYPE_NAME[g['out_t']]}_{_TYPE_NAME[comp]}",
+              f"{r['ms']:.6f}", f"{2.0 * n ** 3 / 1e9:.3f}", f"{r['value']:.3f}",
+              f"{100.0 * r['frac']:.2f}", "BENCH"]
+    return ", ".join(str(f) for f in fields)
 
 
 def gemm_case(name, in_t, out_t, size, alpha, beta, peak_scale, simple=False, iters=20):
@@ -80,6 +113,8 @@ def gemm_case(name, in_t, out_t, size, alpha, beta, peak_scale, simple=False, it
     peak = peak_bf16 * peak_scale if peak_scale else 40.0
     return {"config": name, "ms": ms, "value": tf, "unit": "TFLOP/s", "bound": "tensor",
             "peak": peak, "frac": tf / peak,
+            "gemm": {"in_t": in_t, "out_t": out_t, "size": size, "alpha": alpha, "beta": beta,
+                     "simple": simple},
             "peak_source": (f"{src} bf16 peak x {peak_scale}" if peak_scale
                             else "nominal fp64 tensor 40 TFLOP/s")}
 
@@ -124,6 +159,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="")
     ap.add_argument("--iters", type=int, default=0)
+    ap.add_argument("--csv", default="", help="also write the GEMM results as a rocWMMA-style table")
     ap.add_argument("--small", action="store_true",
                     help="reduced sizes (for profiler captures): GEMMs 2048^3, DLRM b=8192, "
                          "GEMV 8192^2")
@@ -146,15 +182,24 @@ def main():
         "i8": lambda: gemm_case(f"gemm {big}^3 i8->i32", I8, I32, big, 1, 0, 2.0, iters=it(20)),
         "fp8": lambda: gemm_case(f"gemm {big}^3 e4m3->bf16", E4M3, BF16, big, 1.0, 0.0, 2.0,
                                  iters=it(20)),
+        "bf8": lambda: gemm_case(f"gemm {big}^3 e5m2->bf16", E5M2, BF16, big, 1.0, 0.0, 2.0,
+                                 iters=it(20)),
         "sgemv": lambda: gemv_case(8192 if args.small else 16384, iters=it(50)),
         "dlrm": lambda: dlrm_cases(8192 if args.small else 65536, iters=it(20)),
     }
+    rows = []
     for name, fn in cases.items():
         if only and name not in only:
             continue
         res = fn()
         for r in (res if isinstance(res, list) else [res]):
+            if "gemm" in r:
+                rows.append(csv_row(r))
+                r = {k: v for k, v in r.items() if k != "gemm"}
             print(json.dumps(r), flush=True)
+    if args.csv:
+        with open(args.csv, "w") as f:
+            f.write(CSV_HEADER + "\n" + "\n".join(rows) + "\n")
 
 
 if __name__ == "__main__":

@@ -24,7 +24,7 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-li
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
          "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
-PRODUCT = ["runtime.cu", "simple_gemm.cu", "gemm_tcgen05.cu", "gemm_f64.cu", "gemv.cu", "dlrm.cu"]
+PRODUCT = ["runtime.cu", "simple_gemm.cu", "simple_gemm_blockk.cu", "gemm_tcgen05.cu", "gemm_f64.cu", "gemv.cu", "dlrm.cu"]
 TESTLIB = ["test_kernels.cu"]
 
 

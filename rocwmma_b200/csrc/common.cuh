@@ -32,6 +32,7 @@ namespace b200wmma
         case B200WMMA_BF16:
             return 2;
         case B200WMMA_E4M3:
+        case B200WMMA_E5M2:
         case B200WMMA_I8:
             return 1;
         case B200WMMA_F32:

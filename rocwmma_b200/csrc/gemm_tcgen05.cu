@@ -161,6 +161,13 @@ namespace
         static constexpr uint32_t fmt = FMT_E4M3, acc = ACC_F32;
     };
 
+    template <>
+    struct KindOf<__nv_fp8_e5m2>
+    {
+        static constexpr MmaKind  kind = MmaKind::F8F6F4;
+        static constexpr uint32_t fmt = FMT_E5M2, acc = ACC_F32;
+    };
+
     __device__ inline void tileCoord(uint32_t t, uint32_t tilesM, uint32_t tilesN, uint32_t band,
                                      uint32_t& tm, uint32_t& tn)
     {
@@ -1400,6 +1407,10 @@ extern "C" int b200wmma_gemm(int in_dtype, int out_dtype, uint32_t m, uint32_t n
     B200WMMA_GEMM_CASE(B200WMMA_E4M3, B200WMMA_BF16, __nv_fp8_e4m3, __nv_bfloat16, float,
                        CU_TENSOR_MAP_DATA_TYPE_UINT8)
     B200WMMA_GEMM_CASE(B200WMMA_E4M3, B200WMMA_F32, __nv_fp8_e4m3, float, float,
+                       CU_TENSOR_MAP_DATA_TYPE_UINT8)
+    B200WMMA_GEMM_CASE(B200WMMA_E5M2, B200WMMA_BF16, __nv_fp8_e5m2, __nv_bfloat16, float,
+                       CU_TENSOR_MAP_DATA_TYPE_UINT8)
+    B200WMMA_GEMM_CASE(B200WMMA_E5M2, B200WMMA_F32, __nv_fp8_e5m2, float, float,
                        CU_TENSOR_MAP_DATA_TYPE_UINT8)
 #undef B200WMMA_GEMM_CASE
     if(in_dtype == B200WMMA_F64 && out_dtype == B200WMMA_F64)

@@ -1,125 +1,16 @@
-// One-tile-per-warp GEMM written on the fragment API, and its C launcher.
-//
-// Same algorithm and call sites as the reference's simple GEMM samples
-// (samples/simple_hgemm.cpp:81-139; simple_sgemm.cpp:81; simple_dgemm.cpp:81):
-// each warp owns one BlockM x BlockN tile of D, walks K in BlockK steps with
-// load_matrix_sync / mma_sync, then scales element-wise across two accumulator
-// fragments of different types and stores.  The thread block is
-// (4 * 32, 4) = 16 warps as in the sample (samples/simple_hgemm.cpp:64-65).
-#include "common.cuh"
-#include <rocwmma/rocwmma.hpp>
+// C launchers of the one-tile-per-warp GEMM (kernel: simple_gemm.cuh), each type's usual
+// fragment K extent.
+#include "simple_gemm.cuh"
 
-using namespace rocwmma;
+using namespace b200wmma::simple;
 
 namespace
 {
-    constexpr uint32_t T_BLOCK_X = 4 * Constants::AMDGCN_WAVE_SIZE;
-    constexpr uint32_t T_BLOCK_Y = 4;
-
-    template <typename InT,
-              typename OutT,
-              typename CompT,
-              typename LayoutA,
-              typename LayoutB,
-              uint32_t BM,
-              uint32_t BN,
-              uint32_t BK>
-    __global__ void __launch_bounds__(T_BLOCK_X* T_BLOCK_Y)
-        gemm_simple_d(uint32_t    m,
-                      uint32_t    n,
-                      uint32_t    k,
-                      InT const*  a,
-                      InT const*  b,
-                      OutT const* c,
-                      OutT*       d,
-                      uint32_t    lda,
-                      uint32_t    ldb,
-                      uint32_t    ldc,
-                      uint32_t    ldd,
-                      CompT       alpha,
-                      CompT       beta,
-                      layout_t    layoutCD)
-    {
-        auto fragA   = fragment<matrix_a, BM, BN, BK, InT, LayoutA>();
-        auto fragB   = fragment<matrix_b, BM, BN, BK, InT, LayoutB>();
-        auto fragC   = fragment<accumulator, BM, BN, BK, OutT>();
-        auto fragAcc = fragment<accumulator, BM, BN, BK, CompT>();
-
-        fill_fragment(fragAcc, CompT(0));
-
-        // Tile using a 2D grid: warps along x own tile rows, along y tile columns.
-        auto majorWarp = (blockIdx.x * blockDim.x + threadIdx.x) / Constants::AMDGCN_WAVE_SIZE;
-        auto minorWarp = (blockIdx.y * blockDim.y + threadIdx.y);
-
-        auto cRow = majorWarp * BM;
-        auto cCol = minorWarp * BN;
-
-        if(cRow < m && cCol < n)
-        {
-            constexpr bool aRow = std::is_same<LayoutA, row_major>::value;
-            constexpr bool bRow = std::is_same<LayoutB, row_major>::value;
-            for(uint32_t i = 0; i < k; i += BK)
-            {
-                load_matrix_sync(fragA, a + (aRow ? (cRow * lda + i) : (i * lda + cRow)), lda);
-                load_matrix_sync(fragB, b + (bRow ? (i * ldb + cCol) : (i + cCol * ldb)), ldb);
-                mma_sync(fragAcc, fragA, fragB, fragAcc);
-            }
-
-            const bool     cdRow = (layoutCD == mem_row_major);
-            const uint32_t cOff  = cdRow ? (cRow * ldc + cCol) : (cRow + cCol * ldc);
-            const uint32_t dOff  = cdRow ? (cRow * ldd + cCol) : (cRow + cCol * ldd);
-
-            load_matrix_sync(fragC, c + cOff, ldc, layoutCD);
-
-            for(uint32_t i = 0; i < fragC.num_elements; ++i)
-            {
-                // OutputT(alpha * acc + beta * ComputeT(c)), in ComputeT arithmetic
-                fragC.x[i] = OutT(alpha * fragAcc.x[i] + beta * CompT(fragC.x[i]));
-            }
-
-            store_matrix_sync(d + dOff, fragC, ldd, layoutCD);
-        }
-    }
-
-    template <typename InT, typename OutT, typename CompT, typename LA, typename LB, uint32_t BM,
-              uint32_t BN, uint32_t BK>
-    int launch(uint32_t m, uint32_t n, uint32_t k, void const* a, void const* b, void const* c,
-               void* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, double alpha,
-               double beta, int layoutCD, cudaStream_t stream)
-    {
-        if(m % BM || n % BN || k % BK)
-            return B200WMMA_ERR_INVALID_ARG;
-        dim3 block(T_BLOCK_X, T_BLOCK_Y);
-        dim3 grid(ceilDiv(m, BM * T_BLOCK_X / Constants::AMDGCN_WAVE_SIZE),
-                  ceilDiv(n, BN * T_BLOCK_Y));
-        gemm_simple_d<InT, OutT, CompT, LA, LB, BM, BN, BK><<<grid, block, 0, stream>>>(
-            m, n, k, static_cast<InT const*>(a), static_cast<InT const*>(b),
-            static_cast<OutT const*>(c), static_cast<OutT*>(d), lda, ldb, ldc, ldd, CompT(alpha),
-            CompT(beta), layoutCD == B200WMMA_ROW_MAJOR ? mem_row_major : mem_col_major);
-        return b200wmma::cudaToStatus(cudaGetLastError());
-    }
-
-    template <typename InT, typename OutT, typename CompT, uint32_t BM, uint32_t BN, uint32_t BK,
-              typename... Args>
-    int launchLayouts(int la, int lb, Args... args)
-    {
-        if(la == B200WMMA_ROW_MAJOR && lb == B200WMMA_ROW_MAJOR)
-            return launch<InT, OutT, CompT, row_major, row_major, BM, BN, BK>(args...);
-        if(la == B200WMMA_ROW_MAJOR && lb == B200WMMA_COL_MAJOR)
-            return launch<InT, OutT, CompT, row_major, col_major, BM, BN, BK>(args...);
-        if(la == B200WMMA_COL_MAJOR && lb == B200WMMA_ROW_MAJOR)
-            return launch<InT, OutT, CompT, col_major, row_major, BM, BN, BK>(args...);
-        if(la == B200WMMA_COL_MAJOR && lb == B200WMMA_COL_MAJOR)
-            return launch<InT, OutT, CompT, col_major, col_major, BM, BN, BK>(args...);
-        return B200WMMA_ERR_INVALID_ARG;
-    }
-
-    // BlockK per element width: 16 everywhere except 32x32 tiles of 8-bit types.
-    template <typename InT, typename OutT, typename CompT, typename... Args>
-    int launchBlock(int block, int la, int lb, Args... args)
+    template <typename InT, typename OutT, typename CompT>
+    int launchDefault(int block, Args const& g)
     {
         if(block == 16)
-            return launchLayouts<InT, OutT, CompT, 16, 16, 16>(la, lb, args...);
+            return launchTile<InT, OutT, CompT, 16, 16, 16>(g);
         if(block == 32)
         {
             // 64-bit fragments exist as 16x16 only, as in the reference
@@ -127,13 +18,48 @@ namespace
             if constexpr(sizeof(InT) == 8)
                 return B200WMMA_ERR_UNSUPPORTED;
             else if constexpr(sizeof(InT) == 1)
-                return launchLayouts<InT, OutT, CompT, 32, 32, 32>(la, lb, args...);
+                return launchTile<InT, OutT, CompT, 32, 32, 32>(g);
             else
-                return launchLayouts<InT, OutT, CompT, 32, 32, 16>(la, lb, args...);
+                return launchTile<InT, OutT, CompT, 32, 32, 16>(g);
         }
         return B200WMMA_ERR_UNSUPPORTED;
     }
+
+    // The compute type a (input, output) pair gets when the caller names none.
+    int defaultCompute(int in_dtype)
+    {
+        return in_dtype == B200WMMA_I8 ? B200WMMA_I32
+               : in_dtype == B200WMMA_F64 ? B200WMMA_F64
+                                          : B200WMMA_F32;
+    }
 } // namespace
+
+extern "C" int b200wmma_gemm_simple_ex(int in_dtype, int out_dtype, int compute_dtype, uint32_t m,
+                                       uint32_t n, uint32_t k, const void* a, const void* b,
+                                       const void* c, void* d, uint32_t lda, uint32_t ldb,
+                                       uint32_t ldc, uint32_t ldd, double alpha, double beta,
+                                       int layout_a, int layout_b, int layout_cd, int block,
+                                       int block_k, void* stream)
+{
+    if(!a || !b || !c || !d || m == 0 || n == 0 || k == 0)
+        return B200WMMA_ERR_INVALID_ARG;
+    if(layout_cd != B200WMMA_ROW_MAJOR && layout_cd != B200WMMA_COL_MAJOR)
+        return B200WMMA_ERR_INVALID_ARG;
+    if(compute_dtype < 0)
+        compute_dtype = defaultCompute(in_dtype);
+    const Args g{m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b,
+                 layout_cd, static_cast<cudaStream_t>(stream)};
+#define B200WMMA_SIMPLE_CASE(I, O, C, IT, OT, CT)                                    \
+    if(in_dtype == I && out_dtype == O && compute_dtype == C)                        \
+    {                                                                                \
+        if(block_k == 0 || uint32_t(block_k) == defaultBlockK<IT>(uint32_t(block)))  \
+            return launchDefault<IT, OT, CT>(block, g);                              \
+        return launchOtherBlockK(in_dtype, out_dtype, compute_dtype, block, block_k, g); \
+    }
+    B200WMMA_SIMPLE_TRIPLES(B200WMMA_SIMPLE_CASE)
+#undef B200WMMA_SIMPLE_CASE
+    return B200WMMA_ERR_UNSUPPORTED;
+}
 
 extern "C" int b200wmma_gemm_simple(int in_dtype, int out_dtype, uint32_t m, uint32_t n,
                                     uint32_t k, const void* a, const void* b, const void* c,
@@ -141,24 +67,6 @@ extern "C" int b200wmma_gemm_simple(int in_dtype, int out_dtype, uint32_t m, uin
                                     uint32_t ldd, double alpha, double beta, int layout_a,
                                     int layout_b, int layout_cd, int block, void* stream)
 {
-    if(!a || !b || !c || !d || m == 0 || n == 0 || k == 0)
-        return B200WMMA_ERR_INVALID_ARG;
-    if(layout_cd != B200WMMA_ROW_MAJOR && layout_cd != B200WMMA_COL_MAJOR)
-        return B200WMMA_ERR_INVALID_ARG;
-    auto s = static_cast<cudaStream_t>(stream);
-#define B200WMMA_SIMPLE_CASE(I, O, IT, OT, CT)                                                  \
-    if(in_dtype == I && out_dtype == O)                                                         \
-        return launchBlock<IT, OT, CT>(block, layout_a, layout_b, m, n, k, a, b, c, d, lda, ldb, \
-                                       ldc, ldd, alpha, beta, layout_cd, s);
-    B200WMMA_SIMPLE_CASE(B200WMMA_F16, B200WMMA_F32, float16_t, float32_t, float32_t)
-    B200WMMA_SIMPLE_CASE(B200WMMA_F16, B200WMMA_F16, float16_t, float16_t, float32_t)
-    B200WMMA_SIMPLE_CASE(B200WMMA_BF16, B200WMMA_F32, bfloat16_t, float32_t, float32_t)
-    B200WMMA_SIMPLE_CASE(B200WMMA_BF16, B200WMMA_BF16, bfloat16_t, bfloat16_t, float32_t)
-    B200WMMA_SIMPLE_CASE(B200WMMA_E4M3, B200WMMA_F32, float8_t, float32_t, float32_t)
-    B200WMMA_SIMPLE_CASE(B200WMMA_I8, B200WMMA_I32, int8_t, int32_t, int32_t)
-    B200WMMA_SIMPLE_CASE(B200WMMA_F32, B200WMMA_F32, float32_t, float32_t, float32_t)
-    B200WMMA_SIMPLE_CASE(B200WMMA_XF32, B200WMMA_F32, xfloat32_t, float32_t, float32_t)
-    B200WMMA_SIMPLE_CASE(B200WMMA_F64, B200WMMA_F64, float64_t, float64_t, float64_t)
-#undef B200WMMA_SIMPLE_CASE
-    return B200WMMA_ERR_UNSUPPORTED;
+    return b200wmma_gemm_simple_ex(in_dtype, out_dtype, -1, m, n, k, a, b, c, d, lda, ldb, ldc, ldd,
+                                   alpha, beta, layout_a, layout_b, layout_cd, block, 0, stream);
 }

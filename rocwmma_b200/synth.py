@@ -15,11 +15,11 @@ from __future__ import annotations
 
 import numpy as np
 
-F16, BF16, E4M3, I8, F32, XF32, F64, I32 = range(8)
+F16, BF16, E4M3, I8, F32, XF32, F64, I32, E5M2 = range(9)
 CHUNK_ROWS = 128
 
 NP_DTYPE = {F16: np.float16, BF16: np.uint16, E4M3: np.uint8, I8: np.int8, F32: np.float32,
-            XF32: np.float32, F64: np.float64, I32: np.int32}
+            XF32: np.float32, F64: np.float64, I32: np.int32, E5M2: np.uint8}
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
@@ -64,6 +64,31 @@ def e4m3_bits_to_f32(b: np.ndarray) -> np.ndarray:
     return np.where(s == 1, -val, val).astype(np.float32)
 
 
+def f32_to_e5m2_bits(x: np.ndarray) -> np.ndarray:
+    """float32 -> OCP e5m2 bits, round to nearest even, saturate to +-57344 (no infinities)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    sign = ((x.view(np.uint32) >> 24) & 0x80).astype(np.uint8)
+    a = np.abs(x).astype(np.float64)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        e = np.floor(np.log2(np.where(a > 0, a, 1.0))).astype(np.int64)
+    e = np.maximum(e, -14)
+    q = np.rint(a * np.exp2(2 - e)).astype(np.int64)
+    carry = q == 8
+    q = np.where(carry, 4, q)
+    e = np.where(carry, e + 1, e)
+    bits = np.where(q >= 4, ((e + 15) << 2) | (q - 4), q)
+    out = bits.astype(np.uint8)
+    out = np.where(a >= 57344.0, 0x7B, out).astype(np.uint8)
+    out = np.where(a < 2.0 ** -17, 0, out).astype(np.uint8)
+    out = np.where(np.isnan(x), 0x7F, out).astype(np.uint8)
+    return out | sign
+
+
+def e5m2_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    """e5m2 is the upper byte of a binary16 number."""
+    return (b.astype(np.uint16) << 8).view(np.float16).astype(np.float32)
+
+
 def truncate_xf32(x: np.ndarray) -> np.ndarray:
     u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32) & np.uint32(0xFFFFE000)
     return u.view(np.float32)
@@ -80,6 +105,8 @@ def _encode(x: np.ndarray, dtype: int) -> np.ndarray:
         return f32_to_bf16_bits(x.astype(np.float32))
     if dtype == E4M3:
         return f32_to_e4m3_bits(x.astype(np.float32))
+    if dtype == E5M2:
+        return f32_to_e5m2_bits(x.astype(np.float32))
     if dtype == XF32:
         return truncate_xf32(x.astype(np.float32))
     if dtype == F32:

@@ -52,7 +52,8 @@ def gemm_outputs():
     for name, case in GEMM_GOLDEN_CASES.items():
         a, b, c = gemm_inputs(case)
         d = O.ref_gemm(case["in_t"], case["out_t"], case["m"], case["n"], case["k"], a, b, c,
-                       case["alpha"], case["beta"], case["la"], case["lb"])
+                       case["alpha"], case["beta"], case["la"], case["lb"],
+                       comp_t=case.get("comp_t"))
         out[name] = d
     np.savez_compressed(os.path.join(HERE, "gemm_ref_outputs.npz"), **out)
 

@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 ROW, COL = 0, 1
 
 
-ELEM = {O.F16: 2, O.BF16: 2, O.E4M3: 1, O.I8: 1, O.F32: 4, O.XF32: 4, O.F64: 8, O.I32: 4}
+ELEM = {O.F16: 2, O.BF16: 2, O.E4M3: 1, O.I8: 1, O.F32: 4, O.XF32: 4, O.F64: 8, O.I32: 4,
+        O.E5M2: 1}
 
 
 def _pad_ld(extent, dtype_code):

@@ -55,7 +55,8 @@ def test_gemm_matches_reference_host_code(name, golden_dir):
     a, b, c = gemm_inputs(case)
     for literal in (False, True):
         got = O.gemm(case["in_t"], case["out_t"], case["m"], case["n"], case["k"], a, b, c,
-                     case["alpha"], case["beta"], case["la"], case["lb"], literal=literal)
+                     case["alpha"], case["beta"], case["la"], case["lb"], literal=literal,
+                     comp_t=case.get("comp_t"))
         assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (name, literal)
 
 
@@ -87,6 +88,62 @@ def test_live_reference_build_agrees():
     got = O.gemm(O.F16, O.F32, m, n, k, a, b, c, 1.5, 0.5)
     want = O.ref_gemm(O.F16, O.F32, m, n, k, a, b, c, 1.5, 0.5)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.skipif(not os.path.isdir("/root/reference"), reason="reference tree not mounted")
+@pytest.mark.parametrize("triple", [(O.F16, O.F16, O.F16), (O.I8, O.I8, O.I32),
+                                    (O.E4M3, O.F32, O.F32), (O.E5M2, O.F32, O.F32)])
+def test_live_reference_build_agrees_on_other_type_triples(triple):
+    it, ot, ct = triple
+    rng = np.random.default_rng(9)
+    m, n, k = 24, 40, 96
+
+    def draw(dt, count):
+        if dt == O.I8:
+            return rng.integers(-128, 128, count).astype(np.int8)
+        v = rng.standard_normal(count).astype(np.float32)
+        return {O.F16: lambda: v.astype(np.float16), O.F32: lambda: v,
+                O.E4M3: lambda: O.encode_e4m3(v), O.E5M2: lambda: O.encode_e5m2(v)}[dt]()
+
+    a, b, c = draw(it, m * k), draw(it, k * n), draw(ot, m * n)
+    alpha, beta = (3, -2) if it == O.I8 else (2.0, -1.0)
+    want = O.ref_gemm(it, ot, m, n, k, a, b, c, alpha, beta, comp_t=ct)
+    for literal in (False, True):
+        got = O.gemm(it, ot, m, n, k, a, b, c, alpha, beta, comp_t=ct, literal=literal)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (triple, literal)
+
+
+def test_e5m2_codec():
+    """e5m2 is the upper byte of binary16; the encoder rounds to nearest even, saturates to
+    +-57344 and agrees with the input generators' numpy encoder."""
+    from rocwmma_b200 import synth
+    codes = np.arange(256, dtype=np.uint8)
+    dec = O.decode_e5m2(codes)
+    via16 = (codes.astype(np.uint16) << 8).view(np.float16).astype(np.float32)
+    assert np.array_equal(np.isnan(dec), np.isnan(via16))
+    assert np.array_equal(dec[~np.isnan(dec)], via16[~np.isnan(via16)])
+    fin = np.isfinite(dec) & (dec != 0)
+    assert np.array_equal(O.encode_e5m2(dec[fin]), codes[fin])
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal(50000) * np.exp(rng.uniform(-14, 12, 50000))).astype(np.float32)
+    x[:6] = [0.0, 57344.0, 61000.0, -1e9, 2.0 ** -17, 1.5 * 2.0 ** -16]
+    enc = O.encode_e5m2(x)
+    assert np.array_equal(enc, synth.f32_to_e5m2_bits(x))
+    assert enc[1] == 0x7B and enc[2] == 0x7B and enc[3] == 0xFB and enc[4] == 0
+    assert enc[5] == 2  # tie between 1 and 2 units of 2^-16: to even
+
+
+def test_bf16_compute_type_rounds_every_operation():
+    """BF16 / BF16 / BF16: blocked and literal forms agree; 64 products rounded one by one
+    to 8 significant bits leave visible noise against fp32 compute, but only noise."""
+    rng = np.random.default_rng(4)
+    m, n, k = 16, 24, 64
+    a, b, c = (O.encode_bf16(rng.standard_normal(s)) for s in (m * k, k * n, m * n))
+    d16 = O.gemm(O.BF16, O.BF16, m, n, k, a, b, c, 2.0, -1.0, comp_t=O.BF16)
+    lit = O.gemm(O.BF16, O.BF16, m, n, k, a, b, c, 2.0, -1.0, comp_t=O.BF16, literal=True)
+    d32 = O.gemm(O.BF16, O.BF16, m, n, k, a, b, c, 2.0, -1.0)
+    assert np.array_equal(d16, lit)
+    assert 0 < O.max_rel_err(O.BF16, d16, d32) < 0.3
 
 
 def test_leading_dimensions_and_cd_layouts():

@@ -25,3 +25,21 @@ def test_distributions_and_encodings():
     assert set(np.unique(np.abs(p))) <= {0, 1, 2, 3, 4}
     e = synth.rows(1, 6, synth.E4M3, 0, 128, 64, dist="normal", scale=100.0)
     assert np.abs(synth.e4m3_bits_to_f32(e)).max() <= 448
+
+
+def test_benchmark_table_rows_match_the_reference_header():
+    """bench_all --csv writes rocWMMA's result table: one value per header column."""
+    from rocwmma_b200 import bench_all as B
+    cols = [c.strip() for c in B.CSV_HEADER.split(",")]
+    assert cols[:5] == ["TBlkX", "TBlkY", "BlkM", "BlkN", "BlkK"] and cols[-1] == "Result"
+    for simple, in_t, out_t in [(True, B.F16, B.F32), (False, B.E5M2, B.BF16),
+                                (False, B.F64, B.F64), (False, B.I8, B.I32)]:
+        r = {"ms": 0.5, "value": 100.0, "frac": 0.25,
+             "gemm": {"in_t": in_t, "out_t": out_t, "size": 1024, "alpha": 1.0, "beta": 0.0,
+                      "simple": simple}}
+        row = [c.strip() for c in B.csv_row(r).split(",")]
+        assert len(row) == len(cols)
+        assert row[cols.index("Result")] == "BENCH"
+        assert row[cols.index("Efficiency(%)")] == "25.00"
+    assert "bf8_bf16_f32" in B.csv_row({"ms": 1, "value": 1, "frac": 1, "gemm": {
+        "in_t": B.E5M2, "out_t": B.BF16, "size": 64, "alpha": 1, "beta": 0, "simple": False}})
