@@ -450,21 +450,31 @@ namespace
 
         // The packed upstream row of a sample is only 2-byte aligned, and each value is used
         // once, so it never goes through shared memory: a lane reads its share of the NEXT
-        // sample's triangle (entries lane, lane+32, ...) into registers one iteration ahead;
-        // a warp-wide 2-byte load covers 64 contiguous bytes.
+        // sample's row (entries lane, lane+32, ... of the first k values and of the triangle)
+        // into registers one iteration ahead, so that no instruction of the current sample
+        // waits for a load from global memory; a warp-wide 2-byte load covers 64 contiguous
+        // bytes.
         constexpr uint32_t TRI_REGS = 16; // ceil(496 / 32) for m = 32
-        __half             triNext[TRI_REGS];
-        auto prefetchTriangle = [&](uint32_t q) {
+        constexpr uint32_t MLP_REGS = MAX_K / 32;
+        __half             triNext[TRI_REGS], mlpNext[MLP_REGS];
+        auto prefetchUpstream = [&](uint32_t q) {
             const uint32_t s = feed.sample(q);
             if(s < sh.batch)
             {
-                __half const* src = upstream + size_t(s) * sh.outLen + sh.k;
+                __half const* src = upstream + size_t(s) * sh.outLen;
+#pragma unroll
+                for(uint32_t i = 0; i < MLP_REGS; ++i)
+                {
+                    const uint32_t idx = i * 32u + lane;
+                    if(idx < sh.k)
+                        mlpNext[i] = src[idx];
+                }
 #pragma unroll
                 for(uint32_t i = 0; i < TRI_REGS; ++i)
                 {
                     const uint32_t idx = i * 32u + lane;
                     if(idx < triCount)
-                        triNext[i] = src[idx];
+                        triNext[i] = src[sh.k + idx];
                 }
             }
         };
@@ -472,7 +482,7 @@ namespace
 #pragma unroll
         for(uint32_t q = 0; q < NSTAGES - 1; ++q)
             fill(q);
-        prefetchTriangle(0);
+        prefetchUpstream(0);
 
         const uint32_t lmRow = ((lane >> 3) & 1u) * 8u + (lane & 7u);
         const uint32_t lmCol = (lane >> 4) * 8u;
@@ -491,19 +501,17 @@ namespace
             uint8_t*       slotPtr  = mine + (q % NSTAGES) * sh.stageBytes;
             const uint32_t slotAddr = ring.slotAddr(q % NSTAGES);
 
-            // this sample's triangle (fetched one iteration ago), then start on the next one's
-            __half triCur[TRI_REGS];
-#pragma unroll
-            for(uint32_t i = 0; i < TRI_REGS; ++i)
-                triCur[i] = triNext[i];
-            prefetchTriangle(q + 1);
-
-            // bottom-MLP gradient: the first k upstream values, copied as they are
+            // bottom-MLP gradient: the first k upstream values (fetched one iteration ago),
+            // copied as they are
             {
-                __half const* up  = upstream + size_t(sample) * sh.outLen;
-                __half*       dst = mlpGrad + size_t(sample) * sh.k;
-                for(uint32_t j = lane; j < sh.k; j += 32)
-                    dst[j] = up[j];
+                __half* dst = mlpGrad + size_t(sample) * sh.k;
+#pragma unroll
+                for(uint32_t i = 0; i < MLP_REGS; ++i)
+                {
+                    const uint32_t idx = i * 32u + lane;
+                    if(idx < sh.k)
+                        dst[idx] = mlpNext[i];
+                }
             }
 
             // symmetric G (fp16, zero diagonal) from the packed triangle
@@ -514,11 +522,13 @@ namespace
                 if(idx < triCount)
                 {
                     const uint32_t at = tri[idx];
-                    gTile[at & 0xffffu] = triCur[i];
-                    gTile[at >> 16]     = triCur[i];
+                    gTile[at & 0xffffu] = triNext[i];
+                    gTile[at >> 16]     = triNext[i];
                 }
             }
             __syncwarp();
+            // the registers are free again: start on the next sample's row
+            prefetchUpstream(q + 1);
 
             // A fragments of G: [mt][kt]
             uint32_t ga[2][2][4];
