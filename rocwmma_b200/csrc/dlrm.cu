@@ -9,15 +9,15 @@
 // bound by HBM bandwidth, so here each pass is ONE kernel that touches every input
 // and output byte exactly once:
 //
-//   * a warp owns whole samples; eight consecutive samples form a group so that the
-//     packed [k + m(m-1)/2]-wide rows, which are only 2-byte aligned one by one, start
-//     on a 16-byte boundary as a group;
+//   * a warp owns whole samples, handed out in groups of eight consecutive ones; the
+//     packed [k + m(m-1)/2]-wide rows are only 2-byte aligned, so the forward pass stages
+//     a row at the offset from a 16-byte boundary that it has in global memory and writes
+//     all but its first and last few values with 128-bit stores;
 //   * samples stream through a per-warp cp.async ring in shared memory (16-byte pieces into
-//     rows padded by 16 bytes, so that ldmatrix is conflict-free).  A finished group of
-//     packed forward rows leaves as ONE bulk copy (cp.async.bulk shared -> global, 16 x
-//     outLen bytes).  Bulk copies per 256-byte row, for the loads or for the gradient,
-//     were slower than 16-byte cp.async / 128-bit stores: the copy engine took about 17
-//     cycles per request.
+//     rows padded by 16 bytes, so that ldmatrix is conflict-free).  Bulk copies
+//     (cp.async.bulk) per 256-byte row, for the loads or for the gradient, were slower
+//     than 16-byte cp.async / 128-bit stores: the copy engine took about 17 cycles per
+//     request;
 //   * the m x m (forward) and m x k (backward) products run on warp-level tensor-core
 //     instructions (mma.sync m16n8k16, fp32 accumulate) with m padded to 32 by a shared
 //     row of zeros; nothing is written to global scratch;
@@ -30,18 +30,18 @@
 //
 // Limits: fp16, m <= 32, k a multiple of 16 and <= 256, pointers 16-byte aligned.
 #include "common.cuh"
-#include "rocwmma/rocwmma_block.hpp"
 #include "runtime.cuh"
 #include <cstdlib>
 #include <cuda_fp16.h>
 
 namespace
 {
-    namespace blk = rocwmma::block;
-
     constexpr uint32_t GROUP      = 8; // samples per aligned group
     constexpr uint32_t MAX_K      = 256;
     constexpr uint32_t G_LD       = 40; // halves per row of the 32x32 G tile (80 bytes)
+    // Warps per block.  The backward pass cannot have more (168 registers per thread); the
+    // forward pass could (shared memory allows 14 at 27 x 128) but measured best at 11-12:
+    // 5.28, 5.68, 5.69, 5.56, 5.39 TB/s with 10, 11, 12, 13, 14 warps.
     constexpr uint32_t MAX_WARPS  = 12;
     constexpr uint32_t ZERO_BYTES = MAX_K * 2 + 16;
 
@@ -189,6 +189,13 @@ namespace
         return (m * (m - 1) / 2 * 4 + 15) / 16 * 16;
     }
 
+    // Forward pass: staging for one packed output row, placed up to 14 bytes into the
+    // buffer so that it has the alignment it will have in global memory.
+    __host__ __device__ inline uint32_t fwdStagingBytes(uint32_t outLen)
+    {
+        return (outLen * 2u + 14u + 15u) / 16u * 16u;
+    }
+
     // One warp's ring of staged samples.  A sample is m rows of k halves, contiguous in
     // global memory; in a slot its rows are rowStride bytes apart.  A lane moves the 16-byte
     // pieces lane, lane + 32, ...; the slot offset of piece c needs c / chunksPerRow, which
@@ -250,8 +257,7 @@ namespace
         const uint32_t g = lane >> 2, t = lane & 3;
 
         // layout: [zero row][warp 0: ring slots, out staging][warp 1: ...]
-        const uint32_t outStageBytes = GROUP * sh.outLen * 2; // multiple of 16
-        const uint32_t perWarp       = NSTAGES * sh.stageBytes + outStageBytes;
+        const uint32_t perWarp       = NSTAGES * sh.stageBytes + fwdStagingBytes(sh.outLen);
         uint8_t*       zeroRow       = smem;
         uint8_t*       mine          = smem + ZERO_BYTES + warp * perWarp;
         __half*        outStage      = reinterpret_cast<__half*>(mine + NSTAGES * sh.stageBytes);
@@ -315,7 +321,6 @@ namespace
             fill(q + NSTAGES - 1);
 
             const uint32_t sample = feed.sample(q);
-            const uint32_t slot   = q % GROUP;
             if(sample < sh.batch)
             {
                 const uint32_t slotAddr = ring.slotAddr(q % NSTAGES);
@@ -343,15 +348,13 @@ namespace
                 for(uint32_t kk = 16; kk < sh.k; kk += 16)
                     kStep(FalseT{}, kk);
 
-                // The staging rows of the previous group may still be on their way out.
-                if(slot == 0)
-                {
-                    if(lane == 0)
-                        blk::tma_store_wait_read<0>();
-                    __syncwarp();
-                }
+                // The packed row of a sample starts on a 2-byte boundary only.  It is staged
+                // at the same offset from a 16-byte boundary as it has in global memory, so
+                // that all but its first and last few values leave with 128-bit stores.
+                const size_t   gByte = size_t(sample) * sh.outLen * 2u;
+                const uint32_t shift = uint32_t(gByte) & 15u;
                 // row 0 of the sample, then the strict lower triangle
-                __half*       dst   = outStage + slot * sh.outLen;
+                __half*       dst   = outStage + shift / 2u;
                 __half const* row0p = reinterpret_cast<__half const*>(
                     mine + (q % NSTAGES) * sh.stageBytes);
                 for(uint32_t j = lane; j < sh.k; j += 32)
@@ -366,37 +369,27 @@ namespace
                         stSharedIf(at, __float2half_rn(acc[i][2 * h]), (v >> 16) & 1u);
                         stSharedIf(at + 2u, __float2half_rn(acc[i][2 * h + 1]), (v >> 17) & 1u);
                     }
-            }
+                __syncwarp();
 
-            // end of a group: its packed rows are contiguous in the output and start on a
-            // 16-byte boundary -- one bulk copy when the group is complete
-            if(slot == GROUP - 1)
-            {
-                const uint32_t first = feed.g0 * GROUP;
-                const uint32_t cnt   = min(GROUP, sh.batch - first);
-                __half*        gout  = output + size_t(first) * sh.outLen;
-                if(cnt == GROUP)
-                {
-                    blk::fence_async_shared();
-                    __syncwarp();
-                    if(lane == 0)
-                    {
-                        blk::bulk_store(gout, smemAddr(outStage), outStageBytes);
-                        blk::tma_store_commit();
-                    }
-                }
-                else
-                {
-                    __syncwarp();
-                    for(uint32_t i = lane; i < cnt * sh.outLen; i += 32)
-                        gout[i] = outStage[i];
-                    __syncwarp();
-                }
+                // flush: up to 7 single values, 16-byte pieces, up to 7 single values
+                uint8_t*       gptr  = reinterpret_cast<uint8_t*>(output) + gByte;
+                uint8_t const* sptr  = reinterpret_cast<uint8_t const*>(dst);
+                const uint32_t total = sh.outLen * 2u;
+                const uint32_t head  = min((16u - shift) & 15u, total);
+                const uint32_t body  = (total - head) / 16u;
+                const uint32_t tail  = (total - head) % 16u;
+                if(lane < head / 2u)
+                    reinterpret_cast<__half*>(gptr)[lane] = reinterpret_cast<__half const*>(sptr)[lane];
+                for(uint32_t c = lane; c < body; c += 32)
+                    reinterpret_cast<uint4*>(gptr + head)[c]
+                        = reinterpret_cast<uint4 const*>(sptr + head)[c];
+                if(lane < tail / 2u)
+                    reinterpret_cast<__half*>(gptr + head + body * 16u)[lane]
+                        = reinterpret_cast<__half const*>(sptr + head + body * 16u)[lane];
+                // (the next iteration's __syncwarp orders these reads before the next row)
             }
         }
         cpAsyncWait<0>();
-        if(lane == 0)
-            blk::tma_store_wait_all<0>();
     }
 
     // =====================================================================================
@@ -661,7 +654,8 @@ namespace
     // other warps, so warps count first; a second ring slot is all a warp needs to keep a
     // load in flight while it computes, a third helps when few warps fit.
     // B200WMMA_DLRM_STAGES / B200WMMA_DLRM_WARPS override the choice (tuning only).
-    Plan choosePlan(uint32_t fixedBytes, uint32_t stageBytes, uint32_t otherPerWarp)
+    Plan choosePlan(uint32_t fixedBytes, uint32_t stageBytes, uint32_t otherPerWarp,
+                    uint32_t maxWarps)
     {
         const char* es = getenv("B200WMMA_DLRM_STAGES");
         const char* ew = getenv("B200WMMA_DLRM_WARPS");
@@ -676,7 +670,7 @@ namespace
             if(fixedBytes + perWarp > SMEM_LIMIT)
                 continue;
             uint32_t warps = (SMEM_LIMIT - fixedBytes) / perWarp;
-            warps          = warps > MAX_WARPS ? MAX_WARPS : warps;
+            warps          = warps > maxWarps ? maxWarps : warps;
             if(forceWarps && forceWarps < warps)
                 warps = forceWarps;
             // 3 slots only if that costs no warps
@@ -709,7 +703,8 @@ extern "C" int b200wmma_dlrm_fwd(int dtype, const void* input, void* output, uin
         return rc;
     if(!aligned16(input) || !aligned16(output))
         return B200WMMA_ERR_ALIGNMENT;
-    const Plan plan = choosePlan(ZERO_BYTES, sh.stageBytes, GROUP * sh.outLen * 2);
+    const Plan plan
+        = choosePlan(ZERO_BYTES, sh.stageBytes, fwdStagingBytes(sh.outLen), MAX_WARPS);
     if(plan.warps == 0)
         return B200WMMA_ERR_UNSUPPORTED;
     const int sms = b200wmma::smCount();
@@ -751,7 +746,8 @@ extern "C" int b200wmma_dlrm_bwd(int dtype, const void* input, const void* upstr
         return B200WMMA_ERR_INVALID_ARG;
     if(!aligned16(input) || !aligned16(upstream) || !aligned16(grad) || !aligned16(mlp_grad))
         return B200WMMA_ERR_ALIGNMENT;
-    const Plan plan = choosePlan(ZERO_BYTES + triTableBytes(m), sh.stageBytes, 32 * G_LD * 2);
+    const Plan plan
+        = choosePlan(ZERO_BYTES + triTableBytes(m), sh.stageBytes, 32 * G_LD * 2, MAX_WARPS);
     if(plan.warps == 0)
         return B200WMMA_ERR_UNSUPPORTED;
     const int sms = b200wmma::smCount();

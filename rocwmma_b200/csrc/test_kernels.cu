@@ -204,7 +204,69 @@ namespace
         __syncthreads();
         out[3] = abortState.flag;
     }
+
+    // Untiled bulk copies: rows of `rowBytes` go global -> shared (one copy per lane, all
+    // signalling one mbarrier that every lane arrives on once) and come back shared -> global
+    // with every byte incremented, which shows that both directions and the proxy fence
+    // between them work.  out status: 0 ok, 1 the wait ran out.
+    __global__ void bulkCopyKernel(uint8_t const* src, uint8_t* dst, uint32_t rows,
+                                   uint32_t rowBytes, uint32_t* status)
+    {
+        extern __shared__ __align__(128) uint8_t tile[];
+        __shared__ uint64_t                    bar;
+        __shared__ rocwmma::block::AbortState abortState;
+        namespace blk = rocwmma::block;
+        const uint32_t lane = threadIdx.x;
+        if(lane == 0)
+        {
+            blk::mbar_init(&bar, 32);
+            abortState.flag = 0;
+            abortState.code = 0;
+            blk::mbar_init_fence();
+        }
+        __syncwarp();
+        const bool     mine = lane < rows;
+        const uint32_t barA = blk::smem_addr(&bar);
+        blk::mbar_arrive_expect_tx(barA, mine ? rowBytes : 0u);
+        if(mine)
+            blk::bulk_load(blk::smem_addr(tile) + lane * rowBytes, src + size_t(lane) * rowBytes,
+                           rowBytes, barA);
+        const bool ok = blk::mbar_wait(&bar, 0, &abortState, blk::WAIT_STAGE_FULL, 200000000ll);
+        if(__all_sync(0xffffffffu, ok))
+        {
+            for(uint32_t i = lane; i < rows * rowBytes; i += 32)
+                tile[i] = uint8_t(tile[i] + 1u);
+            blk::fence_async_shared();
+            __syncwarp();
+            if(mine)
+                blk::bulk_store(dst + size_t(lane) * rowBytes, blk::smem_addr(tile) + lane * rowBytes,
+                                rowBytes);
+            blk::tma_store_commit();
+            blk::tma_store_wait_all<0>();
+            if(lane == 0)
+                status[0] = 0u;
+        }
+        else if(lane == 0)
+            status[0] = 1u;
+    }
 } // namespace
+
+// rows <= 32 rows of row_bytes (a multiple of 16, rows * row_bytes <= 64 KiB) travel
+// src -> shared memory -> dst through cp.async.bulk in both directions; dst[i] = src[i] + 1.
+TEST_API int b200wmma_test_bulk_copy(const void* src, void* dst, uint32_t rows, uint32_t row_bytes,
+                                     uint32_t* status, void* stream)
+{
+    if(rows == 0 || rows > 32 || row_bytes == 0 || row_bytes % 16 != 0
+       || size_t(rows) * row_bytes > 65536 || (reinterpret_cast<uintptr_t>(src) % 16) != 0
+       || (reinterpret_cast<uintptr_t>(dst) % 16) != 0)
+        return -1;
+    if(cudaFuncSetAttribute(bulkCopyKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536)
+       != cudaSuccess)
+        return -4;
+    bulkCopyKernel<<<1, 32, rows * row_bytes, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint8_t const*>(src), static_cast<uint8_t*>(dst), rows, row_bytes, status);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 // Runs the never-satisfied wait with a limit of `limit_cycles` SM cycles (keep it around a
 // millisecond); the kernel always terminates by itself.

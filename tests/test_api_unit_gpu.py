@@ -31,6 +31,9 @@ def tlib():
                                           C.c_uint32, C.c_uint32, C.c_void_p]
     lib.b200wmma_test_bounded_wait.restype = C.c_int
     lib.b200wmma_test_bounded_wait.argtypes = [C.c_void_p, C.c_longlong, C.c_void_p]
+    lib.b200wmma_test_bulk_copy.restype = C.c_int
+    lib.b200wmma_test_bulk_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
+                                            C.c_void_p, C.c_void_p]
     return lib
 
 
@@ -162,6 +165,23 @@ def test_bounded_wait_gives_up_and_reports():
     assert gave_up == 1 and code == 2 and follower_left == 1 and flag == 1
     # the device is still healthy
     assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,row_bytes", [(1, 16), (27, 256), (32, 512), (5, 2048)])
+def test_untiled_bulk_copies_round_trip(rows, row_bytes):
+    """cp.async.bulk global -> shared (mbarrier completion, one copy per lane) and shared ->
+    global (bulk-group completion) of the block API: dst = src + 1 for every byte."""
+    src = torch.randint(0, 256, (rows * row_bytes,), dtype=torch.uint8, device="cuda")
+    dst = torch.zeros_like(src)
+    status = torch.full((1,), 7, dtype=torch.int32, device="cuda")
+    rc = tlib().b200wmma_test_bulk_copy(src.data_ptr(), dst.data_ptr(), rows, row_bytes,
+                                        status.data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    assert torch.equal(dst, src + 1)  # uint8 arithmetic wraps, like the kernel's
 
 
 @pytest.mark.gpu
