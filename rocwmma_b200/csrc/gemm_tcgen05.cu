@@ -250,7 +250,8 @@ namespace
     template <typename OutT, typename CompT, uint32_t VBYTES>
     __device__ inline void epilogueRowV(uint32_t const (&raw)[32], GemmParams const& p,
                                         CompT alpha, CompT beta, bool useC, uint32_t row,
-                                        uint32_t col0, uint32_t mode, float const* dPre)
+                                        uint32_t col0, uint32_t mode, float const* dPre,
+                                        OutT const* cPre = nullptr)
     {
         constexpr uint32_t VEC = VBYTES / sizeof(OutT); // elements per access
         constexpr bool     CAN_CHUNK
@@ -271,7 +272,13 @@ namespace
             const bool       whole = (col + VEC <= p.n);
             if(readC)
             {
-                if(whole)
+                if(cPre != nullptr) // C already fetched by the caller
+                {
+#pragma unroll
+                    for(uint32_t e = 0; e < VEC; ++e)
+                        cin[e] = cPre[v * VEC + e];
+                }
+                else if(whole)
                     ldVec<VBYTES>(cin, cRow + col);
                 else
                     for(uint32_t e = 0; e < VEC; ++e)
@@ -330,12 +337,41 @@ namespace
     template <typename OutT, typename CompT>
     __device__ inline void epilogueRow(uint32_t const (&raw)[32], GemmParams const& p, CompT alpha,
                                        CompT beta, bool useC, uint32_t row, uint32_t col0,
-                                       uint32_t mode = EPI_WHOLE, float const* dPre = nullptr)
+                                       uint32_t mode = EPI_WHOLE, float const* dPre = nullptr,
+                                       OutT const* cPre = nullptr)
     {
         if(p.wide) // C and D rows are 32-byte aligned: whole-sector accesses
-            epilogueRowV<OutT, CompT, 32>(raw, p, alpha, beta, useC, row, col0, mode, dPre);
+            epilogueRowV<OutT, CompT, 32>(raw, p, alpha, beta, useC, row, col0, mode, dPre, cPre);
         else
-            epilogueRowV<OutT, CompT, 16>(raw, p, alpha, beta, useC, row, col0, mode, dPre);
+            epilogueRowV<OutT, CompT, 16>(raw, p, alpha, beta, useC, row, col0, mode, dPre, cPre);
+    }
+
+    // 32 consecutive values of row `rowPtr` starting at column col0 (zeros outside n).
+    template <typename T>
+    __device__ inline void loadGroup(T (&dst)[32], T const* rowPtr, uint32_t col0, uint32_t n,
+                                     bool rowValid, bool wide)
+    {
+        constexpr uint32_t V32 = 32u / sizeof(T), V16 = 16u / sizeof(T);
+        if(wide && rowValid && col0 + 32u <= n)
+        {
+#pragma unroll
+            for(uint32_t v = 0; v < 32u / V32; ++v)
+                ldVec<32>(&dst[v * V32], rowPtr + col0 + v * V32);
+            return;
+        }
+#pragma unroll
+        for(uint32_t v = 0; v < 32u / V16; ++v)
+        {
+            const uint32_t col = col0 + v * V16;
+            if(rowValid && col + V16 <= n)
+                ldVec<16>(&dst[v * V16], rowPtr + col);
+            else
+            {
+#pragma unroll
+                for(uint32_t e = 0; e < V16; ++e)
+                    dst[v * V16 + e] = (rowValid && col + e < n) ? rowPtr[col + e] : T(0);
+            }
+        }
     }
 
     // 32 consecutive fp32 values of row `rowPtr` starting at column col0 (zeros outside n).
@@ -414,6 +450,43 @@ namespace
                 tc_fence_before_sync();
                 return true;
             }
+        }
+        if(useC && (mode == EPI_WHOLE || mode == EPI_LAST))
+        {
+            // beta != 0: the rows of C are fetched two 32-column groups ahead of use, the
+            // first two before the accumulator is even ready, so that their latency hides
+            // behind the wait and behind the groups in front of them (fetched group by group
+            // inside the loop they cost 15 % of a 4096^3 bf16 -> fp32 product).
+            constexpr uint32_t AHEAD = 2;
+            alignas(32) OutT   cq[AHEAD + 1][32];
+            const bool         rowValid = row < p.m;
+            OutT const*        cRow
+                = static_cast<OutT const*>(p.c) + size_t(rowValid ? row : 0u) * p.ldc;
+#pragma unroll
+            for(uint32_t c = 0; c < AHEAD; ++c)
+                loadGroup(cq[c], cRow, colBase + c * 32u, p.n, rowValid, p.wide != 0u);
+            if(!mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL))
+                return false;
+            tc_fence_after_sync();
+#pragma unroll
+            for(uint32_t chunk = 0; chunk < BN / 32; ++chunk)
+            {
+                if(chunk >= groups)
+                    break;
+                if(chunk + AHEAD < BN / 32)
+                    loadGroup(cq[(chunk + AHEAD) % (AHEAD + 1)], cRow,
+                              colBase + (chunk + AHEAD) * 32u, p.n, rowValid, p.wide != 0u);
+                uint32_t raw[32];
+                __syncwarp();
+                tmem_load_32x32b_x32(taddrRowBase + chunk * 32u, raw);
+                tmem_load_wait();
+                const uint32_t col0 = colBase + chunk * 32u;
+                if(rowValid && col0 < p.n)
+                    epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0, mode, nullptr,
+                                             cq[chunk % (AHEAD + 1)]);
+            }
+            tc_fence_before_sync();
+            return true;
         }
         if(!mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL))
             return false;
