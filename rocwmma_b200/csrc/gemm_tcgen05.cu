@@ -78,6 +78,7 @@ namespace
         uint32_t    band; // tile rows per raster band (tiles of a band share their rows of A in L2)
         uint32_t    tmaStore; // 1: D leaves through shared memory and TMA stores
         uint32_t    aMN, bMN; // 1: operand is MN-major in memory (A column-major, B row-major)
+        uint32_t    sumInTmem; // 1: chunked accumulation keeps its running sum in tensor memory
     };
 
     // One operand tile for one K block.  K-major: one TMA box of `rows` rows x 128 bytes of
@@ -501,6 +502,98 @@ namespace
             const uint32_t col0 = colBase + chunk * 32u;
             if(row < p.m && col0 < p.n)
                 epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0, mode);
+        }
+        tc_fence_before_sync();
+        return true;
+    }
+
+    // ---- chunked accumulation with the running sum in tensor memory --------------------------
+    // The pair kernel's two accumulator buffers start at columns 0 and 256 of the 512 the block
+    // owns; a tile of bn <= 160 columns leaves [bn, 256) and [256 + bn, 512) unused, which is
+    // enough for a third, thread-managed copy of the tile: the running sum over the K chunks.
+    // After every chunk but the last the epilogue threads read the fresh accumulator, add it
+    // to the sum in fp32 with round-to-nearest and write the sum back with tcgen05.st -- no
+    // global traffic; the last chunk goes out through the ordinary row epilogue with the sum
+    // as its addend.  A thread only ever touches its own lane, so program order plus the
+    // ld / st waits is all the ordering needed.
+    __device__ inline uint32_t sumColumn(uint32_t group, uint32_t bn)
+    {
+        const uint32_t inFirstGap = (256u - bn) / 32u;
+        return group < inFirstGap ? bn + 32u * group : 256u + bn + 32u * (group - inFirstGap);
+    }
+
+    __device__ inline bool drainAccumulatorToTmemSum(uint64_t* accFullBar, uint32_t accPh,
+                                                     AbortState* abort, uint32_t taddrAcc,
+                                                     uint32_t taddrLane, GemmParams const& p,
+                                                     float alpha, float beta, bool useC,
+                                                     uint32_t row, uint32_t colBase, uint32_t mode)
+    {
+        const uint32_t groups = p.bn / 32u;
+        if(mode == EPI_FIRST || mode == EPI_MIDDLE)
+        {
+            if(!mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL))
+                return false;
+            tc_fence_after_sync();
+#pragma unroll 1
+            for(uint32_t g = 0; g < groups; ++g)
+            {
+                uint32_t raw[32];
+                __syncwarp();
+                tmem_load_32x32b_x32(taddrAcc + g * 32u, raw);
+                if(mode == EPI_MIDDLE)
+                {
+                    uint32_t sum[32];
+                    tmem_load_32x32b_x32(taddrLane + sumColumn(g, p.bn), sum);
+                    tmem_load_wait();
+#pragma unroll
+                    for(uint32_t e = 0; e < 32; ++e)
+                        raw[e] = __float_as_uint(
+                            __fadd_rn(__uint_as_float(sum[e]), __uint_as_float(raw[e])));
+                }
+                else
+                    tmem_load_wait();
+                tmem_store_32x32b_x32(taddrLane + sumColumn(g, p.bn), raw);
+            }
+            tmem_store_wait();
+            tc_fence_before_sync();
+            return true;
+        }
+        // last chunk: D = alpha * (sum + acc) + beta * C, C fetched two groups ahead
+        constexpr uint32_t AHEAD = 2;
+        alignas(32) float  cq[AHEAD + 1][32];
+        const bool         rowValid = row < p.m;
+        float const*       cRow
+            = static_cast<float const*>(p.c) + size_t(rowValid ? row : 0u) * p.ldc;
+        if(useC)
+        {
+#pragma unroll
+            for(uint32_t c = 0; c < AHEAD; ++c)
+                loadGroup(cq[c], cRow, colBase + c * 32u, p.n, rowValid, p.wide != 0u);
+        }
+        if(!mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL))
+            return false;
+        tc_fence_after_sync();
+#pragma unroll
+        for(uint32_t g = 0; g < 160u / 32u; ++g)
+        {
+            if(g >= groups)
+                break;
+            if(useC && g + AHEAD < 160u / 32u)
+                loadGroup(cq[(g + AHEAD) % (AHEAD + 1)], cRow, colBase + (g + AHEAD) * 32u, p.n,
+                          rowValid, p.wide != 0u);
+            uint32_t raw[32], sum[32];
+            __syncwarp();
+            tmem_load_32x32b_x32(taddrAcc + g * 32u, raw);
+            tmem_load_32x32b_x32(taddrLane + sumColumn(g, p.bn), sum);
+            tmem_load_wait();
+            float dq[32];
+#pragma unroll
+            for(uint32_t e = 0; e < 32; ++e)
+                dq[e] = __uint_as_float(sum[e]);
+            const uint32_t col0 = colBase + g * 32u;
+            if(rowValid && col0 < p.n)
+                epilogueRow<float, float>(raw, p, alpha, beta, useC, row, col0, EPI_LAST, dq,
+                                          useC ? cq[g % (AHEAD + 1)] : nullptr);
         }
         tc_fence_before_sync();
         return true;
@@ -1032,16 +1125,39 @@ namespace
                                           : ch == 0u            ? EPI_FIRST
                                           : ch + 1u < numChunks ? EPI_MIDDLE
                                                                 : EPI_LAST;
-                    const uint32_t taddr = tmemBase + ((quad * 32u) << 16) + buf * BN;
-                    const bool     drained
-                        = p.tmaStore
-                              ? drainAccumulatorTma<OutT, CompT>(
-                                  &ctl->accFull[buf], accPh, &ctl->abort, taddr, p, &tmapD, staging,
-                                  stagedGroups, alpha, beta, useC, quad * 32u + lane,
-                                  tm * P_TILE_M + rank * 128u, tn * bn, mode, threadIdx.x == 64u)
-                              : drainAccumulator<OutT, CompT>(&ctl->accFull[buf], accPh,
-                                                              &ctl->abort, taddr, p, alpha, beta,
-                                                              useC, row, tn * bn, mode);
+                    const uint32_t taddrLane = tmemBase + ((quad * 32u) << 16);
+                    const uint32_t taddr     = taddrLane + buf * BN;
+                    bool           drained;
+                    if constexpr(std::is_same<OutT, float>::value
+                                 && std::is_same<CompT, float>::value)
+                    {
+                        if(p.sumInTmem && numChunks > 1u)
+                            drained = drainAccumulatorToTmemSum(&ctl->accFull[buf], accPh,
+                                                                &ctl->abort, taddr, taddrLane, p,
+                                                                alpha, beta, useC, row, tn * bn,
+                                                                mode);
+                        else
+                            drained = p.tmaStore
+                                          ? drainAccumulatorTma<OutT, CompT>(
+                                              &ctl->accFull[buf], accPh, &ctl->abort, taddr, p,
+                                              &tmapD, staging, stagedGroups, alpha, beta, useC,
+                                              quad * 32u + lane, tm * P_TILE_M + rank * 128u,
+                                              tn * bn, mode, threadIdx.x == 64u)
+                                          : drainAccumulator<OutT, CompT>(
+                                              &ctl->accFull[buf], accPh, &ctl->abort, taddr, p,
+                                              alpha, beta, useC, row, tn * bn, mode);
+                    }
+                    else
+                        drained = p.tmaStore
+                                      ? drainAccumulatorTma<OutT, CompT>(
+                                          &ctl->accFull[buf], accPh, &ctl->abort, taddr, p, &tmapD,
+                                          staging, stagedGroups, alpha, beta, useC,
+                                          quad * 32u + lane, tm * P_TILE_M + rank * 128u, tn * bn,
+                                          mode, threadIdx.x == 64u)
+                                      : drainAccumulator<OutT, CompT>(&ctl->accFull[buf], accPh,
+                                                                      &ctl->abort, taddr, p, alpha,
+                                                                      beta, useC, row, tn * bn,
+                                                                      mode);
                     if(!drained)
                     {
                         ok = false;
@@ -1247,7 +1363,7 @@ namespace
         useTma = useTma && tmaSafe;
         GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
                      status, chunkKB, wide, BN, bandEnv ? bandEnv : GROUP_M, useTma ? 1u : 0u,
-                     aMN ? 1u : 0u,      bMN ? 1u : 0u};
+                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u};
         CUtensorMap mapA, mapB, mapD;
         {
             int rcD = makeOutputMap(&mapD, outputMapType<OutT>(), sizeof(OutT), d, m, n, ldd);
@@ -1287,6 +1403,24 @@ namespace
             }();
             if(bnEnv >= 128 && bnEnv <= 256 && bnEnv % 32 == 0)
                 bn = bnEnv;
+            // Chunked accumulation: tiles of at most 160 columns leave room in tensor memory
+            // for the running sum, which takes the chunks' read-modify-write of D (an L2 round
+            // trip per 512 elements of K) out of the picture.  Measured on xf32 4096^3: 446
+            // TFLOP/s with the sum in D (256-wide tiles, TMA reduce-add), 572 with the sum in
+            // tensor memory (160-wide tiles); one unbroken chain runs at 588 with 160-wide and
+            // 692 with 256-wide tiles, so what is left is the narrower tile, not the chunks.
+            // B200WMMA_GEMM_TMEMSUM=0 keeps the sum in D (tuning / comparison only).
+            static const bool tmemSumEnv = [] {
+                const char* e = getenv("B200WMMA_GEMM_TMEMSUM");
+                return !(e && e[0] == '0');
+            }();
+            if(chunkKB != 0u && tmemSumEnv)
+            {
+                if(bnEnv == 0u || bn > 160u)
+                    bn = n <= 128u ? 128u : 160u;
+                p.sumInTmem = 1u;
+                p.tmaStore  = 0u;
+            }
             p.bn   = bn;
             int rc = aMN ? makeOperandMapMN(&mapA, dt, sizeof(InT), a, m, k, lda)
                          : makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, 128);
