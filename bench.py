@@ -55,11 +55,19 @@ def measured_peaks():
         return FALLBACK_PEAK_TFLOPS, "fallback (no MEASURED_PEAKS.json)", {}
 
 
+# The B200s this runs on are power-capped: a dense GEMM holds its top clock for roughly the
+# first 100 ms and then settles 10-15 % lower, for the vendor library as for this kernel,
+# which is why the measured peaks come as a burst and a sustained figure.  A timed region
+# shorter than this is compared with the burst peak, a longer one with the sustained peak;
+# both fractions are reported either way.
+BURST_REGION_MS = 100.0
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU while the timed region runs
     (read-only NVML queries)."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -196,8 +204,8 @@ def run_reference_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=None,
                     help="steps of the host-buffer measurement (default: min(steps, 10))")
@@ -289,10 +297,21 @@ def main():
     e2e_value = flops / (e2e_ms * 1e-3) / 1e12
 
     # ---- roofline of the dominant (only) kernel: this rank's launch ----
-    peak, peak_src, _ = measured_peaks()
+    peak, peak_src, peaks_json = measured_peaks()
     kernel_tflops = 2.0 * m_local * N * K / (ms_per_step * 1e-3) / 1e12
+    burst_peak = peak
+    sustained_peak = float(peaks_json.get("bf16_tflops_sustained", 0.0)) or None
+    if sustained_peak and ms_total > BURST_REGION_MS:
+        peak = sustained_peak
+        peak_src = ("measured (MEASURED_PEAKS.json bf16_tflops_sustained: the timed region of "
+                    f"{ms_total:.0f} ms is past the ~{BURST_REGION_MS:.0f} ms the power cap allows "
+                    "at top clock)")
     roofline = {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
                 "frac": kernel_tflops / peak,
+                "frac_of_burst_peak": kernel_tflops / burst_peak,
+                "frac_of_sustained_peak": (kernel_tflops / sustained_peak
+                                           if sustained_peak else None),
+                "timed_region_ms": ms_total,
                 "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
                 "peak_source": peak_src, "kernel": "gemm_tcgen05_pair_kernel<half,half,float>",
                 "algorithmic_flops_per_launch": 2.0 * m_local * N * K}
