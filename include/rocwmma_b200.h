@@ -111,7 +111,7 @@ B200WMMA_API int b200wmma_gemm_simple_ex(int in_dtype, int out_dtype, int comput
  * (samples/perf_hgemm.cpp:518-714, perf_sgemm.cpp:472, perf_dgemm.cpp:464; same
  * argument order as above).  C and D are row-major.  When beta == 0, c may be
  * NULL and is never read.  Type pairs: F16->F16, F16->F32, BF16->F32, BF16->BF16,
- * XF32->F32, I8->I32, E4M3->BF16, E4M3->F32, E5M2->BF16, E5M2->F32; F64->F64 runs on the warp-level
+ * XF32->F32, F32->F32, I8->I32, E4M3->BF16, E4M3->F32, E5M2->BF16, E5M2->F32; F64->F64 runs on the warp-level
  * double-precision tensor path with a shared-memory pipeline.
  * Requirements: a, b, c, d 16-byte aligned; lda, ldb, ldc, ldd times the element
  * size multiples of 16 bytes.  Any m, n, k >= 1 (edge tiles are zero-filled on
@@ -120,7 +120,11 @@ B200WMMA_API int b200wmma_gemm_simple_ex(int in_dtype, int out_dtype, int comput
  * column-major A / row-major B as MN-major ones), except for 32- and 64-bit
  * inputs (XF32, F64): those transpose column-major A / row-major B into a
  * per-device scratch buffer first (allocated on first use, grown on demand; such
- * calls on different streams of one device must not overlap).  The first call on a device allocates a few bytes of status memory.
+ * calls on different streams of one device must not overlap).  F32->F32 (the reference's
+ * perf_sgemm: full fp32 products) runs as three TF32 products over split copies
+ * (hi + lo) of A and B, which also live in that scratch buffer (2 (m + n) k floats), for every
+ * layout; its A and B need no 16-byte alignment.  The first call on a device allocates a few
+ * bytes of status memory.
  */
 B200WMMA_API int b200wmma_gemm(int in_dtype, int out_dtype, uint32_t m, uint32_t n, uint32_t k, const void* a,
                   const void* b, const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,

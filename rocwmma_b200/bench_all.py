@@ -177,6 +177,8 @@ def main():
                                   iters=it(20)),
         "xf32": lambda: gemm_case(f"gemm {mid}^3 xf32->f32", XF32, F32, mid, 2.0, -1.0, 0.5,
                                   iters=it(20)),
+        "f32": lambda: gemm_case(f"gemm {mid}^3 f32 (3 x TF32)", F32, F32, mid, 2.0, -1.0, 0.5 / 3,
+                                 iters=it(10)),
         "f64": lambda: gemm_case(f"gemm {mid}^3 f64", F64, F64, mid, 2.0, -1.0, None,
                                  iters=it(5)),
         "i8": lambda: gemm_case(f"gemm {big}^3 i8->i32", I8, I32, big, 1, 0, 2.0, iters=it(20)),

@@ -1572,6 +1572,121 @@ namespace
         return launch<InT, OutT, CompT>(dt, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
                                         stream, aMN, bMN);
     }
+
+    // ---- float32_t: full fp32 products from three TF32 products ------------------------------
+    // The tensor core has no fp32 operand format.  x = hi + lo with hi = tf32(x) and
+    // lo = tf32(x - hi) keeps 21 of x's 24 significand bits, and
+    //     A B  ~  Ahi Bhi + Alo Bhi + Ahi Blo            (the lo x lo term, 2^-22 relative, dropped)
+    // -- the same split mma_sync uses for float32_t fragments.  Here it is three runs of the
+    // xf32 kernel over split copies of the operands: D = alpha Ahi Bhi + beta C, then twice
+    // D += alpha (correction term).  The main term uses the chunked accumulation of the xf32
+    // path; the corrections are 2^-11 of it, so a single chain is accurate enough for them.
+    // The split pass also brings column-major A / row-major B into K-major order.
+    __device__ inline float tf32Round(float v)
+    {
+        uint32_t u;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+        return __uint_as_float(u);
+    }
+
+    // in: `rows` x `cols` values, element (r, c) at in[r * ldIn + c]; TRANSPOSE writes element
+    // (r, c) to out[c * ldOut + r], otherwise to out[r * ldOut + c].
+    template <bool TRANSPOSE>
+    __global__ void splitTf32Kernel(float const* __restrict__ in, float* __restrict__ hi,
+                                    float* __restrict__ lo, uint32_t rows, uint32_t cols,
+                                    uint32_t ldIn, uint32_t ldOut)
+    {
+        __shared__ float tileHi[32][33], tileLo[32][33];
+        const uint32_t   c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+        for(uint32_t j = threadIdx.y; j < 32; j += blockDim.y)
+        {
+            const uint32_t r = r0 + j, c = c0 + threadIdx.x;
+            if(r < rows && c < cols)
+            {
+                const float v = in[size_t(r) * ldIn + c];
+                const float h = tf32Round(v);
+                const float l = tf32Round(v - h);
+                if constexpr(TRANSPOSE)
+                {
+                    tileHi[j][threadIdx.x] = h;
+                    tileLo[j][threadIdx.x] = l;
+                }
+                else
+                {
+                    hi[size_t(r) * ldOut + c] = h;
+                    lo[size_t(r) * ldOut + c] = l;
+                }
+            }
+        }
+        if constexpr(TRANSPOSE)
+        {
+            __syncthreads();
+            for(uint32_t j = threadIdx.y; j < 32; j += blockDim.y)
+            {
+                const uint32_t c = c0 + j, r = r0 + threadIdx.x;
+                if(r < rows && c < cols)
+                {
+                    hi[size_t(c) * ldOut + r] = tileHi[threadIdx.x][j];
+                    lo[size_t(c) * ldOut + r] = tileLo[threadIdx.x][j];
+                }
+            }
+        }
+    }
+
+    int splitTf32(float const* in, float* hi, float* lo, uint32_t rows, uint32_t cols,
+                  uint32_t ldIn, uint32_t ldOut, bool transpose, cudaStream_t stream)
+    {
+        dim3 block(32, 8);
+        dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+        if(transpose)
+            splitTf32Kernel<true><<<grid, block, 0, stream>>>(in, hi, lo, rows, cols, ldIn, ldOut);
+        else
+            splitTf32Kernel<false><<<grid, block, 0, stream>>>(in, hi, lo, rows, cols, ldIn, ldOut);
+        return b200wmma::cudaToStatus(cudaGetLastError());
+    }
+
+    int runF32(uint32_t m, uint32_t n, uint32_t k, void const* a, void const* b, void const* c,
+               void* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, double alpha,
+               double beta, int layoutA, int layoutB, cudaStream_t stream)
+    {
+        const bool aMN = layoutA == B200WMMA_COL_MAJOR, bMN = layoutB == B200WMMA_ROW_MAJOR;
+        auto       misaligned = [](void const* ptr, uint32_t ld) {
+            return (reinterpret_cast<uintptr_t>(ptr) % 16) != 0 || (size_t(ld) * 4) % 16 != 0;
+        };
+        if(misaligned(d, ldd) || (beta != 0.0 && misaligned(c, ldc)))
+            return B200WMMA_ERR_ALIGNMENT;
+        if(lda < (aMN ? m : k) || ldb < (bMN ? n : k) || ldd < n || (beta != 0.0 && ldc < n))
+            return B200WMMA_ERR_INVALID_ARG;
+        const uint32_t kPad   = roundUp(k, 4);
+        const size_t   aElems = (size_t(m) * kPad + 63) / 64 * 64; // keeps every part 256-byte aligned
+        const size_t   bElems = (size_t(n) * kPad + 63) / 64 * 64;
+        float* scratch = static_cast<float*>(b200wmma::deviceScratch((2 * aElems + 2 * bElems) * 4));
+        if(!scratch)
+            return B200WMMA_ERR_CUDA;
+        float *aHi = scratch, *aLo = aHi + aElems, *bHi = aLo + aElems, *bLo = bHi + bElems;
+        // A is m x k: row-major = K-major already; column-major is k rows of m values.
+        int rc = aMN ? splitTf32(static_cast<float const*>(a), aHi, aLo, k, m, lda, kPad, true, stream)
+                     : splitTf32(static_cast<float const*>(a), aHi, aLo, m, k, lda, kPad, false,
+                                 stream);
+        if(rc != B200WMMA_OK)
+            return rc;
+        // B is k x n: column-major = n rows of k values = K-major; row-major is k rows of n.
+        rc = bMN ? splitTf32(static_cast<float const*>(b), bHi, bLo, k, n, ldb, kPad, true, stream)
+                 : splitTf32(static_cast<float const*>(b), bHi, bLo, n, k, ldb, kPad, false, stream);
+        if(rc != B200WMMA_OK)
+            return rc;
+        const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+        rc = launch<float, float, float>(dt, m, n, k, aHi, bHi, c, d, kPad, kPad, ldc, ldd, alpha,
+                                         beta, stream, false, false);
+        if(rc != B200WMMA_OK)
+            return rc;
+        rc = launch<float, float, float>(dt, m, n, k, aLo, bHi, d, d, kPad, kPad, ldd, ldd, alpha, 1.0,
+                                         stream, false, false);
+        if(rc != B200WMMA_OK)
+            return rc;
+        return launch<float, float, float>(dt, m, n, k, aHi, bLo, d, d, kPad, kPad, ldd, ldd, alpha,
+                                           1.0, stream, false, false);
+    }
 } // namespace
 
 namespace b200wmma
@@ -1620,6 +1735,8 @@ extern "C" int b200wmma_gemm(int in_dtype, int out_dtype, uint32_t m, uint32_t n
     B200WMMA_GEMM_CASE(B200WMMA_E5M2, B200WMMA_F32, __nv_fp8_e5m2, float, float,
                        CU_TENSOR_MAP_DATA_TYPE_UINT8)
 #undef B200WMMA_GEMM_CASE
+    if(in_dtype == B200WMMA_F32 && out_dtype == B200WMMA_F32)
+        return runF32(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, s);
     if(in_dtype == B200WMMA_F64 && out_dtype == B200WMMA_F64)
         return b200wmma::gemmF64(m, n, k, static_cast<double const*>(a),
                                  static_cast<double const*>(b), static_cast<double const*>(c),

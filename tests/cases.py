@@ -28,7 +28,8 @@ def tolerance(in_t, out_t):
 SIMPLE_PAIRS = [(F16, F32), (F16, F16), (BF16, F32), (BF16, BF16), (E4M3, F32), (I8, I32),
                 (F32, F32), (XF32, F32), (F64, F64)]
 # pairs of the block-cooperative GEMM
-BLOCK_PAIRS = [(F16, F16), (F16, F32), (BF16, F32), (BF16, BF16), (XF32, F32), (I8, I32),
+BLOCK_PAIRS = [(F16, F16), (F16, F32), (BF16, F32), (BF16, BF16), (XF32, F32), (F32, F32),
+               (I8, I32),
                (E4M3, BF16), (E4M3, F32), (E5M2, BF16), (E5M2, F32), (F64, F64)]
 
 # (input, output, compute) triples of the simple GEMM beyond SIMPLE_PAIRS' usual compute

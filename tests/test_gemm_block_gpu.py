@@ -199,9 +199,11 @@ def _metric64(x, y):
     return float((np.abs(x - y) / (np.abs(x) + np.abs(y) + 1.0)).max())
 
 
-@pytest.mark.parametrize("in_t,out_t", [(O.BF16, O.F32), (O.XF32, O.F32), (O.F64, O.F64)])
+@pytest.mark.parametrize("in_t,out_t", [(O.BF16, O.F32), (O.XF32, O.F32), (O.F32, O.F32),
+                                        (O.F64, O.F64)])
 def test_config_precision_sweep_4096(in_t, out_t):
-    """M=N=K=4096, alpha=2, beta=-1, C nonzero; bf16 -> fp32, xf32 -> fp32, fp64.
+    """M=N=K=4096, alpha=2, beta=-1, C nonzero; bf16 -> fp32, xf32 -> fp32, fp64 -- and full
+    fp32 (three TF32 products over split operands), judged like xf32.
 
     Checked on a sample of rows against the oracle.  For xf32 the oracle's own fp32
     rounding (4096 products added one by one) already sits ~1.2e-4 away from the exact
@@ -223,7 +225,7 @@ def test_config_precision_sweep_4096(in_t, out_t):
                   bt.reshape(-1), np.ascontiguousarray(c[pick]).reshape(-1), 2.0, -1.0)
     g = np.ascontiguousarray(got[pick])
     err = O.max_rel_err(out_t, g.reshape(-1), want)
-    if in_t == O.XF32:
+    if in_t in (O.XF32, O.F32):
         exact = _exact_rows(a[pick], bt, c[pick], 2.0, -1.0, lambda v: v)
         gpu_vs_exact = _metric64(g.astype(np.float64), exact)
         oracle_vs_exact = _metric64(want.reshape(pick.size, n).astype(np.float64), exact)
