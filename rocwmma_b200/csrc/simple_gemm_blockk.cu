@@ -2,8 +2,8 @@
 // (the reference runs BlockK from the per-type minimum up to 128,
 // test/gemm/gemm_common_test_params.hpp:51-121 and
 // docs/api-reference/api-reference-guide.rst:80-153).  Built here: 32 and 64 for 8- and
-// 16-bit types (8-bit 32x32 tiles: 16 and 64), 8 and 32 for float32_t / xfloat32_t, 4 and 8
-// for float64_t.  A translation unit of its own only to keep compile times apart.
+// 16-bit types (8-bit 32x32 tiles: 16 and 64), 128 as well for their 16x16 tiles, 8 and 32
+// for float32_t / xfloat32_t, 4 and 8 for float64_t.  A translation unit of its own only to keep compile times apart.
 #include "simple_gemm.cuh"
 
 namespace b200wmma
@@ -40,6 +40,11 @@ namespace simple
                     return launchTile<InT, OutT, CompT, BLOCK, BLOCK, 32>(g);
                 if(block_k == 64)
                     return launchTile<InT, OutT, CompT, BLOCK, BLOCK, 64>(g);
+                if constexpr(BLOCK == 16)
+                {
+                    if(block_k == 128)
+                        return launchTile<InT, OutT, CompT, 16, 16, 128>(g);
+                }
             }
             return B200WMMA_ERR_UNSUPPORTED;
         }

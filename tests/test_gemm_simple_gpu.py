@@ -96,7 +96,8 @@ BLOCK_K_CASES = [(O.F16, O.F32, 16, 32), (O.F16, O.F32, 16, 64), (O.F16, O.F32, 
                  (O.I8, O.I32, 16, 32), (O.I8, O.I32, 32, 16), (O.I8, O.I32, 32, 64),
                  (O.F32, O.F32, 16, 8), (O.F32, O.F32, 32, 32), (O.XF32, O.F32, 16, 8),
                  (O.XF32, O.F32, 32, 8), (O.XF32, O.F32, 32, 32), (O.F64, O.F64, 16, 4),
-                 (O.F64, O.F64, 16, 8)]
+                 (O.F64, O.F64, 16, 8), (O.F16, O.F32, 16, 128), (O.BF16, O.F32, 16, 128),
+                 (O.E4M3, O.F32, 16, 128), (O.I8, O.I32, 16, 128)]
 
 
 @pytest.mark.parametrize("in_t,out_t,block,block_k", BLOCK_K_CASES)
@@ -115,7 +116,7 @@ def test_unbuilt_fragment_k_extent_is_refused():
     case = dict(in_t=O.F16, out_t=O.F32, m=64, n=64, k=128, la=ROW, lb=COL, alpha=1.0, beta=0.0,
                 seed=1)
     with pytest.raises(Exception):
-        _run_simple(case, ROW, 16, block_k=128)
+        _run_simple(case, ROW, 32, block_k=128)
 
 
 @pytest.mark.parametrize("in_t,out_t", [(O.F16, O.F32), (O.I8, O.I32), (O.F64, O.F64)])
