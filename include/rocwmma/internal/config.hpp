@@ -40,6 +40,14 @@ namespace rocwmma
 #define ROCWMMA_KERNEL __global__
 
 #define ROCWMMA_ARCH_SM100A 1
+// 1 while the host side of a translation unit is compiled, 0 in the device pass: kernels
+// written for rocWMMA wrap their bodies in `if constexpr(!ROCWMMA_ARCH_HOST)`
+// (rocWMMA internal/config.hpp:73-111, samples/perf_hgemm.cpp:532).
+#if defined(__CUDA_ARCH__)
+#define ROCWMMA_ARCH_HOST 0
+#else
+#define ROCWMMA_ARCH_HOST 1
+#endif
 #define ROCWMMA_WAVE32_MODE 1
 
 #define ROCWMMA_VERSION_MAJOR 1

@@ -67,6 +67,21 @@ namespace rocwmma
         return Coord2d{{c.data[1], c.data[0]}};
     }
 
+    // Log2<N>::value for a power of two N, as a compile-time constant (rocWMMA
+    // internal/utils.hpp:151-168; kernels use it to turn divisions by tile sizes into
+    // shifts, samples/simple_dlrm.cpp:206).
+    template <uint32_t N>
+    struct Log2
+    {
+        static_assert(N != 0u && (N & (N - 1u)) == 0u, "Log2 needs a power of two");
+        static constexpr uint32_t value = 1u + Log2<(N >> 1)>::value;
+    };
+    template <>
+    struct Log2<1u>
+    {
+        static constexpr uint32_t value = 0u;
+    };
+
     template <typename IntT1, typename IntT2>
     ROCWMMA_HOST_DEVICE constexpr inline auto ceilDiv(IntT1 numerator, IntT2 divisor)
     {

@@ -54,7 +54,31 @@ namespace rocwmma
                 return false;
             }
 
-            // Moves units [Begin, Begin+Count) between x[] and memory.
+            // Position of unit u in the fragment's WORK-ITEM order, the order cooperative
+            // transfers cut into per-warp slices.  For matrix_a and accumulator fragments it
+            // is the unit order itself.  For a matrix_b fragment that has a transpose
+            // (BlockN a multiple of 16) it is the index of the SAME data in the transposed
+            // matrix_a fragment (applyTranspose, rocwmma_transforms.hpp), so that a slice
+            // loaded into a B fragment is, after applyTranspose, exactly the slice a
+            // cooperative store of the A fragment with the same warp index writes -- which
+            // is how rocWMMA's macro-tile kernels stage B through shared memory
+            // (samples/perf_hgemm.cpp:356-365).  In the reference the two fragment types
+            // share one register layout and the property is automatic.
+            ROCWMMA_DEVICE static constexpr uint32_t workIndex(uint32_t u)
+            {
+                if constexpr(Geom::IsB && (Geom::AtomsMajor % 2u == 0u))
+                {
+                    constexpr uint32_t UB = Geom::UnitsPerAtom, KT = Geom::AtomsMinor;
+                    const uint32_t     atom = u / UB, jk = u % UB;
+                    const uint32_t     nt = atom / KT, kt = atom % KT;
+                    return ((nt / 2u) * KT + kt) * (2u * UB) + ((jk << 1) | (nt & 1u));
+                }
+                else
+                    return u;
+            }
+
+            // Moves the units whose work-item index lies in [begin, begin + count) between
+            // x[] and memory.
             template <bool Vectorized, typename DataT, uint32_t N>
             ROCWMMA_DEVICE static inline void
                 load(DataT (&x)[N], DataT const* data, uint32_t ldm, uint32_t begin, uint32_t count)
@@ -63,7 +87,7 @@ namespace rocwmma
                 ROCWMMA_UNROLL
                 for(uint32_t u = 0; u < Geom::Units; ++u)
                 {
-                    if(u >= begin && u < begin + count)
+                    if(workIndex(u) >= begin && workIndex(u) < begin + count)
                     {
                         const uint32_t off = offset(Geom::unitCoord(u, lane), ldm);
                         if constexpr(Vectorized)
@@ -95,7 +119,7 @@ namespace rocwmma
                 ROCWMMA_UNROLL
                 for(uint32_t u = 0; u < Geom::Units; ++u)
                 {
-                    if(u >= begin && u < begin + count)
+                    if(workIndex(u) >= begin && workIndex(u) < begin + count)
                     {
                         const uint32_t off = offset(Geom::unitCoord(u, lane), ldm);
                         if constexpr(Vectorized)

@@ -171,6 +171,27 @@ namespace rocwmma
 
     template <typename FragT>
     using GetDataType_t = typename stdx::decay_t<FragT>::element_type;
+
+    // GetDataLayout_t<FragT>: the 1-D address map of the fragment's memory layout
+    // (rocWMMA internal/accessors_impl.hpp:107-118): fromMatrixCoord((row, col), ld) is the
+    // element offset row * ld + col for row_major, col * ld + row for col_major
+    // (internal/mapping_util_impl.hpp:142-150).  Kernels use it to step through matrices in
+    // units of fragments (samples/perf_hgemm.cpp:371-377, 558-571).
+    namespace detail
+    {
+        template <typename FragT>
+        struct GetDataLayout;
+        template <typename MatrixT, uint32_t BlockM, uint32_t BlockN, uint32_t BlockK,
+                  typename DataT, typename DataLayoutT>
+        struct GetDataLayout<fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>>
+        {
+            static_assert(!stdx::is_same<DataLayoutT, void>::value,
+                          "the fragment has no compile-time memory layout");
+            using type = DataSpace<DataLayoutT>;
+        };
+    } // namespace detail
+    template <typename FragT>
+    using GetDataLayout_t = typename detail::GetDataLayout<stdx::decay_t<FragT>>::type;
 } // namespace rocwmma
 
 #endif // ROCWMMA_B200_TRANSFORMS_API_HPP

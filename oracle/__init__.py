@@ -39,10 +39,27 @@ def build(force: bool = False) -> None:
     if os.path.isdir("/root/reference") and (
             force or not os.path.exists(os.path.join(_HERE, "_ref", "libref.so"))):
         subprocess.run(["make", "-C", _HERE, "ref"], check=True, stdout=subprocess.DEVNULL)
+    if os.path.isdir("/root/reference") and (force or _ref_kernels_stale()):
+        subprocess.run(["make", "-C", _HERE, "refkernels"], check=True, stdout=subprocess.DEVNULL)
+
+
+def _ref_kernels_stale() -> bool:
+    """The reference's sample kernels are compiled against this repository's headers, so the
+    library is stale when it is older than any of them (or than its own shim)."""
+    target = os.path.join(_HERE, "_ref", "libref_kernels.so")
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    deps = [os.path.join(_HERE, "ref_kernels.cu"), os.path.join(_HERE, "Makefile")]
+    inc = os.path.join(os.path.dirname(_HERE), "include", "rocwmma")
+    for root, _, files in os.walk(inc):
+        deps += [os.path.join(root, f) for f in files]
+    return any(os.path.getmtime(d) > t for d in deps)
 
 
 _lib = None
 _ref = None
+_ref_kernels = None
 
 
 def _ptr(a):
@@ -108,6 +125,40 @@ def ref():
                                 C.c_float, C.c_float]
         _ref = L
     return _ref
+
+
+def ref_kernels():
+    """The reference's own sample kernels compiled against this repository's headers
+    (oracle/ref_kernels.cu), or None when the library was not built."""
+    global _ref_kernels
+    if _ref_kernels is None:
+        path = os.path.join(_HERE, "_ref", "libref_kernels.so")
+        if os.path.isdir("/root/reference"):
+            build()
+        if not os.path.exists(path):
+            return None
+        L = C.CDLL(path)
+        gemm = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_double, C.c_double, C.c_void_p]
+        for name in ("refk_perf_hgemm", "refk_perf_sgemm", "refk_perf_dgemm", "refk_simple_hgemm",
+                     "refk_simple_sgemm", "refk_simple_dgemm"):
+            getattr(L, name).restype = C.c_int
+            getattr(L, name).argtypes = gemm
+        for name in ("refk_perf_hgemm_tile", "refk_perf_sgemm_tile", "refk_perf_dgemm_tile"):
+            getattr(L, name).restype = None
+            getattr(L, name).argtypes = [C.POINTER(C.c_uint32)]
+        for name in ("refk_simple_sgemv", "refk_simple_dgemv"):
+            getattr(L, name).restype = C.c_int
+            getattr(L, name).argtypes = [C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.c_double, C.c_double, C.c_void_p]
+        L.refk_dlrm_fwd.restype = C.c_int
+        L.refk_dlrm_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
+                                    C.c_uint32, C.c_void_p]
+        L.refk_dlrm_bwd.restype = C.c_int
+        L.refk_dlrm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p]
+        _ref_kernels = L
+    return _ref_kernels
 
 
 def num_threads() -> int:

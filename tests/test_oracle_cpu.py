@@ -113,6 +113,21 @@ def test_live_reference_build_agrees_on_other_type_triples(triple):
         assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (triple, literal)
 
 
+@pytest.mark.skipif(not os.path.isdir("/root/reference"), reason="reference tree not mounted")
+def test_reference_sample_kernels_compile_unmodified():
+    """Source-level drop-in: the kernel text of the reference's perf_*gemm, simple_*gemm,
+    simple_*gemv and simple_dlrm samples compiles, unmodified, against include/rocwmma
+    (oracle/ref_kernels.cu; nvcc cross-compiles without a GPU).  The GPU tests run them."""
+    lib = O.ref_kernels()
+    assert lib is not None
+    import ctypes as C
+    tile = (C.c_uint32 * 4)()
+    lib.refk_perf_hgemm_tile(tile)
+    # the sample's parameters for 32-lane hardware: 16 x 16 x 16 fragments, 4 x 2 per warp,
+    # 2 x 4 warps -> 128 x 128 macro tile, 256 threads (samples/perf_hgemm.cpp:239-252)
+    assert list(tile) == [128, 128, 16, 256]
+
+
 def test_e5m2_codec():
     """e5m2 is the upper byte of binary16; the encoder rounds to nearest even, saturates to
     +-57344 and agrees with the input generators' numpy encoder."""
