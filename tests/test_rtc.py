@@ -2,6 +2,7 @@
 samples/hipRTC_gemm.cpp).  Compilation needs no GPU and proves the device headers are
 self-contained; running it is a GPU test."""
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -34,6 +35,21 @@ def test_all_api_headers_compile_under_nvrtc():
     }
     """
     assert b"sm_100a" in rtc.compile_to_ptx(src)
+
+
+@pytest.mark.skipif(not os.path.isfile("/root/reference/samples/hipRTC_gemm.cpp"),
+                    reason="reference tree not mounted")
+def test_reference_rtc_kernel_source_compiles_unmodified():
+    """The kernel source string of the reference's own run-time compilation sample
+    (samples/hipRTC_gemm.cpp:73-173, a raw string literal handed to hipRTC) goes through NVRTC
+    against these headers as it is: read from the mounted tree, never stored here."""
+    text = open("/root/reference/samples/hipRTC_gemm.cpp").read()
+    start = text.index('R"(') + 3
+    source = text[start:text.index(')";', start)]
+    assert "#include <rocwmma/rocwmma.hpp>" in source and "gemm_rocwmma_d" in source
+    ptx = rtc.compile_to_ptx(source, "reference_hiprtc_kernel.cu").decode(errors="replace")
+    assert ".target sm_100a" in ptx and "gemm_rocwmma_d" in ptx
+    assert "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32" in ptx
 
 
 def test_compile_errors_are_reported():
