@@ -8,7 +8,13 @@ and the DLRM passes.  GEMMs report TFLOP/s = 2*M*N*K / time against the measured
 bf16 peak scaled per type; GEMV and DLRM report algorithmic bytes / time against the
 measured HBM copy bandwidth.  Inputs are random device tensors (timing only; parity is
 the test-suite's job).  Timed with CUDA events over `iters` back-to-back launches after
-3 warm-ups; every working set exceeds the 126 MB L2 except where noted.
+3 warm-ups; working sets that do not exceed the 126 MB L2 are timed launch by launch with an
+L2 flush in between.
+
+Under torchrun (python -m torch.distributed.run --nproc-per-node N -m rocwmma_b200.bench_all)
+every configuration is split over the N GPUs the way rocwmma_b200.shard says -- GEMM by rows
+of A / C / D with B replicated, GEMV by rows, DLRM by batch; no collective in the timed region --
+and the figures are whole-job totals over the slowest rank's time.
 
 --csv FILE also writes the GEMM results as the table rocWMMA's GEMM test programs print
 (header and row format: test/gemm/gemm_kernel_base_impl.hpp:441-523), which its plotting
@@ -22,7 +28,7 @@ import os
 
 import torch
 
-from . import api
+from . import api, shard
 from ._lib import BF16, COL_MAJOR, E4M3, E5M2, F16, F32, F64, I8, I32, ROW_MAJOR, XF32
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -37,18 +43,52 @@ def peaks():
         return 1590.0, 6650.0, "fallback"
 
 
-def timed(fn, iters):
+WORLD = int(os.environ.get("WORLD_SIZE", "1"))
+RANK = int(os.environ.get("RANK", "0"))
+
+
+def _barrier():
+    if WORLD > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+L2_BYTES = 126 << 20
+_flush = None
+
+
+def timed(fn, iters, working_set=None):
+    """Per-launch time in ms, the slowest rank's.  A working set larger than the L2 is timed
+    as `iters` back-to-back launches between two device events; a smaller one (the 1024^3
+    sample, a shard of a many-GPU run) would be served from L2, so every launch is then
+    timed on its own with a 256 MiB buffer written in between."""
+    global _flush
     for _ in range(3):
         fn()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
+    _barrier()
+    if working_set is None or working_set > L2_BYTES:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        _barrier()
+        total = e0.elapsed_time(e1)
+    else:
+        if _flush is None:
+            _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        pairs = []
+        for i in range(iters):
+            _flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            pairs.append((e0, e1))
+        _barrier()
+        total = sum(a.elapsed_time(b) for a, b in pairs)
     api.check_device()
-    return e0.elapsed_time(e1) / iters
+    return shard.max_over_ranks(total, device="cuda") / iters
 
 
 def rand(n, code):
@@ -98,7 +138,8 @@ def csv_row(r):
 
 
 def gemm_case(name, in_t, out_t, size, alpha, beta, peak_scale, simple=False, iters=20):
-    m = n = k = size
+    n = k = size
+    _, m = shard.gemm_shard(size, WORLD, RANK)   # this rank's rows of A, C, D
     a, b = rand(m * k, in_t), rand(k * n, in_t)
     c = rand(m * n, out_t) if beta != 0 else None
     d = torch.empty(m * n, dtype=api.torch_dtype(out_t), device="cuda")
@@ -107,12 +148,12 @@ def gemm_case(name, in_t, out_t, size, alpha, beta, peak_scale, simple=False, it
                                      COL_MAJOR, ROW_MAJOR, 16, out=d)
     else:
         fn = lambda: api.gemm(in_t, out_t, m, n, k, a, b, c, alpha, beta, out=d)  # noqa: E731
-    ms = timed(fn, iters)
-    tf = 2.0 * m * n * k / ms / 1e9
+    ms = timed(fn, iters, (m * k + k * n) * a.element_size() + m * n * d.element_size())
+    tf = 2.0 * size * n * k / ms / 1e9
     peak_bf16, _, src = peaks()
-    peak = peak_bf16 * peak_scale if peak_scale else 40.0
-    return {"config": name, "ms": ms, "value": tf, "unit": "TFLOP/s", "bound": "tensor",
-            "peak": peak, "frac": tf / peak,
+    peak = (peak_bf16 * peak_scale if peak_scale else 40.0) * WORLD
+    return {"config": name, "n_gpus": WORLD, "ms": ms, "value": tf, "unit": "TFLOP/s",
+            "bound": "tensor", "peak": peak, "frac": tf / peak,
             "gemm": {"in_t": in_t, "out_t": out_t, "size": size, "alpha": alpha, "beta": beta,
                      "simple": simple},
             "peak_source": (f"{src} bf16 peak x {peak_scale}" if peak_scale
@@ -120,36 +161,44 @@ def gemm_case(name, in_t, out_t, size, alpha, beta, peak_scale, simple=False, it
 
 
 def gemv_case(size, iters=50):
-    m = k = size
+    k = size
+    _, m = shard.gemv_shard(size, WORLD, RANK)   # this rank's rows: its own column-major block
     a, x, y = rand(m * k, F32), rand(k, F32), rand(m, F32)
     out = torch.empty_like(y)
-    ms = timed(lambda: api.gemv(F32, m, k, a, x, y, 2.1, 2.1, out=out), iters)
-    nbytes = m * k * 4 + k * 4 + 2 * m * 4
+    ms = timed(lambda: api.gemv(F32, m, k, a, x, y, 2.1, 2.1, out=out), iters, m * k * 4)
+    nbytes = size * k * 4 + WORLD * k * 4 + 2 * size * 4
     _, hbm, src = peaks()
+    hbm *= WORLD
     gbs = nbytes / ms / 1e6
-    return {"config": f"sgemv {size}^2 fp32 col-major", "ms": ms, "value": gbs, "unit": "GB/s",
+    return {"config": f"sgemv {size}^2 fp32 col-major", "n_gpus": WORLD, "ms": ms, "value": gbs,
+            "unit": "GB/s",
             "bound": "hbm", "algorithmic_bytes": nbytes, "peak": hbm, "frac": gbs / hbm,
             "peak_source": f"{src} copy bandwidth"}
 
 
-def dlrm_cases(batch, iters=20):
+def dlrm_cases(total_batch, iters=20):
     m, k = 27, 128
     out_len = k + m * (m - 1) // 2
+    _, batch = shard.dlrm_shard(total_batch, WORLD, RANK)   # this rank's samples
     x = torch.randn(batch * m * k, device="cuda").half()
     up = torch.randn(batch * out_len, device="cuda").half()
     out = torch.empty(batch * out_len, device="cuda", dtype=torch.float16)
     grad = torch.empty(batch * m * k, device="cuda", dtype=torch.float16)
     mlp = torch.empty(batch * k, device="cuda", dtype=torch.float16)
     _, hbm, src = peaks()
+    hbm *= WORLD
     res = []
-    ms = timed(lambda: api.dlrm_fwd(x, m, k, batch, out=out), iters)
-    nb = batch * (m * k + out_len) * 2
-    res.append({"config": f"dlrm fwd b={batch} 27x128 fp16", "ms": ms, "value": nb / ms / 1e6,
+    ms = timed(lambda: api.dlrm_fwd(x, m, k, batch, out=out), iters, batch * m * k * 2)
+    nb = total_batch * (m * k + out_len) * 2
+    res.append({"config": f"dlrm fwd b={total_batch} 27x128 fp16", "n_gpus": WORLD, "ms": ms,
+                "value": nb / ms / 1e6,
                 "unit": "GB/s", "bound": "hbm", "algorithmic_bytes": nb, "peak": hbm,
                 "frac": nb / ms / 1e6 / hbm, "peak_source": f"{src} copy bandwidth"})
-    ms = timed(lambda: api.dlrm_bwd(x, up, m, k, batch, grad=grad, mlp_grad=mlp), iters)
-    nb = batch * (m * k + out_len + m * k + k) * 2
-    res.append({"config": f"dlrm bwd b={batch} 27x128 fp16", "ms": ms, "value": nb / ms / 1e6,
+    ms = timed(lambda: api.dlrm_bwd(x, up, m, k, batch, grad=grad, mlp_grad=mlp), iters,
+               batch * m * k * 4)
+    nb = total_batch * (m * k + out_len + m * k + k) * 2
+    res.append({"config": f"dlrm bwd b={total_batch} 27x128 fp16", "n_gpus": WORLD, "ms": ms,
+                "value": nb / ms / 1e6,
                 "unit": "GB/s", "bound": "hbm", "algorithmic_bytes": nb, "peak": hbm,
                 "frac": nb / ms / 1e6 / hbm, "peak_source": f"{src} copy bandwidth"})
     return res
@@ -164,6 +213,9 @@ def main():
                     help="reduced sizes (for profiler captures): GEMMs 2048^3, DLRM b=8192, "
                          "GEMV 8192^2")
     args = ap.parse_args()
+    if WORLD > 1:
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        torch.distributed.init_process_group("nccl")
     only = set(filter(None, args.only.split(",")))
     big, mid = (2048, 2048) if args.small else (8192, 4096)
     it = (lambda d: args.iters or d)
@@ -198,10 +250,13 @@ def main():
             if "gemm" in r:
                 rows.append(csv_row(r))
                 r = {k: v for k, v in r.items() if k != "gemm"}
-            print(json.dumps(r), flush=True)
-    if args.csv:
+            if RANK == 0:
+                print(json.dumps(r), flush=True)
+    if args.csv and RANK == 0:
         with open(args.csv, "w") as f:
             f.write(CSV_HEADER + "\n" + "\n".join(rows) + "\n")
+    if WORLD > 1:
+        torch.distributed.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -30,6 +30,12 @@ def dlrm_shard(batch: int, world: int, rank: int):
     return row_range(batch, world, rank, 8)
 
 
+def gemv_shard(m: int, world: int, rank: int):
+    """Rows of A and y owned by `rank`; each rank holds its own column-major block with
+    lda = its row count, x is replicated.  Multiples of 64 rows (one thread block's share)."""
+    return row_range(m, world, rank, 64)
+
+
 def max_over_ranks(value: float, device=None) -> float:
     """Slowest rank's time (torch.distributed must be initialised when world > 1)."""
     import torch
