@@ -148,13 +148,17 @@ namespace
         else
         {
             // ---- one row per thread, columns in ascending order ----
+            // The ordered sum is a chain of dependent additions (4 cycles each); the loads of
+            // the NEXT tile are issued before the chain of the current one starts, into a
+            // second set of registers, so that their latency and the barrier wait hide
+            // behind the chain.  (With one register set a tile cost ~600 cycles, which held a
+            // block to ~25 GB/s -- just enough for one GPU's bandwidth with 256 blocks.)
             const uint32_t r   = threadIdx.x;
             T              acc = T(0);
-            for(uint32_t kb = 0; kb < numKB; ++kb)
-            {
+            // copies tile kb's column values of row r, and its x values, into registers
+            auto fetch = [&](uint32_t kb, T (&av)[COLS], T (&xv)[COLS]) -> bool {
                 const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
                 const uint32_t h0 = kb * COLS;
-                T xv[COLS];
                 if(!xStaged)
                 {
 #pragma unroll
@@ -162,7 +166,7 @@ namespace
                         xv[j] = (h0 + j < k) ? __ldg(x + h0 + j) : T(0);
                 }
                 if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
-                    break;
+                    return false;
                 if(xStaged)
                 {
                     Vec<T, XV> const* xs
@@ -177,21 +181,52 @@ namespace
                     }
                 }
                 T const* tile = reinterpret_cast<T const*>(tiles + s * SLOT_BYTES);
-                // the row's element of every column first (independent loads) ...
-                T av[COLS];
 #pragma unroll
                 for(uint32_t j = 0; j < COLS; ++j)
                     av[j] = tile[j * ROWS + r];
-                __syncwarp();
-                if((threadIdx.x & 31u) == 0u)
-                    mbar_arrive(&ctl->empty[s]); // slot is in registers: one arrival per warp
-                // ... then the ordered sum.  Columns beyond k hold zeros and must not enter
-                // it (adding +0 could turn a -0 into +0).
+                return true;
+            };
+            // the ordered sum over one tile, then the slot goes back to the loaders (its
+            // values have been consumed, so the loads are certainly complete).  Columns
+            // beyond k hold zeros and must not enter the sum (adding +0 could turn a -0
+            // into +0).
+            auto consume = [&](uint32_t kb, T const (&av)[COLS], T const (&xv)[COLS]) {
+                const uint32_t h0    = kb * COLS;
                 const uint32_t valid = (k - h0) < COLS ? (k - h0) : COLS;
 #pragma unroll
                 for(uint32_t j = 0; j < COLS; ++j)
                     if(j < valid)
                         acc = addRn(acc, mulRn(av[j], xv[j]));
+                __syncwarp();
+                if((threadIdx.x & 31u) == 0u)
+                    mbar_arrive(&ctl->empty[kb % STAGES]); // one arrival per warp
+            };
+            if constexpr(sizeof(T) == 4)
+            {
+                T    avA[COLS], xvA[COLS], avB[COLS], xvB[COLS];
+                bool ok = numKB == 0u || fetch(0, avA, xvA);
+                for(uint32_t kb = 0; ok && kb < numKB; kb += 2)
+                {
+                    const bool has1 = kb + 1 < numKB, has2 = kb + 2 < numKB;
+                    if(has1 && !fetch(kb + 1, avB, xvB))
+                        break;
+                    consume(kb, avA, xvA);
+                    if(has2 && !fetch(kb + 2, avA, xvA))
+                        break;
+                    if(has1)
+                        consume(kb + 1, avB, xvB);
+                }
+            }
+            else
+            {
+                // 64-bit elements: two register sets would not fit; one tile at a time
+                T av[COLS], xv[COLS];
+                for(uint32_t kb = 0; kb < numKB; ++kb)
+                {
+                    if(!fetch(kb, av, xv))
+                        break;
+                    consume(kb, av, xv);
+                }
             }
             if(row0 + r < m && ctl->abort.flag == 0u)
                 yOut[row0 + r] = addRn(mulRn(alpha, acc), mulRn(beta, yIn[row0 + r]));
