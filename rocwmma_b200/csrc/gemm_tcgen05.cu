@@ -24,6 +24,7 @@
 // records the event in the library's device status word.
 #include "common.cuh"
 #include "runtime.cuh"
+#include "tile_schedule.cuh"
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cstdlib>
@@ -33,6 +34,7 @@
 
 using namespace rocwmma;
 using namespace rocwmma::block;
+using b200wmma::TileSchedule;
 
 namespace
 {
@@ -79,6 +81,8 @@ namespace
         uint32_t    tmaStore; // 1: D leaves through shared memory and TMA stores
         uint32_t    aMN, bMN; // 1: operand is MN-major in memory (A column-major, B row-major)
         uint32_t    sumInTmem; // 1: chunked accumulation keeps its running sum in tensor memory
+        uint32_t    wideCols; // pair kernel: tile columns of width bn ...
+        uint32_t    tailCols, bnTail; // ... followed by tailCols columns of width bnTail (0: none)
     };
 
     // One operand tile for one K block.  K-major: one TMA box of `rows` rows x 128 bytes of
@@ -955,19 +959,23 @@ namespace
     __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
         gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmapA,
                                  const __grid_constant__ CUtensorMap tmapB,
+                                 const __grid_constant__ CUtensorMap tmapBTail,
                                  const __grid_constant__ CUtensorMap tmapD,
                                  const GemmParams                    p)
     {
         constexpr uint32_t BK     = ROW_BYTES / sizeof(InT);
         constexpr uint32_t UMMA_K = 32 / sizeof(InT);
-        // The tile width is chosen per launch (a multiple of 32 up to 256) so that the tile
-        // count divides evenly over the pairs; it is the N of the MMA instruction.
+        // The tile width is chosen per launch (a multiple of 32 up to 256); it is the N of the
+        // MMA instruction.  A launch may use a second, narrower width for the right-hand
+        // columns of the output (TileSchedule); tmapBTail is B's tensor map with that box.
         const uint32_t bn    = p.bn;
         const uint32_t IDESC = make_instr_desc(KindOf<InT>::acc, KindOf<InT>::fmt,
                                                KindOf<InT>::fmt, P_TILE_M, bn, p.aMN, p.bMN);
+        const uint32_t IDESC_TAIL
+            = make_instr_desc(KindOf<InT>::acc, KindOf<InT>::fmt, KindOf<InT>::fmt, P_TILE_M,
+                              p.bnTail != 0u ? p.bnTail : bn, p.aMN, p.bMN);
         // bytes per K block and block: its 128 rows of A and its half of the B tile
-        const uint32_t pairSlotBytes = operandTileBytes<InT>(p.aMN != 0u, 128u)
-                                       + operandTileBytes<InT>(p.bMN != 0u, bn / 2u);
+        const uint32_t aSlotBytes = operandTileBytes<InT>(p.aMN != 0u, 128u);
 
         extern __shared__ uint8_t smemRaw[];
         const uint32_t            rawAddr = smem_addr(smemRaw);
@@ -983,11 +991,10 @@ namespace
         const uint32_t nPairs = gridDim.x / 2;
 
         const uint32_t tilesM   = (p.m + P_TILE_M - 1) / P_TILE_M;
-        const uint32_t tilesN   = (p.n + bn - 1) / bn;
-        const uint32_t numTiles = tilesM * tilesN;
         const uint32_t numKB    = (p.k + BK - 1) / BK;
         const uint32_t chunkKB  = p.chunkKB != 0u ? p.chunkKB : numKB; // K blocks per chain
         const uint32_t numChunks = (numKB + chunkKB - 1) / chunkKB;
+        const TileSchedule sched{tilesM, p.wideCols, p.tailCols, bn, p.bnTail, p.band, nPairs};
 
         if(threadIdx.x == 0)
         {
@@ -1006,6 +1013,7 @@ namespace
             mbar_init_fence();
             tma_prefetch_descriptor(&tmapA);
             tma_prefetch_descriptor(&tmapB);
+            tma_prefetch_descriptor(&tmapBTail);
             tma_prefetch_descriptor(&tmapD);
         }
         if(warp == 1)
@@ -1026,12 +1034,17 @@ namespace
             {
                 uint32_t it = 0;
                 bool     ok = true;
-                for(uint32_t t = pairId; ok && t < numTiles; t += nPairs)
+                for(uint32_t i = 0; ok; ++i)
                 {
-                    uint32_t tm, tn;
-                    tileCoord(t, tilesM, tilesN, p.band, tm, tn);
-                    const int32_t rowA = int32_t(tm * P_TILE_M + rank * 128u);
-                    const int32_t rowB = int32_t(tn * bn + rank * (bn / 2u));
+                    uint32_t tm, col0, width;
+                    if(!sched.get(pairId, i, tm, col0, width))
+                        break;
+                    const int32_t  rowA = int32_t(tm * P_TILE_M + rank * 128u);
+                    const int32_t  rowB = int32_t(col0 + rank * (width / 2u));
+                    const void*    mapB = width == bn ? static_cast<void const*>(&tmapB)
+                                                      : static_cast<void const*>(&tmapBTail);
+                    const uint32_t pairSlotBytes
+                        = aSlotBytes + operandTileBytes<InT>(p.bMN != 0u, width / 2u);
                     for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
                     {
                         const uint32_t s  = it % P_STAGES;
@@ -1047,8 +1060,9 @@ namespace
                         const uint32_t leaderFull = map_to_cta(smem_addr(&ctl->full[s]), 0);
                         loadOperandTile<InT, true>(slot, &tmapA, nullptr, leaderFull, p.aMN != 0u,
                                                    uint32_t(rowA), 128u, kb * BK);
-                        loadOperandTile<InT, true>(slot + P_A_BYTES, &tmapB, nullptr, leaderFull,
-                                                   p.bMN != 0u, uint32_t(rowB), bn / 2u, kb * BK);
+                        loadOperandTile<InT, true>(slot + P_A_BYTES, mapB, nullptr, leaderFull,
+                                                   p.bMN != 0u, uint32_t(rowB), width / 2u,
+                                                   kb * BK);
                     }
                 }
             }
@@ -1060,8 +1074,12 @@ namespace
             {
                 uint32_t it = 0, accIter = 0;
                 bool     ok = true;
-                for(uint32_t t = pairId; ok && t < numTiles; t += nPairs)
+                for(uint32_t i = 0; ok; ++i)
                 {
+                    uint32_t tm, col0, width;
+                    if(!sched.get(pairId, i, tm, col0, width))
+                        break;
+                    const uint32_t idesc = width == bn ? IDESC : IDESC_TAIL;
                     for(uint32_t kb0 = 0; ok && kb0 < numKB; kb0 += chunkKB, ++accIter)
                     {
                         const uint32_t buf   = accIter & 1u;
@@ -1092,7 +1110,7 @@ namespace
                             {
                                 const uint64_t da = operandDesc<InT>(aAddr, p.aMN != 0u, ks);
                                 const uint64_t db = operandDesc<InT>(bAddr, p.bMN != 0u, ks);
-                                mma_ss_pair<KindOf<InT>::kind>(dTmem, da, db, IDESC,
+                                mma_ss_pair<KindOf<InT>::kind>(dTmem, da, db, idesc,
                                                                (kb > kb0 || ks > 0u) ? 1u : 0u);
                             }
                             mma_commit_pair(&ctl->empty[s], 0x3); // frees the slot in both blocks
@@ -1112,10 +1130,13 @@ namespace
             const bool     useC  = (p.beta != 0.0) && (p.c != nullptr);
             uint32_t       accIter = 0, stagedGroups = 0;
             bool           ok      = true;
-            for(uint32_t t = pairId; ok && t < numTiles; t += nPairs)
+            for(uint32_t i = 0; ok; ++i)
             {
-                uint32_t tm, tn;
-                tileCoord(t, tilesM, tilesN, p.band, tm, tn);
+                uint32_t tm, col0, width;
+                if(!sched.get(pairId, i, tm, col0, width))
+                    break;
+                GemmParams pt = p; // the drain routines read the tile width from here
+                pt.bn         = width;
                 const uint32_t row = tm * P_TILE_M + rank * 128u + quad * 32u + lane;
                 for(uint32_t ch = 0; ch < numChunks; ++ch, ++accIter)
                 {
@@ -1133,31 +1154,29 @@ namespace
                     {
                         if(p.sumInTmem && numChunks > 1u)
                             drained = drainAccumulatorToTmemSum(&ctl->accFull[buf], accPh,
-                                                                &ctl->abort, taddr, taddrLane, p,
-                                                                alpha, beta, useC, row, tn * bn,
-                                                                mode);
+                                                                &ctl->abort, taddr, taddrLane, pt,
+                                                                alpha, beta, useC, row, col0, mode);
                         else
                             drained = p.tmaStore
                                           ? drainAccumulatorTma<OutT, CompT>(
-                                              &ctl->accFull[buf], accPh, &ctl->abort, taddr, p,
+                                              &ctl->accFull[buf], accPh, &ctl->abort, taddr, pt,
                                               &tmapD, staging, stagedGroups, alpha, beta, useC,
-                                              quad * 32u + lane, tm * P_TILE_M + rank * 128u,
-                                              tn * bn, mode, threadIdx.x == 64u)
+                                              quad * 32u + lane, tm * P_TILE_M + rank * 128u, col0,
+                                              mode, threadIdx.x == 64u)
                                           : drainAccumulator<OutT, CompT>(
-                                              &ctl->accFull[buf], accPh, &ctl->abort, taddr, p,
-                                              alpha, beta, useC, row, tn * bn, mode);
+                                              &ctl->accFull[buf], accPh, &ctl->abort, taddr, pt,
+                                              alpha, beta, useC, row, col0, mode);
                     }
                     else
                         drained = p.tmaStore
                                       ? drainAccumulatorTma<OutT, CompT>(
-                                          &ctl->accFull[buf], accPh, &ctl->abort, taddr, p, &tmapD,
-                                          staging, stagedGroups, alpha, beta, useC,
-                                          quad * 32u + lane, tm * P_TILE_M + rank * 128u, tn * bn,
+                                          &ctl->accFull[buf], accPh, &ctl->abort, taddr, pt,
+                                          &tmapD, staging, stagedGroups, alpha, beta, useC,
+                                          quad * 32u + lane, tm * P_TILE_M + rank * 128u, col0,
                                           mode, threadIdx.x == 64u)
                                       : drainAccumulator<OutT, CompT>(&ctl->accFull[buf], accPh,
-                                                                      &ctl->abort, taddr, p, alpha,
-                                                                      beta, useC, row, tn * bn,
-                                                                      mode);
+                                                                      &ctl->abort, taddr, pt, alpha,
+                                                                      beta, useC, row, col0, mode);
                     if(!drained)
                     {
                         ok = false;
@@ -1363,7 +1382,7 @@ namespace
         useTma = useTma && tmaSafe;
         GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
                      status, chunkKB, wide, BN, bandEnv ? bandEnv : GROUP_M, useTma ? 1u : 0u,
-                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u};
+                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u};
         CUtensorMap mapA, mapB, mapD;
         {
             int rcD = makeOutputMap(&mapD, outputMapType<OutT>(), sizeof(OutT), d, m, n, ldd);
@@ -1373,55 +1392,101 @@ namespace
 
         if(pairEnabled() && m > BM && sms >= 2)
         {
-            // Tile width: 256, 224 or 192 columns, whichever needs the least time by a simple
-            // model -- waves of tiles over the pairs, each wave costing the tile width plus a
-            // fixed part (A is loaded per tile whatever its width, so narrow tiles pay more
-            // L2 traffic per flop; measured: 128-wide tiles lose at 4096^3).  8192^2 and 4096^2
-            // keep 256; the 2048- and 1024-row shards of a 4- or 8-GPU run of 8192^3 come out
-            // at 224, which turns 3.46 resp. 1.73 waves into 4 resp. 2 full ones.
+            // Tile widths.  A tile costs its width plus a fixed part (A is loaded per tile
+            // whatever its width, so narrow tiles pay more L2 traffic per flop; measured:
+            // 128-wide tiles lose at 4096^3), and a launch takes as long as its busiest pair.
+            // Candidates: one width for the whole output (256, 224 or 192 columns).  8192^2 and
+            // 4096^2 keep 256; the 2048- and 1024-row shards of a 4- or 8-GPU run of 8192^3
+            // come out at 224, which turns 3.46 resp. 1.73 waves into 4 resp. 2 full ones.
+            // The kernel can also follow its wide tile columns with 128-wide ones that fill the
+            // last, partial wave (TileSchedule; B200WMMA_GEMM_TAIL=1).  That is off by default
+            // because it measured slower: a 4096^2 output (256 tiles on 74 pairs, 3.46 waves)
+            // as 13 wide + 6 narrow tile columns ran 3 % slower than 16 wide ones -- the last
+            // wave's 34 tiles already run faster than a full wave (less contention, higher
+            // clock), and narrow tiles cost more than their width suggests.
             const uint32_t pairsMax = uint32_t(sms / 2);
             const uint32_t tilesM   = (m + P_TILE_M - 1) / P_TILE_M;
-            uint32_t       bn = BN, bestCost = 0xffffffffu;
-            for(uint32_t cand = 256; cand >= 192; cand -= 32)
-            {
-                const uint32_t tiles = tilesM * ((n + cand - 1) / cand);
-                const uint32_t waves = (tiles + pairsMax - 1) / pairsMax;
-                const uint32_t cost  = waves * (cand + 64u);
-                if(cost < bestCost)
-                {
-                    bestCost = cost;
-                    bn       = cand;
-                }
-            }
-            // problems narrower than a tile: no wider than needed (multiples of 32)
-            if(n < bn)
-                bn = n <= 128u ? 128u : (n + 31u) / 32u * 32u;
-            // B200WMMA_GEMM_BN overrides the tile width (tuning only)
+            // B200WMMA_GEMM_BN forces one width, B200WMMA_GEMM_TMEMSUM=0 keeps the running sum
+            // of chunked accumulation in D (tuning / comparison only)
             static const uint32_t bnEnv = [] {
                 const char* e = getenv("B200WMMA_GEMM_BN");
-                return e ? uint32_t(atoi(e)) : 0u;
+                const uint32_t v = e ? uint32_t(atoi(e)) : 0u;
+                return (v >= 128 && v <= 256 && v % 32 == 0) ? v : 0u;
             }();
-            if(bnEnv >= 128 && bnEnv <= 256 && bnEnv % 32 == 0)
-                bn = bnEnv;
+            static const bool tmemSumEnv = [] {
+                const char* e = getenv("B200WMMA_GEMM_TMEMSUM");
+                return !(e && e[0] == '0');
+            }();
             // Chunked accumulation: tiles of at most 160 columns leave room in tensor memory
             // for the running sum, which takes the chunks' read-modify-write of D (an L2 round
             // trip per 512 elements of K) out of the picture.  Measured on xf32 4096^3: 446
             // TFLOP/s with the sum in D (256-wide tiles, TMA reduce-add), 572 with the sum in
             // tensor memory (160-wide tiles); one unbroken chain runs at 588 with 160-wide and
             // 692 with 256-wide tiles, so what is left is the narrower tile, not the chunks.
-            // B200WMMA_GEMM_TMEMSUM=0 keeps the sum in D (tuning / comparison only).
-            static const bool tmemSumEnv = [] {
-                const char* e = getenv("B200WMMA_GEMM_TMEMSUM");
-                return !(e && e[0] == '0');
-            }();
-            if(chunkKB != 0u && tmemSumEnv)
+            const bool tmemSum = chunkKB != 0u && tmemSumEnv;
+            if(tmemSum)
             {
-                if(bnEnv == 0u || bn > 160u)
-                    bn = n <= 128u ? 128u : 160u;
                 p.sumInTmem = 1u;
                 p.tmaStore  = 0u;
             }
-            p.bn   = bn;
+            const uint32_t widest = tmemSum ? 160u : 256u, narrowest = tmemSum ? 128u : 192u;
+            auto makespan = [&](uint32_t bnW, uint32_t wideCols, uint32_t tailCols, uint32_t bnT) {
+                const uint32_t total = tilesM * (wideCols + tailCols);
+                const uint32_t pairs = total < pairsMax ? total : pairsMax;
+                TileSchedule   sc{tilesM, wideCols, tailCols, bnW, bnT, GROUP_M, pairs};
+                uint32_t       worst = 0;
+                for(uint32_t pr = 0; pr < pairs; ++pr)
+                {
+                    uint32_t load = 0, tm, col0, width;
+                    for(uint32_t i = 0; sc.get(pr, i, tm, col0, width); ++i)
+                        load += width + 64u;
+                    worst = load > worst ? load : worst;
+                }
+                return worst;
+            };
+            uint32_t bn = widest, wideCols = (n + widest - 1) / widest, tailCols = 0, bnTail = 0;
+            if(bnEnv != 0u && !(tmemSum && bnEnv > 160u))
+            {
+                bn       = bnEnv;
+                wideCols = (n + bn - 1) / bn;
+            }
+            else if(n <= widest)
+            {
+                // narrower than one tile: no wider than needed (multiples of 32)
+                bn       = n <= 128u ? 128u : (n + 31u) / 32u * 32u;
+                wideCols = 1;
+            }
+            else
+            {
+                uint32_t best = 0xffffffffu;
+                for(uint32_t cand = widest; cand >= narrowest; cand -= 32)
+                {
+                    const uint32_t cols = (n + cand - 1) / cand;
+                    const uint32_t cost = makespan(cand, cols, 0, 0);
+                    if(cost < best)
+                        best = cost, bn = cand, wideCols = cols, tailCols = 0, bnTail = 0;
+                }
+                // wide columns, then 128-wide ones over what is left (tuning switch, see above)
+                const char* tailEnv = getenv("B200WMMA_GEMM_TAIL");
+                if(widest > 128u && tailEnv && tailEnv[0] == '1')
+                {
+                    const uint32_t full = n / widest;
+                    for(uint32_t wc = full > 6u ? full - 6u : 1u; wc <= full; ++wc)
+                    {
+                        const uint32_t left = n - wc * widest;
+                        if(left == 0u)
+                            continue;
+                        const uint32_t tc   = (left + 127u) / 128u;
+                        const uint32_t cost = makespan(widest, wc, tc, 128u);
+                        if(cost + cost / 50u < best)
+                            best = cost, bn = widest, wideCols = wc, tailCols = tc, bnTail = 128u;
+                    }
+                }
+            }
+            p.bn       = bn;
+            p.wideCols = wideCols;
+            p.tailCols = tailCols;
+            p.bnTail   = bnTail;
             int rc = aMN ? makeOperandMapMN(&mapA, dt, sizeof(InT), a, m, k, lda)
                          : makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, 128);
             if(rc != B200WMMA_OK)
@@ -1430,14 +1495,23 @@ namespace
                      : makeOperandMap(&mapB, dt, sizeof(InT), b, n, k, ldb, bn / 2);
             if(rc != B200WMMA_OK)
                 return rc;
+            // B again with the box of a narrow tile (K-major boxes are half a tile high; the
+            // MN-major box does not depend on the tile width)
+            CUtensorMap mapBTail = mapB;
+            if(bnTail != 0u && !bMN)
+            {
+                rc = makeOperandMap(&mapBTail, dt, sizeof(InT), b, n, k, ldb, bnTail / 2);
+                if(rc != B200WMMA_OK)
+                    return rc;
+            }
             auto        kernel = gemm_tcgen05_pair_kernel<InT, OutT, CompT>;
             static bool done[64] = {};
             rc = optInSharedMemory(kernel, P_SMEM_BYTES, done);
             if(rc != B200WMMA_OK)
                 return rc;
-            const uint32_t tiles = tilesM * ((n + bn - 1) / bn);
+            const uint32_t tiles = tilesM * (wideCols + tailCols);
             const uint32_t pairs = tiles < pairsMax ? tiles : pairsMax;
-            kernel<<<2 * pairs, NUM_THREADS, P_SMEM_BYTES, stream>>>(mapA, mapB, mapD, p);
+            kernel<<<2 * pairs, NUM_THREADS, P_SMEM_BYTES, stream>>>(mapA, mapB, mapBTail, mapD, p);
             return b200wmma::cudaToStatus(cudaGetLastError());
         }
 

@@ -15,6 +15,7 @@
 #include <rocwmma/rocwmma_block.hpp>
 #include <rocwmma/rocwmma_coop.hpp>
 #include <rocwmma/rocwmma_transforms.hpp>
+#include "tile_schedule.cuh"
 
 using namespace rocwmma;
 
@@ -266,6 +267,46 @@ TEST_API int b200wmma_test_bulk_copy(const void* src, void* dst, uint32_t rows, 
     bulkCopyKernel<<<1, 32, rows * row_bytes, static_cast<cudaStream_t>(stream)>>>(
         static_cast<uint8_t const*>(src), static_cast<uint8_t*>(dst), rows, row_bytes, status);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Host-side walk over the pair kernel's tile schedule: counts[tm * (wide_cols + tail_cols) + c]
+// is incremented for every tile some pair is given (tile column c counts wide columns first),
+// loads[p] is the summed width of pair p's tiles.  Returns the number of tiles handed out, or
+// -1 when a tile lies outside the grid or has the wrong width.
+TEST_API int b200wmma_test_tile_schedule(uint32_t tiles_m, uint32_t wide_cols, uint32_t tail_cols,
+                                         uint32_t bn, uint32_t bn_tail, uint32_t band,
+                                         uint32_t pairs, uint32_t* counts, uint32_t* loads)
+{
+    b200wmma::TileSchedule sc{tiles_m, wide_cols, tail_cols, bn, bn_tail, band, pairs};
+    int                    total = 0;
+    for(uint32_t p = 0; p < pairs; ++p)
+    {
+        uint32_t tm, col0, width;
+        for(uint32_t i = 0; sc.get(p, i, tm, col0, width); ++i)
+        {
+            uint32_t c;
+            if(col0 < wide_cols * bn)
+            {
+                if(width != bn || col0 % bn != 0)
+                    return -1;
+                c = col0 / bn;
+            }
+            else
+            {
+                if(width != bn_tail || (col0 - wide_cols * bn) % bn_tail != 0)
+                    return -1;
+                c = wide_cols + (col0 - wide_cols * bn) / bn_tail;
+            }
+            if(tm >= tiles_m || c >= wide_cols + tail_cols)
+                return -1;
+            counts[tm * (wide_cols + tail_cols) + c] += 1;
+            loads[p] += width;
+            ++total;
+            if(i > 100000)
+                return -1;
+        }
+    }
+    return total;
 }
 
 // Runs the never-satisfied wait with a limit of `limit_cycles` SM cycles (keep it around a

@@ -1,0 +1,78 @@
+// Tile schedule of the CTA-pair GEMM kernel: host and device see the same sequence.
+#ifndef ROCWMMA_B200_CSRC_TILE_SCHEDULE_CUH
+#define ROCWMMA_B200_CSRC_TILE_SCHEDULE_CUH
+#include <cstdint>
+
+namespace b200wmma
+{
+    // Which tiles a CTA pair works on, in which order (pair kernel).  The output is cut into
+    // `wideCols` tile columns of width bn and, to their right, `tailCols` columns of width
+    // bnTail.  Every pair takes the wide tiles p, p + P, p + 2P, ...  (P pairs); when their
+    // number does not divide by P some pairs are one tile short -- up to a quarter of the run
+    // on a 4096^2 output (256 tiles on 74 pairs).  The narrow tiles of the tail fill that gap:
+    // the pairs that are short take two of them each first, the rest is dealt round-robin.
+    // All three roles of both blocks of a pair call get() with i = 0, 1, 2, ... and see the
+    // same sequence; the host uses the same code to compare schedules.
+    struct TileSchedule
+    {
+        uint32_t tilesM, wideCols, tailCols, bn, bnTail, band, pairs;
+
+        __host__ __device__ uint32_t wideTiles() const
+        {
+            return tilesM * wideCols;
+        }
+        __host__ __device__ uint32_t tailTiles() const
+        {
+            return tilesM * tailCols;
+        }
+        // i-th tile of pair p: tile row, first column, width.  false when the pair is done.
+        __host__ __device__ bool get(uint32_t p, uint32_t i, uint32_t& tm, uint32_t& col0,
+                                     uint32_t& width) const
+        {
+            const uint32_t W = wideTiles(), T = tailTiles();
+            const uint32_t base = W / pairs, nHi = W % pairs; // pairs [0, nHi) have base + 1
+            const uint32_t mine = base + (p < nHi ? 1u : 0u);
+            if(i < mine)
+            {
+                const uint32_t t        = p + i * pairs;
+                const uint32_t perGroup = band * wideCols;
+                const uint32_t group    = t / perGroup;
+                const uint32_t firstM   = group * band;
+                const uint32_t rows     = (tilesM - firstM) < band ? (tilesM - firstM) : band;
+                const uint32_t r        = t % perGroup;
+                tm                      = firstM + r % rows;
+                col0                    = (r / rows) * bn;
+                width                   = bn;
+                return true;
+            }
+            i -= mine;
+            // the pairs that are one wide tile short take two tail tiles each first
+            const uint32_t nLo    = nHi == 0u ? 0u : pairs - nHi;
+            const uint32_t bonus  = (2u * nLo) < T ? (2u * nLo) : T; // tail tiles dealt that way
+            uint32_t       j      = 0xffffffffu;
+            if(p >= nHi && nLo != 0u)
+            {
+                const uint32_t l  = p - nHi;
+                const uint32_t my = (l < bonus ? 1u : 0u) + (l + nLo < bonus ? 1u : 0u);
+                if(i < my)
+                    j = l + i * nLo;
+                else
+                    i -= my;
+            }
+            if(j == 0xffffffffu)
+            {
+                const uint32_t rest = T - bonus;
+                const uint32_t jj   = p + i * pairs;
+                if(jj >= rest)
+                    return false;
+                j = bonus + jj;
+            }
+            tm    = j % tilesM;
+            col0  = wideCols * bn + (j / tilesM) * bnTail;
+            width = bnTail;
+            return true;
+        }
+    };
+
+} // namespace b200wmma
+#endif

@@ -101,6 +101,25 @@ def test_block_gemm_other_layouts(in_t, out_t, la, lb, m, n, k):
     assert 0 <= O.max_rel_err(out_t, got, want) <= tolerance(in_t, out_t)
 
 
+@pytest.mark.parametrize("in_t,out_t", [(O.F16, O.F16), (O.BF16, O.F32), (O.XF32, O.F32)])
+def test_two_width_tile_schedule(in_t, out_t, monkeypatch):
+    """The pair kernel's optional schedule of wide tile columns followed by 128-wide ones
+    (off by default, B200WMMA_GEMM_TAIL=1): for a 4096 x 4072 output on 74 pairs the launcher
+    then picks 13 wide and 6 narrow columns, the last one ragged, so both widths, both tensor
+    maps of B and the edge masks are exercised (K = 640 also makes xf32 accumulate in chunks)."""
+    monkeypatch.setenv("B200WMMA_GEMM_TAIL", "1")
+    m, n, k = 4096, 4072, 640
+    case = dict(in_t=in_t, out_t=out_t, m=m, n=n, k=k, la=ROW, lb=COL, alpha=2.0, beta=-1.0,
+                seed=77)
+    a, b, c = gemm_inputs(case)
+    want = O.gemm(in_t, out_t, m, n, k, a, b, c, 2.0, -1.0)
+    got = api.gemm(in_t, out_t, m, n, k, to_device(a, in_t), to_device(b, in_t),
+                   to_device(c, out_t), 2.0, -1.0)
+    api.check_device()
+    err = O.max_rel_err(out_t, to_host(got, out_t), want)
+    assert 0 <= err <= tolerance(in_t, out_t), err
+
+
 def test_beta_zero_never_reads_c():
     case = dict(in_t=O.F16, out_t=O.F16, m=256, n=256, k=128, la=ROW, lb=COL, alpha=1.0, beta=0.0,
                 seed=70)

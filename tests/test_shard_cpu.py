@@ -74,3 +74,44 @@ def test_two_ranks_reproduce_the_single_rank_result(tmp_path):
     wantf = O.dlrm_fwd(O.F16, x, 5, 16, 48)
     assert np.array_equal(np.load(tmp_path / "f.npy").view(np.uint16), wantf.view(np.uint16))
     assert np.load(tmp_path / "t.npy")[0] == 2.0      # max over ranks of (rank + 1)
+
+
+def test_pair_kernel_tile_schedule_hands_out_every_tile_once():
+    """The CTA-pair GEMM's tile schedule (wide tile columns, then 128-wide ones that fill the
+    last partial wave): every tile exactly once, for many grids and pair counts, and the
+    busiest pair of a 4096^2 output carries less than the 4 wide tiles it had before."""
+    import ctypes as C
+    import os
+
+    import numpy as np
+
+    from rocwmma_b200 import _lib
+    lib = C.CDLL(os.path.join(os.path.dirname(_lib.LIB_PATH), "libb200wmma_test.so"))
+    fn = lib.b200wmma_test_tile_schedule
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_uint32] * 7 + [C.c_void_p, C.c_void_p]
+
+    def walk(tiles_m, wide, tail, pairs, band=16, bn=256, bn_tail=128):
+        counts = np.zeros(tiles_m * (wide + tail), np.uint32)
+        loads = np.zeros(pairs, np.uint32)
+        total = fn(tiles_m, wide, tail, bn, bn_tail, band, pairs, counts.ctypes.data,
+                   loads.ctypes.data)
+        return total, counts, loads
+
+    rng = np.random.default_rng(0)
+    cases = [(16, 16, 0, 74), (16, 13, 6, 74), (32, 32, 0, 74), (1, 1, 0, 1), (3, 0, 5, 7),
+             (16, 13, 6, 1), (5, 2, 1, 74)]
+    cases += [(int(rng.integers(1, 40)), int(rng.integers(0, 20)), int(rng.integers(0, 9)),
+               int(rng.integers(1, 80))) for _ in range(200)]
+    for tiles_m, wide, tail, pairs in cases:
+        if wide + tail == 0:
+            continue
+        total, counts, loads = walk(tiles_m, wide, tail, pairs, band=int(rng.integers(1, 20)))
+        assert total == tiles_m * (wide + tail), (tiles_m, wide, tail, pairs, total)
+        assert (counts == 1).all(), (tiles_m, wide, tail, pairs)
+    # 4096^2 on 74 pairs: 256-wide tiles only -> 4 tiles on the busiest pair; 13 wide + 6 narrow
+    # tile columns -> at most 3 wide + 1 narrow, or 2 wide + 3 narrow
+    _, _, uniform = walk(16, 16, 0, 74)
+    _, _, mixed = walk(16, 13, 6, 74)
+    assert uniform.max() == 4 * 256
+    assert mixed.max() <= 3 * 256 + 128 and mixed.sum() == 16 * (13 * 256 + 6 * 128)
