@@ -49,7 +49,7 @@ namespace
     constexpr uint32_t TMEM_COLS   = ACC_BUFS * BN; // 512
     constexpr uint32_t NUM_THREADS = 192;
     constexpr uint32_t EPI_THREADS = 128;
-    constexpr uint32_t GROUP_M     = 16; // tile rows that share a band of B in L2
+    constexpr uint32_t GROUP_M     = 16; // most tile rows in a raster band (see bandRows)
 
     struct SharedControl
     {
@@ -1325,6 +1325,20 @@ namespace
     }
 
     // `status`: device word that records a bounded wait giving up (may be nullptr).
+    // Tile rows per raster band.  Tiles are walked band by band, column by column inside a
+    // band, so the rows of A that a band needs stay in L2 while B streams past.  Measured on
+    // 8192^3: with 64 MB of A per band (16 tile rows of fp16) DRAM traffic is 3.5 x the
+    // algorithmic bytes; 32 MB per band is 0.7 % faster there (less energy under the power
+    // cap), while 8-bit inputs and 4096-deep problems -- 32 MB per band at 16 rows -- lose
+    // 2 % with 8 rows.  Hence: about 32 MB of A per band, between 4 and 16 tile rows.
+    inline uint32_t bandRows(uint32_t k, size_t elemBytes)
+    {
+        const size_t perTileRow = size_t(P_TILE_M) * k * elemBytes;
+        size_t       rows       = perTileRow ? (size_t(32) << 20) / perTileRow : GROUP_M;
+        rows                    = rows < 4 ? 4 : rows;
+        return uint32_t(rows > GROUP_M ? GROUP_M : rows);
+    }
+
     template <typename InT, typename OutT, typename CompT>
     int launchWithStatus(CUtensorMapDataType dt, uint32_t m, uint32_t n, uint32_t k,
                          void const* a, void const* b, void const* c, void* d, uint32_t lda,
@@ -1381,7 +1395,8 @@ namespace
             useTma = true;
         useTma = useTma && tmaSafe;
         GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
-                     status, chunkKB, wide, BN, bandEnv ? bandEnv : GROUP_M, useTma ? 1u : 0u,
+                     status, chunkKB, wide, BN, bandEnv ? bandEnv : bandRows(k, sizeof(InT)),
+                     useTma ? 1u : 0u,
                      aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u};
         CUtensorMap mapA, mapB, mapD;
         {
