@@ -9,7 +9,7 @@ bf16 peak scaled per type; GEMV and DLRM report algorithmic bytes / time against
 measured HBM copy bandwidth.  Inputs are random device tensors (timing only; parity is
 the test-suite's job).  Timed with CUDA events over `iters` back-to-back launches after
 3 warm-ups; working sets that do not exceed the 126 MB L2 are timed launch by launch with an
-L2 flush in between.
+L2 flush (a 256 MiB read) in between.
 
 Under torchrun (python -m torch.distributed.run --nproc-per-node N -m rocwmma_b200.bench_all)
 every configuration is split over the N GPUs the way rocwmma_b200.shard says -- GEMM by rows
@@ -61,7 +61,7 @@ def timed(fn, iters, working_set=None):
     """Per-launch time in ms, the slowest rank's.  A working set larger than the L2 is timed
     as `iters` back-to-back launches between two device events; a smaller one (the 1024^3
     sample, a shard of a many-GPU run) would be served from L2, so every launch is then
-    timed on its own with a 256 MiB buffer written in between."""
+    timed on its own with a 256 MiB buffer read in between."""
     global _flush
     for _ in range(3):
         fn()
@@ -76,10 +76,12 @@ def timed(fn, iters, working_set=None):
         total = e0.elapsed_time(e1)
     else:
         if _flush is None:
-            _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+            _flush = torch.zeros(64 << 20, dtype=torch.int32, device="cuda")   # 256 MiB
         pairs = []
         for i in range(iters):
-            _flush.fill_(i & 0xFF)
+            # evict by READING twice the L2's size: a written buffer would leave the L2 full
+            # of dirty lines whose write-back the timed kernel then pays for
+            _flush.sum()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()

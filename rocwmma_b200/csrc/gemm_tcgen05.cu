@@ -496,16 +496,32 @@ namespace
         if(!mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL))
             return false;
         tc_fence_after_sync();
-#pragma unroll 1
-        for(uint32_t chunk = 0; chunk < groups; ++chunk)
-        {
-            uint32_t raw[32];
-            __syncwarp(); // rows masked off below rejoin before the warp-wide load
-            tmem_load_32x32b_x32(taddrRowBase + chunk * 32u, raw); // warp-wide
-            tmem_load_wait();
+        // Two register sets: the tensor-memory load of the next 32 columns is in flight while
+        // the current ones are converted and stored.  Inside a run of tiles the whole drain
+        // hides behind the next tile's MMAs; after a block's last tile it is exposed, and
+        // a 1024-row shard of an 8-GPU run has only two tiles per pair.
+        uint32_t rawA[32], rawB[32];
+        auto     emit = [&](uint32_t const (&raw)[32], uint32_t chunk) {
             const uint32_t col0 = colBase + chunk * 32u;
             if(row < p.m && col0 < p.n)
                 epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0, mode);
+            __syncwarp(); // rows masked off above rejoin before the next warp-wide load
+        };
+        tmem_load_32x32b_x32(taddrRowBase, rawA); // warp-wide
+#pragma unroll 1
+        for(uint32_t chunk = 0; chunk < groups; chunk += 2)
+        {
+            tmem_load_wait();
+            if(chunk + 1 < groups)
+                tmem_load_32x32b_x32(taddrRowBase + (chunk + 1) * 32u, rawB);
+            emit(rawA, chunk);
+            if(chunk + 1 < groups)
+            {
+                tmem_load_wait();
+                if(chunk + 2 < groups)
+                    tmem_load_32x32b_x32(taddrRowBase + (chunk + 2) * 32u, rawA);
+                emit(rawB, chunk + 1);
+            }
         }
         tc_fence_before_sync();
         return true;
