@@ -414,11 +414,11 @@ namespace
                                             AbortState* abort, uint32_t taddrRowBase,
                                             GemmParams const& p, CompT alpha, CompT beta,
                                             bool useC, uint32_t row, uint32_t colBase,
-                                            uint32_t mode)
+                                            uint32_t mode, uint32_t bnTile)
     {
         constexpr bool CAN_CHUNK
             = std::is_same<OutT, float>::value && std::is_same<CompT, float>::value;
-        const uint32_t groups = p.bn / 32u; // 32-column groups in this tile
+        const uint32_t groups = bnTile / 32u; // 32-column groups in this tile
         if constexpr(CAN_CHUNK)
         {
             if(mode == EPI_MIDDLE || mode == EPI_LAST)
@@ -462,7 +462,7 @@ namespace
             // first two before the accumulator is even ready, so that their latency hides
             // behind the wait and behind the groups in front of them (fetched group by group
             // inside the loop they cost 15 % of a 4096^3 bf16 -> fp32 product).
-            constexpr uint32_t AHEAD = 2;
+            constexpr uint32_t AHEAD = sizeof(OutT) >= 4 ? 1u : 2u; // 32 registers per group of fp32
             alignas(32) OutT   cq[AHEAD + 1][32];
             const bool         rowValid = row < p.m;
             OutT const*        cRow
@@ -546,9 +546,10 @@ namespace
                                                      AbortState* abort, uint32_t taddrAcc,
                                                      uint32_t taddrLane, GemmParams const& p,
                                                      float alpha, float beta, bool useC,
-                                                     uint32_t row, uint32_t colBase, uint32_t mode)
+                                                     uint32_t row, uint32_t colBase, uint32_t mode,
+                                                     uint32_t bnTile)
     {
-        const uint32_t groups = p.bn / 32u;
+        const uint32_t groups = bnTile / 32u;
         if(mode == EPI_FIRST || mode == EPI_MIDDLE)
         {
             if(!mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL))
@@ -563,7 +564,7 @@ namespace
                 if(mode == EPI_MIDDLE)
                 {
                     uint32_t sum[32];
-                    tmem_load_32x32b_x32(taddrLane + sumColumn(g, p.bn), sum);
+                    tmem_load_32x32b_x32(taddrLane + sumColumn(g, bnTile), sum);
                     tmem_load_wait();
 #pragma unroll
                     for(uint32_t e = 0; e < 32; ++e)
@@ -572,48 +573,38 @@ namespace
                 }
                 else
                     tmem_load_wait();
-                tmem_store_32x32b_x32(taddrLane + sumColumn(g, p.bn), raw);
+                tmem_store_32x32b_x32(taddrLane + sumColumn(g, bnTile), raw);
             }
             tmem_store_wait();
             tc_fence_before_sync();
             return true;
         }
-        // last chunk: D = alpha * (sum + acc) + beta * C, C fetched two groups ahead
-        constexpr uint32_t AHEAD = 2;
-        alignas(32) float  cq[AHEAD + 1][32];
-        const bool         rowValid = row < p.m;
-        float const*       cRow
-            = static_cast<float const*>(p.c) + size_t(rowValid ? row : 0u) * p.ldc;
-        if(useC)
-        {
-#pragma unroll
-            for(uint32_t c = 0; c < AHEAD; ++c)
-                loadGroup(cq[c], cRow, colBase + c * 32u, p.n, rowValid, p.wide != 0u);
-        }
+        // last chunk: D = alpha * (sum + acc) + beta * C.  The sum is added here (the same
+        // operations in the same order as the EPI_LAST form of the row epilogue), so that its
+        // registers are free before the row leaves.  C is read group by group, not ahead of
+        // use: with prefetch buffers on top of the two tensor-memory register sets every
+        // fp32-output instantiation of the kernel spilled (3.4 KB of spill stores), which cost
+        // the chunk drains -- seven of eight drains per tile -- more than the prefetch saved
+        // in the eighth.
+        const bool rowValid = row < p.m;
         if(!mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL))
             return false;
         tc_fence_after_sync();
-#pragma unroll
-        for(uint32_t g = 0; g < 160u / 32u; ++g)
+#pragma unroll 1
+        for(uint32_t g = 0; g < groups; ++g)
         {
-            if(g >= groups)
-                break;
-            if(useC && g + AHEAD < 160u / 32u)
-                loadGroup(cq[(g + AHEAD) % (AHEAD + 1)], cRow, colBase + (g + AHEAD) * 32u, p.n,
-                          rowValid, p.wide != 0u);
             uint32_t raw[32], sum[32];
             __syncwarp();
             tmem_load_32x32b_x32(taddrAcc + g * 32u, raw);
-            tmem_load_32x32b_x32(taddrLane + sumColumn(g, p.bn), sum);
+            tmem_load_32x32b_x32(taddrLane + sumColumn(g, bnTile), sum);
             tmem_load_wait();
-            float dq[32];
 #pragma unroll
             for(uint32_t e = 0; e < 32; ++e)
-                dq[e] = __uint_as_float(sum[e]);
+                raw[e] = __float_as_uint(
+                    __fadd_rn(__uint_as_float(sum[e]), __uint_as_float(raw[e])));
             const uint32_t col0 = colBase + g * 32u;
             if(rowValid && col0 < p.n)
-                epilogueRow<float, float>(raw, p, alpha, beta, useC, row, col0, EPI_LAST, dq,
-                                          useC ? cq[g % (AHEAD + 1)] : nullptr);
+                epilogueRow<float, float>(raw, p, alpha, beta, useC, row, col0, EPI_WHOLE);
         }
         tc_fence_before_sync();
         return true;
@@ -644,12 +635,13 @@ namespace
                                                uint8_t* staging, uint32_t& stagedGroups,
                                                CompT alpha, CompT beta, bool useC,
                                                uint32_t rowInTile, uint32_t tileRow0,
-                                               uint32_t colBase, uint32_t mode, bool leader)
+                                               uint32_t colBase, uint32_t mode, bool leader,
+                                               uint32_t bnTile)
     {
         constexpr uint32_t ROW_B  = 32 * sizeof(OutT); // bytes of one staged row (128 or 64)
         constexpr uint32_t VEC    = 16 / sizeof(OutT); // elements per 16-byte chunk
         constexpr uint32_t CHUNKS = ROW_B / 16;
-        const uint32_t     groups = p.bn / 32u;
+        const uint32_t     groups = bnTile / 32u;
         const uint32_t     row    = tileRow0 + rowInTile;
         const bool         adds   = (mode == EPI_MIDDLE || mode == EPI_LAST);
         const bool         readC  = useC && !adds && row < p.m;
@@ -907,10 +899,10 @@ namespace
                               ? drainAccumulatorTma<OutT, CompT>(
                                   &ctl->accFull[buf], accPh, &ctl->abort, taddr, p, &tmapD, staging,
                                   stagedGroups, alpha, beta, useC, quad * 32u + lane, tm * BM,
-                                  tn * BN, mode, threadIdx.x == 64u)
+                                  tn * BN, mode, threadIdx.x == 64u, BN)
                               : drainAccumulator<OutT, CompT>(&ctl->accFull[buf], accPh,
                                                               &ctl->abort, taddr, p, alpha, beta,
-                                                              useC, row, tn * BN, mode);
+                                                              useC, row, tn * BN, mode, BN);
                     if(!drained)
                     {
                         ok = false;
@@ -1151,8 +1143,6 @@ namespace
                 uint32_t tm, col0, width;
                 if(!sched.get(pairId, i, tm, col0, width))
                     break;
-                GemmParams pt = p; // the drain routines read the tile width from here
-                pt.bn         = width;
                 const uint32_t row = tm * P_TILE_M + rank * 128u + quad * 32u + lane;
                 for(uint32_t ch = 0; ch < numChunks; ++ch, ++accIter)
                 {
@@ -1170,29 +1160,31 @@ namespace
                     {
                         if(p.sumInTmem && numChunks > 1u)
                             drained = drainAccumulatorToTmemSum(&ctl->accFull[buf], accPh,
-                                                                &ctl->abort, taddr, taddrLane, pt,
-                                                                alpha, beta, useC, row, col0, mode);
+                                                                &ctl->abort, taddr, taddrLane, p,
+                                                                alpha, beta, useC, row, col0, mode,
+                                                                width);
                         else
                             drained = p.tmaStore
                                           ? drainAccumulatorTma<OutT, CompT>(
-                                              &ctl->accFull[buf], accPh, &ctl->abort, taddr, pt,
+                                              &ctl->accFull[buf], accPh, &ctl->abort, taddr, p,
                                               &tmapD, staging, stagedGroups, alpha, beta, useC,
                                               quad * 32u + lane, tm * P_TILE_M + rank * 128u, col0,
-                                              mode, threadIdx.x == 64u)
+                                              mode, threadIdx.x == 64u, width)
                                           : drainAccumulator<OutT, CompT>(
-                                              &ctl->accFull[buf], accPh, &ctl->abort, taddr, pt,
-                                              alpha, beta, useC, row, col0, mode);
+                                              &ctl->accFull[buf], accPh, &ctl->abort, taddr, p,
+                                              alpha, beta, useC, row, col0, mode, width);
                     }
                     else
                         drained = p.tmaStore
                                       ? drainAccumulatorTma<OutT, CompT>(
-                                          &ctl->accFull[buf], accPh, &ctl->abort, taddr, pt,
-                                          &tmapD, staging, stagedGroups, alpha, beta, useC,
+                                          &ctl->accFull[buf], accPh, &ctl->abort, taddr, p, &tmapD,
+                                          staging, stagedGroups, alpha, beta, useC,
                                           quad * 32u + lane, tm * P_TILE_M + rank * 128u, col0,
-                                          mode, threadIdx.x == 64u)
+                                          mode, threadIdx.x == 64u, width)
                                       : drainAccumulator<OutT, CompT>(&ctl->accFull[buf], accPh,
-                                                                      &ctl->abort, taddr, pt, alpha,
-                                                                      beta, useC, row, col0, mode);
+                                                                      &ctl->abort, taddr, p, alpha,
+                                                                      beta, useC, row, col0, mode,
+                                                                      width);
                     if(!drained)
                     {
                         ok = false;
