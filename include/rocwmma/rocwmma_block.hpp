@@ -397,6 +397,20 @@ namespace rocwmma
             asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         }
+        // Programmatic dependent launch.  A kernel launched with the stream-serialization
+        // attribute may start while the previous kernel of its stream still runs;
+        // grid_dependency_wait() returns once that kernel has completed and its writes are
+        // visible (at once if there is no such kernel or the attribute was not given).
+        // grid_launch_dependents() lets the next kernel of the stream be scheduled when every
+        // block of this grid has called it or exited.
+        ROCWMMA_DEVICE inline void grid_dependency_wait()
+        {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+        }
+        ROCWMMA_DEVICE inline void grid_launch_dependents()
+        {
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        }
         // Arrive on an mbarrier that may live in the other block of the pair
         // (`clusterAddr` from map_to_cta).
         ROCWMMA_DEVICE inline void mbar_arrive_cluster(uint32_t clusterAddr)

@@ -1034,6 +1034,13 @@ namespace
         cluster_sync(); // both blocks' barriers exist before anything signals them remotely
         tc_fence_after_sync();
         const uint32_t tmemBase = ctl->tmemBase;
+        // Programmatic dependent launch: everything above (barriers, tensor-memory
+        // allocation, descriptor prefetch) touches no global data and may run while the
+        // previous kernel of the stream drains; from here on its results are needed (A, B or C
+        // may be its output, D its input).  The next kernel of the stream may be scheduled as
+        // soon as every block of this one has got this far: it waits at the same place.
+        grid_dependency_wait();
+        grid_launch_dependents();
 
         if(warp == 0)
         {
@@ -1314,6 +1321,18 @@ namespace
         return on;
     }
 
+    // The pair kernel is launched so that its prologue may overlap the end of the previous
+    // kernel of the stream (programmatic dependent launch); B200WMMA_GEMM_OVERLAP=0 launches
+    // it fully serialised (for comparison).
+    bool overlapPrologue()
+    {
+        static const bool on = [] {
+            const char* e = getenv("B200WMMA_GEMM_OVERLAP");
+            return !(e && e[0] == '0');
+        }();
+        return on;
+    }
+
     template <typename KernelT>
     int optInSharedMemory(KernelT kernel, uint32_t bytes, bool (&done)[64])
     {
@@ -1534,8 +1553,18 @@ namespace
                 return rc;
             const uint32_t tiles = tilesM * (wideCols + tailCols);
             const uint32_t pairs = tiles < pairsMax ? tiles : pairsMax;
-            kernel<<<2 * pairs, NUM_THREADS, P_SMEM_BYTES, stream>>>(mapA, mapB, mapBTail, mapD, p);
-            return b200wmma::cudaToStatus(cudaGetLastError());
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim            = dim3(2 * pairs);
+            cfg.blockDim           = dim3(NUM_THREADS);
+            cfg.dynamicSmemBytes   = P_SMEM_BYTES;
+            cfg.stream             = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs    = attr;
+            cfg.numAttrs = overlapPrologue() ? 1 : 0;
+            return b200wmma::cudaToStatus(
+                cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, mapBTail, mapD, p));
         }
 
         int rc = aMN ? makeOperandMapMN(&mapA, dt, sizeof(InT), a, m, k, lda)
