@@ -4,6 +4,7 @@
 
 #include "rocwmma_b200.h"
 #include <cstdint>
+#include <cstdlib>
 #include <cuda_runtime.h>
 
 namespace b200wmma
@@ -43,6 +44,36 @@ namespace b200wmma
             return 8;
         }
         return 0;
+    }
+
+    // Kernels of this library whose prologue touches no global data are launched with
+    // programmatic stream serialization: they may be scheduled while the previous kernel of
+    // the stream drains, set up shared memory, and block in griddepcontrol.wait until that
+    // kernel has completed.  B200WMMA_LAUNCH_OVERLAP=0 launches them fully serialised.
+    inline bool launchOverlapEnabled()
+    {
+        static const bool on = [] {
+            const char* e = getenv("B200WMMA_LAUNCH_OVERLAP");
+            return !(e && e[0] == '0');
+        }();
+        return on;
+    }
+
+    template <typename... Params, typename... Args>
+    inline cudaError_t launchOverlapped(void (*kernel)(Params...), dim3 grid, dim3 block,
+                                        size_t smemBytes, cudaStream_t stream, Args&&... args)
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim            = grid;
+        cfg.blockDim           = block;
+        cfg.dynamicSmemBytes   = smemBytes;
+        cfg.stream             = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs    = attr;
+        cfg.numAttrs = launchOverlapEnabled() ? 1 : 0;
+        return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
     }
 
     // Device-side error word shared by all kernels that contain bounded waits.

@@ -137,6 +137,14 @@ namespace
         uint32_t numGroups; // ceil(batch / 8)
     };
 
+    // Programmatic dependent launch: block until the previous kernel of the stream has
+    // completed, then let the next one be scheduled (it waits at the same place).
+    __device__ inline void gridDependencyWait()
+    {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
+
     // Work distribution: groups of 8 samples are handed out through one global counter, so
     // a warp that finishes early simply takes the next group (a fixed round-robin deal left
     // the slowest warp one group -- up to 8 % of the run -- behind the rest).  A warp walks
@@ -146,21 +154,31 @@ namespace
     {
         unsigned int* counter;
         uint32_t      numGroups;
+        uint32_t      lastTicket;
         uint32_t      g0, g1; // groups of q in [base, base + 8) and [base + 8, base + 16)
         uint32_t      base;
 
+        // Every warp of the grid draws tickets until its first one past the end and then
+        // stops, so exactly numGroups + (warps of the grid) tickets are drawn per launch.
+        // Whoever draws the last one puts the counter back to zero for the launch that
+        // uses it next: no memset sits between two kernels of a stream.
         __device__ inline uint32_t fetch(uint32_t lane)
         {
             uint32_t v = 0;
             if(lane == 0)
+            {
                 v = atomicAdd(counter, 1u);
+                if(v == lastTicket)
+                    atomicExch(counter, 0u);
+            }
             return __shfl_sync(0xffffffffu, v, 0);
         }
         __device__ inline void init(unsigned int* c, uint32_t groups, uint32_t lane)
         {
-            counter   = c;
-            numGroups = groups;
-            base      = 0;
+            counter    = c;
+            numGroups  = groups;
+            lastTicket = groups + gridDim.x * (blockDim.x / 32u) - 1u;
+            base       = 0;
             g0        = fetch(lane);
             g1        = g0 < numGroups ? fetch(lane) : numGroups;
         }
@@ -268,6 +286,10 @@ namespace
         Ring<NSTAGES> ring;
         ring.init(smemAddr(mine), sh);
         __syncthreads();
+
+        // Nothing above touches global memory: it may run while the previous kernel of the
+        // stream drains.  From here on that kernel's results (and the work counter) are read.
+        gridDependencyWait();
 
         const bool twoM = sh.m > 16;
         GroupFeed  feed;
@@ -429,6 +451,10 @@ namespace
         Ring<NSTAGES> ring;
         ring.init(smemAddr(mine), sh);
         __syncthreads();
+
+        // Nothing above touches global memory: it may run while the previous kernel of the
+        // stream drains.  From here on that kernel's results (and the work counter) are read.
+        gridDependencyWait();
 
         const bool twoM = sh.m > 16;
         GroupFeed  feed;
@@ -718,20 +744,22 @@ extern "C" int b200wmma_dlrm_fwd(int dtype, const void* input, void* output, uin
     unsigned int*  ctr    = b200wmma::launchCounter();
     if(!ctr)
         return B200WMMA_ERR_CUDA;
-    B200WMMA_CUDA_TRY(cudaMemsetAsync(ctr, 0, sizeof(unsigned int), s));
+    cudaError_t launchErr = cudaSuccess;
     if(plan.stages == 3)
     {
         if((rc = prepare(dlrmFwdKernel<3>)) != B200WMMA_OK)
             return rc;
-        dlrmFwdKernel<3><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, out, sh, ctr);
+        launchErr = b200wmma::launchOverlapped(dlrmFwdKernel<3>, dim3(grid), dim3(plan.warps * 32),
+                                               plan.smemBytes, s, in, out, sh, ctr);
     }
     else
     {
         if((rc = prepare(dlrmFwdKernel<2>)) != B200WMMA_OK)
             return rc;
-        dlrmFwdKernel<2><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, out, sh, ctr);
+        launchErr = b200wmma::launchOverlapped(dlrmFwdKernel<2>, dim3(grid), dim3(plan.warps * 32),
+                                               plan.smemBytes, s, in, out, sh, ctr);
     }
-    return b200wmma::cudaToStatus(cudaGetLastError());
+    return b200wmma::cudaToStatus(launchErr);
 }
 
 extern "C" int b200wmma_dlrm_bwd(int dtype, const void* input, const void* upstream, void* grad,
@@ -763,18 +791,20 @@ extern "C" int b200wmma_dlrm_bwd(int dtype, const void* input, const void* upstr
     unsigned int*  ctr    = b200wmma::launchCounter();
     if(!ctr)
         return B200WMMA_ERR_CUDA;
-    B200WMMA_CUDA_TRY(cudaMemsetAsync(ctr, 0, sizeof(unsigned int), s));
+    cudaError_t launchErr = cudaSuccess;
     if(plan.stages == 3)
     {
         if((rc = prepare(dlrmBwdKernel<3>)) != B200WMMA_OK)
             return rc;
-        dlrmBwdKernel<3><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, up, g, mg, sh, ctr);
+        launchErr = b200wmma::launchOverlapped(dlrmBwdKernel<3>, dim3(grid), dim3(plan.warps * 32),
+                                               plan.smemBytes, s, in, up, g, mg, sh, ctr);
     }
     else
     {
         if((rc = prepare(dlrmBwdKernel<2>)) != B200WMMA_OK)
             return rc;
-        dlrmBwdKernel<2><<<grid, plan.warps * 32, plan.smemBytes, s>>>(in, up, g, mg, sh, ctr);
+        launchErr = b200wmma::launchOverlapped(dlrmBwdKernel<2>, dim3(grid), dim3(plan.warps * 32),
+                                               plan.smemBytes, s, in, up, g, mg, sh, ctr);
     }
-    return b200wmma::cudaToStatus(cudaGetLastError());
+    return b200wmma::cudaToStatus(launchErr);
 }

@@ -1321,18 +1321,6 @@ namespace
         return on;
     }
 
-    // The pair kernel is launched so that its prologue may overlap the end of the previous
-    // kernel of the stream (programmatic dependent launch); B200WMMA_GEMM_OVERLAP=0 launches
-    // it fully serialised (for comparison).
-    bool overlapPrologue()
-    {
-        static const bool on = [] {
-            const char* e = getenv("B200WMMA_GEMM_OVERLAP");
-            return !(e && e[0] == '0');
-        }();
-        return on;
-    }
-
     template <typename KernelT>
     int optInSharedMemory(KernelT kernel, uint32_t bytes, bool (&done)[64])
     {
@@ -1553,18 +1541,9 @@ namespace
                 return rc;
             const uint32_t tiles = tilesM * (wideCols + tailCols);
             const uint32_t pairs = tiles < pairsMax ? tiles : pairsMax;
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim            = dim3(2 * pairs);
-            cfg.blockDim           = dim3(NUM_THREADS);
-            cfg.dynamicSmemBytes   = P_SMEM_BYTES;
-            cfg.stream             = stream;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs    = attr;
-            cfg.numAttrs = overlapPrologue() ? 1 : 0;
-            return b200wmma::cudaToStatus(
-                cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, mapBTail, mapD, p));
+            return b200wmma::cudaToStatus(b200wmma::launchOverlapped(
+                kernel, dim3(2 * pairs), dim3(NUM_THREADS), P_SMEM_BYTES, stream, mapA, mapB,
+                mapBTail, mapD, p));
         }
 
         int rc = aMN ? makeOperandMapMN(&mapA, dt, sizeof(InT), a, m, k, lda)

@@ -107,6 +107,10 @@ namespace
             mbar_init_fence();
         }
         __syncthreads();
+        // the barriers are set up while the previous kernel of the stream drains; A, x and y
+        // may be its output
+        grid_dependency_wait();
+        grid_launch_dependents();
 
         if(threadIdx.x >= ROWS)
         {
@@ -278,9 +282,9 @@ namespace
             if(dev >= 0 && dev < 64)
                 attrDone[dev] = true;
         }
-        gemvStreamKernel<T><<<(m + ROWS - 1) / ROWS, THREADS, SMEM_BYTES, stream>>>(
-            m, k, a, x, yIn, yOut, alpha, beta, lda, b200wmma::deviceStatusWord());
-        return b200wmma::cudaToStatus(cudaGetLastError());
+        return b200wmma::cudaToStatus(b200wmma::launchOverlapped(
+            gemvStreamKernel<T>, dim3((m + ROWS - 1) / ROWS), dim3(THREADS), SMEM_BYTES, stream, m,
+            k, a, x, yIn, yOut, alpha, beta, lda, b200wmma::deviceStatusWord()));
     }
 } // namespace
 

@@ -127,9 +127,15 @@ namespace b200wmma
             return nullptr;
         if(!st->counters)
         {
-            if(cudaMalloc(&st->counters, 64 * 32) != cudaSuccess)
+            // zeroed once, before any launch can use them: the kernels put their counter back
+            // to zero themselves
+            if(cudaMalloc(&st->counters, 64 * 32) != cudaSuccess
+               || cudaMemset(st->counters, 0, 64 * 32) != cudaSuccess
+               || cudaDeviceSynchronize() != cudaSuccess)
             {
                 (void)cudaGetLastError();
+                if(st->counters)
+                    (void)cudaFree(st->counters);
                 st->counters = nullptr;
                 return nullptr;
             }

@@ -13,8 +13,10 @@ namespace b200wmma
     void* stagingBuffer(int slot, size_t bytes);
 
     // A 4-byte device counter for one kernel launch (work distribution).  Counters come from
-    // a per-device ring of 64, so up to 64 launches may be in flight; the caller zeroes the
-    // counter on its stream before the launch.  nullptr on failure.
+    // a per-device ring of 64, so up to 64 launches may be in flight.  A counter is zero when
+    // it is handed out and the kernel that uses it must leave it at zero (the ring is zeroed
+    // once, synchronously, when it is allocated: the first call on a device must not be made
+    // while a stream is being captured).  nullptr on failure.
     unsigned int* launchCounter();
 
     // Copy streams and events for the host-buffer GEMM entry point (created on first use,
