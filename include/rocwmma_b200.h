@@ -197,7 +197,9 @@ B200WMMA_API int b200wmma_gemv(int dtype, uint32_t m, uint32_t k, const void* a,
  * output [batch][k + m(m-1)/2]: the first k values are row 0 of the sample, then
  * the strict lower triangle of X X^T in row-major (i, j<i) order.  dtype F16
  * (fp32 accumulation).  m <= 32, k a multiple of 16 and <= 256.  Unlike the
- * reference no m*m*batch scratch buffer is needed.
+ * reference no m*m*batch scratch buffer is needed.  The first DLRM call on a
+ * device allocates and zeroes a 2 KB ring of work counters (a synchronising
+ * step: make that call outside stream capture); later calls only launch.
  */
 B200WMMA_API int b200wmma_dlrm_fwd(int dtype, const void* input, void* output, uint32_t m, uint32_t k,
                       uint32_t batch, void* stream);
