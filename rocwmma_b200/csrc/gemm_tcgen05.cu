@@ -772,6 +772,10 @@ namespace
         __syncthreads();
         tc_fence_after_sync();
         const uint32_t tmemBase = ctl->tmemBase;
+        // programmatic dependent launch, as in the pair kernel below: the set-up above may
+        // overlap the previous kernel of the stream, global memory is touched only from here
+        grid_dependency_wait();
+        grid_launch_dependents();
 
         if(warp == 0)
         {
@@ -1561,8 +1565,8 @@ namespace
             return rc;
         const uint32_t tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
         const uint32_t grid  = tiles < uint32_t(sms) ? tiles : uint32_t(sms);
-        kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(mapA, mapB, mapD, p);
-        return b200wmma::cudaToStatus(cudaGetLastError());
+        return b200wmma::cudaToStatus(b200wmma::launchOverlapped(
+            kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, mapA, mapB, mapD, p));
     }
 
     template <typename InT, typename OutT, typename CompT>
