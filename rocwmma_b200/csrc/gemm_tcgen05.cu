@@ -1424,7 +1424,18 @@ namespace
                 return rcD;
         }
 
-        if(pairEnabled() && m > BM && sms >= 2)
+        // One tile row of at most 128 rows (a skinny product) is bound by how fast one SM can
+        // pull its operands, not by the tensor cores: 128 x 8192 x 8192 as 32 single-block
+        // tiles of 128 x 256 keeps 32 SMs busy for 57 us.  The pair kernel with 128-wide tiles
+        // spreads the same columns of B over 128 SMs (the second block of each pair gets rows
+        // past m, which the TMA fills with zeros without reading memory).
+        // B200WMMA_GEMM_SKINNY=0 keeps such products on the single-block kernel (comparison).
+        static const bool skinnyEnv = [] {
+            const char* e = getenv("B200WMMA_GEMM_SKINNY");
+            return !(e && e[0] == '0');
+        }();
+        const bool skinny = skinnyEnv && m <= BM && n >= 4u * 128u;
+        if(pairEnabled() && (m > BM || skinny) && sms >= 2)
         {
             // Tile widths.  A tile costs its width plus a fixed part (A is loaded per tile
             // whatever its width, so narrow tiles pay more L2 traffic per flop; measured:
@@ -1463,7 +1474,11 @@ namespace
                 p.sumInTmem = 1u;
                 p.tmaStore  = 0u;
             }
-            const uint32_t widest = tmemSum ? 160u : 256u, narrowest = tmemSum ? 128u : 192u;
+            // Less than one wave of the widest tiles: narrower ones down to 128 columns put
+            // more SMs to work.
+            const uint32_t widest   = tmemSum ? 160u : 256u;
+            const bool     subWave  = tilesM * ((n + widest - 1) / widest) < pairsMax;
+            const uint32_t narrowest = (tmemSum || subWave) ? 128u : 192u;
             auto makespan = [&](uint32_t bnW, uint32_t wideCols, uint32_t tailCols, uint32_t bnT) {
                 const uint32_t total = tilesM * (wideCols + tailCols);
                 const uint32_t pairs = total < pairsMax ? total : pairsMax;
