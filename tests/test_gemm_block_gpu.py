@@ -76,9 +76,12 @@ def test_block_gemm_full_tiles(in_t, out_t):
 
 @pytest.mark.parametrize("in_t,out_t", BLOCK_PAIRS)
 @pytest.mark.parametrize("m,n,k", [(200, 136, 272), (1, 8, 16), (129, 257, 48), (384, 1000, 528),
-                                   (130, 3, 7), (260, 264, 1040)])
+                                   (130, 3, 7), (260, 264, 1040), (128, 1024, 272),
+                                   (65, 777, 1040), (1, 512, 16)])
 def test_block_gemm_ragged_edges(in_t, out_t, m, n, k):
-    """Sizes that are not tile multiples: loads are zero-filled, stores masked."""
+    """Sizes that are not tile multiples: loads are zero-filled, stores masked.  The last three
+    are skinny products (m <= 128, n >= 512), which run on the pair kernel with the second
+    block of every pair entirely past the last row."""
     al, be = _ab(in_t)
     case = dict(in_t=in_t, out_t=out_t, m=m, n=n, k=k, la=ROW, lb=COL, alpha=al, beta=be,
                 seed=50 + in_t)
@@ -90,7 +93,7 @@ def test_block_gemm_ragged_edges(in_t, out_t, m, n, k):
 @pytest.mark.parametrize("in_t,out_t", BLOCK_PAIRS)
 @pytest.mark.parametrize("la,lb", [(COL, ROW), (ROW, ROW), (COL, COL)])
 @pytest.mark.parametrize("m,n,k", [(256, 256, 192), (300, 520, 264), (1024, 2048, 160),
-                                   (100, 72, 40)])
+                                   (100, 72, 40), (100, 520, 264)])
 def test_block_gemm_other_layouts(in_t, out_t, la, lb, m, n, k):
     """Column-major A and row-major B are read in place as MN-major tensor-core operands
     (the layout of the reference's perf samples, samples/perf_hgemm.cpp:268-271)."""
