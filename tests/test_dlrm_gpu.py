@@ -81,3 +81,28 @@ def test_config_batch_65536():
     ggrad = grad.view(b, m * k)[pick].cpu().numpy().reshape(-1)
     assert 0 <= O.max_rel_err(O.F16, ggrad, wgrad) <= TOL
     assert torch.isfinite(out.float()).all() and torch.isfinite(grad.float()).all()
+
+
+def test_many_launches_back_to_back():
+    """The kernels take their work counter from a ring of 64 and leave it at zero themselves
+    (nothing clears it between launches), and consecutive launches overlap their set-up with
+    the previous kernel's tail: 150 forward / backward launches back to back on one stream,
+    alternating two batch sizes (so the number of tickets drawn per launch changes), must all
+    give the oracle's result."""
+    m, k = 27, 128
+    cases = []
+    for b, seed in ((1003, 21), (72, 22)):
+        x, up = dlrm_inputs(m, k, b, seed=seed)
+        cases.append((b, to_device(x, O.F16), to_device(up, O.F16), O.dlrm_fwd(O.F16, x, m, k, b),
+                      O.dlrm_bwd(O.F16, x, up, m, k, b)))
+    results = []
+    for i in range(75):
+        b, dx, dup, _, _ = cases[i % 2]
+        results.append((i % 2, api.dlrm_fwd(dx, m, k, b), api.dlrm_bwd(dx, dup, m, k, b)))
+    api.check_device()
+    for which, out, (mlp, grad) in results:
+        _, _, _, want_fwd, (want_mlp, want_grad) = cases[which]
+        assert O.max_rel_err(O.F16, out.cpu().numpy().reshape(-1), want_fwd) <= 2e-3
+        assert np.array_equal(mlp.cpu().numpy().reshape(-1).view(np.uint16),
+                              np.asarray(want_mlp).reshape(-1).view(np.uint16))
+        assert O.max_rel_err(O.F16, grad.cpu().numpy().reshape(-1), want_grad) <= 2e-3
