@@ -306,3 +306,33 @@ def test_multi_gpu_shard_shapes(m):
                 seed=75)
     got, want = _run(case, with_c=False)
     assert 0 <= O.max_rel_err(O.F16, got, want) <= 2e-3
+
+
+@pytest.mark.parametrize("m", [64, 128, 1024])
+def test_dependent_launches_keep_stream_order(m):
+    """The block kernels are launched so that their set-up overlaps the previous kernel of the
+    stream; everything after it must still see that kernel's results.  A chain X <- X . B of
+    eight launches, each reading the previous launch's output as A (and once as C), issued
+    back to back, must equal the same chain with a device synchronisation after every launch,
+    bit for bit.  m = 64 / 128 take the skinny route, 1024 the ordinary pair kernel."""
+    n = k = 1024
+    a = to_device(synth.rows(91, 1, O.F16, 0, m, k).reshape(-1), O.F16)
+    b = to_device((synth.rows(91, 2, O.F16, 0, n, k) / 16).astype(np.float16).reshape(-1), O.F16)
+
+    def chain(sync):
+        x = a.clone()
+        for i in range(8):
+            y = torch.empty_like(x)
+            api.gemm(O.F16, O.F16, m, n, k, x, b, x if i == 3 else None, 1.0,
+                     0.5 if i == 3 else 0.0, out=y)
+            if sync:
+                torch.cuda.synchronize()
+            x = y
+        torch.cuda.synchronize()
+        return x.cpu().numpy().view(np.uint16)
+
+    want = chain(True)
+    for _ in range(3):
+        assert np.array_equal(chain(False), want)
+    api.check_device()
+    assert np.isfinite(want.view(np.float16).astype(np.float32)).all()
