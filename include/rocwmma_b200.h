@@ -137,6 +137,9 @@ B200WMMA_API int b200wmma_gemm(int in_dtype, int out_dtype, uint32_t m, uint32_t
  * buffers are cached per device and grown on demand; b200wmma_shutdown frees
  * them.  This is the call the reference's host driver makes around its kernel
  * (hipMemcpy in / launch / hipMemcpy out, samples/perf_hgemm.cpp:782-890).
+ * One call per device at a time: the staging buffers, copy streams and events
+ * are per device, and the call holds a per-device lock from start to finish, so
+ * a second host thread calling it for the same device waits for the first.
  */
 B200WMMA_API int b200wmma_gemm_host(int in_dtype, int out_dtype, uint32_t m, uint32_t n, uint32_t k,
                        const void* a, const void* b, const void* c, void* d, uint32_t lda,
@@ -157,8 +160,12 @@ B200WMMA_API int b200wmma_gemm_host(int in_dtype, int out_dtype, uint32_t m, uin
  * column-major A / row-major B into the K-major form with a transposition pass of its
  * own, whose scratch is a fixed array inside the library image.
  *
- * Same arguments, same arithmetic and same results as b200wmma_gemm, for the same type
- * pairs except F64.  Differences:
+ * Same arguments, same checks, same arithmetic and same results as b200wmma_gemm, for
+ * these type pairs: F16->F16, F16->F32, BF16->F32, BF16->BF16, XF32->F32, I8->I32,
+ * E4M3->BF16, E4M3->F32, E5M2->BF16, E5M2->F32.  Not offered (B200WMMA_ERR_UNSUPPORTED):
+ * F32->F32, whose hi / lo split of A and B needs 2 (m + n) k floats of scratch for every
+ * layout, and F64->F64.  Every argument is validated before anything is enqueued.
+ * Differences:
  *   - limit: the transposed copies, m * k' elements of A (if column-major) plus n * k'
  *     of B (if row-major), k' = k rounded up to 16 bytes, must fit in 8 MiB together;
  *     larger problems are refused with B200WMMA_ERR_TOO_LARGE.  Native layouts need no
@@ -200,6 +207,13 @@ B200WMMA_API int b200wmma_gemv(int dtype, uint32_t m, uint32_t k, const void* a,
  * reference no m*m*batch scratch buffer is needed.  The first DLRM call on a
  * device allocates and zeroes a 2 KB ring of work counters (a synchronising
  * step: make that call outside stream capture); later calls only launch.
+ * Each stream of a device owns one of 64 self-resetting counters, shared by
+ * all DLRM launches (forward and backward) of that stream, which run one after
+ * the other; any number of launches may be queued.  A 65th distinct stream on
+ * one device makes the call wait for the device once and start the table over.
+ * A DLRM launch captured into a CUDA graph keeps the counter of the stream it
+ * was captured on: do not replay such a graph concurrently with DLRM work on
+ * that stream.
  */
 B200WMMA_API int b200wmma_dlrm_fwd(int dtype, const void* input, void* output, uint32_t m, uint32_t k,
                       uint32_t batch, void* stream);

@@ -167,7 +167,10 @@ REFK_SIMPLE_GEMM(ref_simple_dgemm, dgemm_rocwmma_d, refk_simple_dgemm, rocwmma::
                  rocwmma::float64_t, rocwmma::float64_t)
 
 // y = alpha * A x + beta * y, A column-major m x k with lda = m (simple_sgemv.cpp:163-167,
-// 207-240: n = 1, ldb = k, ldc = ldd = m).
+// 207-240: n = 1, ldb = k, ldc = ldd = m).  The sample kernel works on whole 16-column tiles
+// (simple_sgemv.cpp:139,145,153), so it reads 16 k elements at x and 16 m elements at yIn
+// and writes 16 m elements at yOut: the caller must pass buffers of that size, with the
+// vectors in their first k resp. m elements.
 #define REFK_SIMPLE_GEMV(NS, KERNEL, FN, T)                                                         \
     extern "C" int FN(uint32_t m, uint32_t k, const void* a, const void* x, const void* yIn,        \
                       void* yOut, double alpha, double beta, void* stream)                          \

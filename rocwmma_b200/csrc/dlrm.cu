@@ -741,7 +741,7 @@ extern "C" int b200wmma_dlrm_fwd(int dtype, const void* input, void* output, uin
     auto           s      = static_cast<cudaStream_t>(stream);
     auto           in     = static_cast<__half const*>(input);
     auto           out    = static_cast<__half*>(output);
-    unsigned int*  ctr    = b200wmma::launchCounter();
+    unsigned int*  ctr    = b200wmma::launchCounter(s);
     if(!ctr)
         return B200WMMA_ERR_CUDA;
     cudaError_t launchErr = cudaSuccess;
@@ -788,7 +788,7 @@ extern "C" int b200wmma_dlrm_bwd(int dtype, const void* input, const void* upstr
     auto           up     = static_cast<__half const*>(upstream);
     auto           g      = static_cast<__half*>(grad);
     auto           mg     = static_cast<__half*>(mlp_grad);
-    unsigned int*  ctr    = b200wmma::launchCounter();
+    unsigned int*  ctr    = b200wmma::launchCounter(s);
     if(!ctr)
         return B200WMMA_ERR_CUDA;
     cudaError_t launchErr = cudaSuccess;

@@ -217,7 +217,16 @@ namespace b200wmma
                 double const* c, double* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                 double alpha, double beta, int layoutA, int layoutB, cudaStream_t stream)
     {
-        if(layoutA == B200WMMA_COL_MAJOR || layoutB == B200WMMA_ROW_MAJOR)
+        // Every argument is checked before anything is enqueued: the transposition pass
+        // below reads a and b with the caller's leading dimensions.
+        const bool aT = layoutA == B200WMMA_COL_MAJOR, bT = layoutB == B200WMMA_ROW_MAJOR;
+        if(lda < (aT ? m : k) || ldb < (bT ? n : k) || ldd < n || (beta != 0.0 && ldc < n))
+            return B200WMMA_ERR_INVALID_ARG;
+        // operands that are transposed are read element by element and need no alignment
+        if((!aT && ((reinterpret_cast<uintptr_t>(a) % 16) || (lda % 2)))
+           || (!bT && ((reinterpret_cast<uintptr_t>(b) % 16) || (ldb % 2))))
+            return B200WMMA_ERR_ALIGNMENT;
+        if(aT || bT)
         {
             const uint32_t kPad   = (k + 1) / 2 * 2;
             const size_t   aElems = layoutA == B200WMMA_COL_MAJOR ? size_t(m) * kPad : 0;
@@ -242,12 +251,6 @@ namespace b200wmma
             }
             B200WMMA_CUDA_TRY(cudaGetLastError());
         }
-        if((reinterpret_cast<uintptr_t>(a) % 16) || (reinterpret_cast<uintptr_t>(b) % 16)
-           || (lda % 2) || (ldb % 2))
-            return B200WMMA_ERR_ALIGNMENT;
-        if(lda < k || ldb < k || ldd < n || (beta != 0.0 && ldc < n))
-            return B200WMMA_ERR_INVALID_ARG;
-
         static bool attrDone[64] = {};
         int         dev          = 0;
         B200WMMA_CUDA_TRY(cudaGetDevice(&dev));

@@ -1877,9 +1877,17 @@ extern "C" int b200wmma_gemm_host(int in_dtype, int out_dtype, uint32_t m, uint3
 {
     if(!a || !b || !d || m == 0 || n == 0 || k == 0 || (beta != 0.0 && !c))
         return B200WMMA_ERR_INVALID_ARG;
+    if((layout_a != B200WMMA_ROW_MAJOR && layout_a != B200WMMA_COL_MAJOR)
+       || (layout_b != B200WMMA_ROW_MAJOR && layout_b != B200WMMA_COL_MAJOR))
+        return B200WMMA_ERR_INVALID_ARG; // the copy sizes below depend on the layouts
     const size_t inB = b200wmma::dtypeSize(in_dtype), outB = b200wmma::dtypeSize(out_dtype);
     if(inB == 0 || outB == 0)
         return B200WMMA_ERR_UNSUPPORTED;
+    // staging buffers, copy streams and events exist once per device: one call at a time
+    std::mutex* hostCall = b200wmma::hostCallMutex();
+    if(!hostCall)
+        return B200WMMA_ERR_CUDA;
+    std::lock_guard<std::mutex> hostLock(*hostCall);
     auto         s      = static_cast<cudaStream_t>(stream);
     const size_t aBytes = size_t(layout_a == B200WMMA_ROW_MAJOR ? m : k) * lda * inB;
     const size_t bBytes = size_t(layout_b == B200WMMA_ROW_MAJOR ? k : n) * ldb * inB;
@@ -1998,7 +2006,19 @@ namespace
                    cudaStream_t stream)
     {
         constexpr uint32_t E16 = 16 / sizeof(InT);
-        if(layoutA == B200WMMA_COL_MAJOR || layoutB == B200WMMA_ROW_MAJOR)
+        // Every argument is checked before anything is enqueued: the transposition pass
+        // below reads a and b with the caller's leading dimensions.
+        auto misaligned = [](void const* ptr, uint32_t ld, size_t elem) {
+            return (reinterpret_cast<uintptr_t>(ptr) % 16) != 0 || (size_t(ld) * elem) % 16 != 0;
+        };
+        const bool aT = layoutA == B200WMMA_COL_MAJOR, bT = layoutB == B200WMMA_ROW_MAJOR;
+        if(lda < (aT ? m : k) || ldb < (bT ? n : k) || ldd < n || (beta != 0.0 && ldc < n))
+            return B200WMMA_ERR_INVALID_ARG;
+        // operands that are transposed are read with ordinary loads and need no alignment
+        if((!aT && misaligned(a, lda, sizeof(InT))) || (!bT && misaligned(b, ldb, sizeof(InT)))
+           || misaligned(d, ldd, sizeof(OutT)) || (beta != 0.0 && misaligned(c, ldc, sizeof(OutT))))
+            return B200WMMA_ERR_ALIGNMENT;
+        if(aT || bT)
         {
             const uint32_t kPad   = roundUp(k, E16);
             const size_t   aBytes = layoutA == B200WMMA_COL_MAJOR ? size_t(m) * kPad * sizeof(InT) : 0;
@@ -2032,14 +2052,6 @@ namespace
                 ldb = kPad;
             }
         }
-        auto misaligned = [](void const* ptr, uint32_t ld, size_t elem) {
-            return (reinterpret_cast<uintptr_t>(ptr) % 16) != 0 || (size_t(ld) * elem) % 16 != 0;
-        };
-        if(misaligned(a, lda, sizeof(InT)) || misaligned(b, ldb, sizeof(InT))
-           || misaligned(d, ldd, sizeof(OutT)) || (beta != 0.0 && misaligned(c, ldc, sizeof(OutT))))
-            return B200WMMA_ERR_ALIGNMENT;
-        if(lda < k || ldb < k || ldd < n || (beta != 0.0 && ldc < n))
-            return B200WMMA_ERR_INVALID_ARG;
         // No status word: the library's one comes from cudaMalloc.
         return launchWithStatus<InT, OutT, CompT>(dt, m, n, k, a, b, c, d, lda, ldb, ldc, ldd,
                                                   alpha, beta, stream, nullptr);
@@ -2079,6 +2091,10 @@ extern "C" int b200wmma_gemm_noalloc(int in_dtype, int out_dtype, uint32_t m, ui
     B200WMMA_NOALLOC_CASE(B200WMMA_E4M3, B200WMMA_BF16, __nv_fp8_e4m3, __nv_bfloat16, float,
                           CU_TENSOR_MAP_DATA_TYPE_UINT8)
     B200WMMA_NOALLOC_CASE(B200WMMA_E4M3, B200WMMA_F32, __nv_fp8_e4m3, float, float,
+                          CU_TENSOR_MAP_DATA_TYPE_UINT8)
+    B200WMMA_NOALLOC_CASE(B200WMMA_E5M2, B200WMMA_BF16, __nv_fp8_e5m2, __nv_bfloat16, float,
+                          CU_TENSOR_MAP_DATA_TYPE_UINT8)
+    B200WMMA_NOALLOC_CASE(B200WMMA_E5M2, B200WMMA_F32, __nv_fp8_e5m2, float, float,
                           CU_TENSOR_MAP_DATA_TYPE_UINT8)
 #undef B200WMMA_NOALLOC_CASE
     return B200WMMA_ERR_UNSUPPORTED;

@@ -20,8 +20,10 @@ namespace b200wmma
             void*     stage[4]      = {nullptr, nullptr, nullptr, nullptr}; // A, B, C, D staging
             size_t    stageBytes[4] = {0, 0, 0, 0};
             HostPipe  pipe;
-            unsigned int* counters    = nullptr; // ring of 64 launch counters, 32 bytes apart
-            unsigned int  nextCounter = 0;
+            unsigned int* counters = nullptr; // 64 launch counters, 32 bytes apart
+            cudaStream_t  counterStream[64] = {}; // stream that owns counter i
+            unsigned int  counterStreams    = 0;
+            std::mutex    hostCall; // serialises the host-buffer entry point per device
         };
 
         std::mutex  g_mutex;
@@ -119,7 +121,7 @@ namespace b200wmma
         return st->stage[slot];
     }
 
-    unsigned int* launchCounter()
+    unsigned int* launchCounter(cudaStream_t stream)
     {
         std::lock_guard<std::mutex> lock(g_mutex);
         DeviceState*                st = current();
@@ -140,9 +142,42 @@ namespace b200wmma
                 return nullptr;
             }
         }
-        unsigned int* c = st->counters + (st->nextCounter % 64u) * 8u;
-        st->nextCounter++;
-        return c;
+        // One counter per stream.  Launches of one stream run one after the other (a kernel
+        // launched with programmatic stream serialization reads its counter only after
+        // griddepcontrol.wait, i.e. after its predecessor has put the counter back to zero
+        // and completed), so they can share a counter however many are queued; launches of
+        // different streams may overlap and never share one.
+        for(unsigned int i = 0; i < st->counterStreams; ++i)
+            if(st->counterStream[i] == stream)
+                return st->counters + i * 8u;
+        if(st->counterStreams == 64u)
+        {
+            // A 65th stream: wait until every launch has finished (all counters are zero
+            // again then) and start the table afresh.
+            if(cudaDeviceSynchronize() != cudaSuccess)
+            {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+            st->counterStreams = 0;
+        }
+        st->counterStream[st->counterStreams] = stream;
+        return st->counters + (st->counterStreams++) * 8u;
+    }
+
+    void resetLaunchCounters()
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceState*                st = current();
+        if(st && st->counters && cudaMemset(st->counters, 0, 64 * 32) != cudaSuccess)
+            (void)cudaGetLastError();
+    }
+
+    std::mutex* hostCallMutex()
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceState*                st = current();
+        return st ? &st->hostCall : nullptr;
     }
 
     HostPipe* hostPipe()
@@ -218,6 +253,10 @@ int b200wmma_check_device(void* stream, uint32_t* detail)
     if(host[0] != 0)
     {
         B200WMMA_CUDA_TRY(cudaMemset(word, 0, sizeof(host)));
+        // a kernel that gave up may have left its work counter in mid-count; the stream is
+        // idle here, so put all of them back to zero
+        B200WMMA_CUDA_TRY(cudaDeviceSynchronize());
+        resetLaunchCounters();
         return B200WMMA_ERR_DEVICE_WAIT;
     }
     return B200WMMA_OK;
@@ -261,7 +300,18 @@ int b200wmma_shutdown(void)
                 (void)cudaEventDestroy(st.pipe.out[i]);
             }
         }
-        st = DeviceState{};
+        st.status = nullptr;
+        st.smCount = 0;
+        st.scratch = nullptr;
+        st.scratchBytes = 0;
+        for(int i = 0; i < 4; ++i)
+        {
+            st.stage[i]      = nullptr;
+            st.stageBytes[i] = 0;
+        }
+        st.pipe           = HostPipe{};
+        st.counters       = nullptr;
+        st.counterStreams = 0;
     }
     if(prev >= 0)
         (void)cudaSetDevice(prev);

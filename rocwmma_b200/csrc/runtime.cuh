@@ -3,6 +3,7 @@
 #define ROCWMMA_B200_CSRC_RUNTIME_CUH
 #include <cstddef>
 #include <cuda_runtime.h>
+#include <mutex>
 
 namespace b200wmma
 {
@@ -12,12 +13,20 @@ namespace b200wmma
     // Staging buffers for the host-buffer GEMM entry point; slot 0..3 = A, B, C, D.
     void* stagingBuffer(int slot, size_t bytes);
 
-    // A 4-byte device counter for one kernel launch (work distribution).  Counters come from
-    // a per-device ring of 64, so up to 64 launches may be in flight.  A counter is zero when
-    // it is handed out and the kernel that uses it must leave it at zero (the ring is zeroed
-    // once, synchronously, when it is allocated: the first call on a device must not be made
-    // while a stream is being captured).  nullptr on failure.
-    unsigned int* launchCounter();
+    // A 4-byte device counter for one kernel launch on `stream` (work distribution).  Every
+    // stream of a device owns one counter (up to 64 streams; a 65th makes the call wait for
+    // the device and start over), which the launches of that stream share: they run one
+    // after the other.  A counter is zero when it is handed out and the kernel that uses it
+    // must leave it at zero (the counters are zeroed once, synchronously, when they are
+    // allocated: the first call on a device must not be made while a stream is being
+    // captured).  nullptr on failure.
+    unsigned int* launchCounter(cudaStream_t stream);
+    // Puts every counter of the current device back to zero (after a kernel gave up).
+    void resetLaunchCounters();
+
+    // Lock held by the host-buffer GEMM entry point for the whole call: its staging buffers,
+    // copy streams and events exist once per device.  nullptr without a device.
+    std::mutex* hostCallMutex();
 
     // Copy streams and events for the host-buffer GEMM entry point (created on first use,
     // one set per device, destroyed by b200wmma_shutdown).

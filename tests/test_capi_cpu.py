@@ -44,6 +44,12 @@ def test_argument_validation_needs_no_device():
                              1.0, 0.5, 0, 1, None) == L.ERR_INVALID_ARG
     assert lib.b200wmma_gemm(L.F16, L.F16, 128, 128, 128, one, one, null, one, 128, 128, 128, 128,
                              1.0, 0.0, 7, 1, None) == L.ERR_INVALID_ARG
+    # fp64 with transposed layouts: an undersized leading dimension is refused before the
+    # transposition pass is enqueued (column-major A needs lda >= m, row-major B ldb >= n)
+    assert lib.b200wmma_gemm(L.F64, L.F64, 64, 64, 64, one, one, null, one, 56, 64, 64, 64,
+                             1.0, 0.0, 1, 1, None) == L.ERR_INVALID_ARG
+    assert lib.b200wmma_gemm(L.F64, L.F64, 64, 64, 64, one, one, null, one, 64, 56, 64, 64,
+                             1.0, 0.0, 0, 0, None) == L.ERR_INVALID_ARG
     assert lib.b200wmma_gemm_simple(L.F16, L.F32, 16, 16, 16, null, one, one, one, 16, 16, 16, 16,
                                     1.0, 0.0, 0, 1, 0, 16, None) == L.ERR_INVALID_ARG
     assert lib.b200wmma_gemv(L.F32, 16, 16, one, null, one, one, 1.0, 0.0, 16, None) \

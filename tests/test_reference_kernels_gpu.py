@@ -77,21 +77,36 @@ def test_reference_simple_kernels(K, fn, dt):
 
 @pytest.mark.parametrize("fn,dt", [("refk_simple_sgemv", O.F32), ("refk_simple_dgemv", O.F64)])
 def test_reference_gemv_kernels(K, fn, dt):
+    """simple_sgemv / simple_dgemv.  The sample kernel multiplies a 16-column B tile and loads /
+    stores 16-column C / D tiles although only column 0 carries the vector
+    (samples/simple_sgemv.cpp:139,145,153: ldb = k, ldc = ldd = m), so it touches 16 k elements
+    from x and 16 m elements from y_in and y_out.  The buffers handed to it here are that
+    large -- column 0 holds the vector, columns 1..15 are padding -- so that no access leaves
+    an allocation; only column 0 of the result is compared."""
     m, k = 256, 192
+    cols = 16
     a, x, y = gemv_inputs(m, k, seed=11)
     if dt == O.F64:
         a, x, y = a.astype(np.float64), x.astype(np.float64), y.astype(np.float64)
     want = O.gemv(dt, m, k, a, x, y, 2.1, 2.1)
-    da, dx, dy = to_device(a, dt), to_device(x, dt), to_device(y, dt)
+    x_pad = np.zeros(cols * k, dtype=x.dtype)
+    x_pad[:k] = x
+    y_pad = np.zeros(cols * m, dtype=y.dtype)
+    y_pad[:m] = y
+    da, dx, dy = to_device(a, dt), to_device(x_pad, dt), to_device(y_pad, dt)
     out = torch.full_like(dy, float("nan"))
+    assert dx.numel() == cols * k and dy.numel() == cols * m and out.numel() == cols * m
     rc = getattr(K, fn)(m, k, da.data_ptr(), dx.data_ptr(), dy.data_ptr(), out.data_ptr(), 2.1,
                         2.1, _stream())
     assert rc == 0
     torch.cuda.synchronize()
+    got = to_host(out, dt)
     # the tensor-core tile sums a column block at a time, the host routine one product at a
     # time: same values, other rounding order
-    err = O.max_rel_err(dt, to_host(out, dt), want)
+    err = O.max_rel_err(dt, np.ascontiguousarray(got[:m]), want)
     assert 0 <= err <= (1e-4 if dt == O.F32 else 1e-12), err
+    # the padding columns were written by the kernel (beta * 0 + alpha * A * 0 = 0), nothing else
+    assert np.all(got[m:] == 0)
 
 
 def test_reference_dlrm_kernels(K):

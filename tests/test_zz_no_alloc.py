@@ -49,6 +49,8 @@ def test_noalloc_matches_regular_entry_point_on_consecutive_calls():
              seed=92),
         dict(in_t=O.I8, out_t=O.I32, m=256, n=256, k=160, la=ROW, lb=ROW, alpha=1, beta=1,
              seed=93),
+        dict(in_t=O.E5M2, out_t=O.BF16, m=160, n=192, k=96, la=COL, lb=COL, alpha=1.0, beta=0.0,
+             seed=94),
     ]
     for case in cases:
         a, b, c = gemm_inputs(case)
@@ -85,3 +87,16 @@ def test_noalloc_rejects_sizes_beyond_its_scratch():
                                          64, 1.0, 0.0, ROW, COL, None) == L.ERR_UNSUPPORTED
     assert L.lib().b200wmma_gemm_noalloc(L.F16, L.F16, 64, 64, 64, None, one, None, one, 64, 64, 64,
                                          64, 1.0, 0.0, ROW, COL, None) == L.ERR_INVALID_ARG
+    # a leading dimension smaller than the extent it strides over is refused before the
+    # transposition pass could read past the operand: column-major A needs lda >= m,
+    # row-major B needs ldb >= n (the pointers are dummies; nothing is launched)
+    assert L.lib().b200wmma_gemm_noalloc(L.F16, L.F16, 64, 64, 64, one, one, None, one, 56, 64, 64,
+                                         64, 1.0, 0.0, COL, COL, None) == L.ERR_INVALID_ARG
+    assert L.lib().b200wmma_gemm_noalloc(L.F16, L.F16, 64, 64, 64, one, one, None, one, 64, 56, 64,
+                                         64, 1.0, 0.0, ROW, ROW, None) == L.ERR_INVALID_ARG
+    assert L.lib().b200wmma_gemm_noalloc(L.F16, L.F16, 64, 64, 64, one, one, None, one, 64, 64, 64,
+                                         56, 1.0, 0.0, COL, ROW, None) == L.ERR_INVALID_ARG
+    # a misaligned output is refused before anything is launched as well
+    assert L.lib().b200wmma_gemm_noalloc(L.F16, L.F16, 64, 64, 64, one, one, None,
+                                         C.c_void_p(258), 64, 64, 64, 64, 1.0, 0.0, COL, ROW,
+                                         None) == L.ERR_ALIGNMENT
