@@ -31,16 +31,29 @@ def np_dtype(code: int):
     return _NP[code]
 
 
+def reference_dir() -> str:
+    """Where the rocWMMA source tree is mounted (it need not exist).  The environment
+    variable ROCWMMA_REFERENCE_DIR overrides the default location; the Makefile beside this
+    file receives it as REF."""
+    return os.environ.get("ROCWMMA_REFERENCE_DIR", "/root/reference")
+
+
+def _have_reference() -> bool:
+    return os.path.isdir(reference_dir())
+
+
 def build(force: bool = False) -> None:
     """Compile liboracle.so (and _ref/libref.so where the reference tree is mounted)."""
     if force or not os.path.exists(os.path.join(_HERE, "liboracle.so")):
         subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True,
                        stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference") and (
+    if _have_reference() and (
             force or not os.path.exists(os.path.join(_HERE, "_ref", "libref.so"))):
-        subprocess.run(["make", "-C", _HERE, "ref"], check=True, stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference") and (force or _ref_kernels_stale()):
-        subprocess.run(["make", "-C", _HERE, "refkernels"], check=True, stdout=subprocess.DEVNULL)
+        subprocess.run(["make", "-C", _HERE, "ref", "REF=" + reference_dir()], check=True,
+                       stdout=subprocess.DEVNULL)
+    if _have_reference() and (force or _ref_kernels_stale()):
+        subprocess.run(["make", "-C", _HERE, "refkernels", "REF=" + reference_dir()],
+                       check=True, stdout=subprocess.DEVNULL)
 
 
 def _ref_kernels_stale() -> bool:
@@ -105,7 +118,7 @@ def ref():
     if _ref is None:
         path = os.path.join(_HERE, "_ref", "libref.so")
         if not os.path.exists(path):
-            if os.path.isdir("/root/reference"):
+            if _have_reference():
                 build()
             if not os.path.exists(path):
                 return None
@@ -133,7 +146,7 @@ def ref_kernels():
     global _ref_kernels
     if _ref_kernels is None:
         path = os.path.join(_HERE, "_ref", "libref_kernels.so")
-        if os.path.isdir("/root/reference"):
+        if _have_reference():
             build()
         if not os.path.exists(path):
             return None

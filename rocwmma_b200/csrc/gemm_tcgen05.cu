@@ -14,10 +14,10 @@
 //               row per thread), alpha/beta in the compute type, conversion, and
 //               128-bit stores along the row.
 //
-// A must be row-major and B column-major (both "K-major", what BASELINE's perf
-// configuration uses); other layouts are transposed into scratch first by
-// transposeInto().  Tiles at the M/N/K edges rely on TMA zero fill for loads and
-// on masks for stores.
+// Row-major A / column-major B are "K-major" tensor-core operands (the layout of the
+// 8192^3 benchmark configuration); column-major A / row-major B are read in place as
+// MN-major operands for 8- and 16-bit types and transposed into scratch first for 32-bit
+// ones.  Tiles at the M/N/K edges rely on TMA zero fill for loads and on masks for stores.
 //
 // Every mbarrier wait is bounded; when one runs out the block raises an abort
 // flag, all roles leave their loops, tensor memory is released, and the kernel

@@ -16,70 +16,6 @@ import os
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CUDA_INCLUDE = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
 
-# The kernel of the reference's run-time compilation sample, unchanged in its body
-# (samples/hipRTC_gemm.cpp:106-165): bf16 inputs, fp32 accumulate and C/D, one 16x16x16
-# tile per warp.
-BF16_SIMPLE_GEMM_SOURCE = r"""
-#include <rocwmma/rocwmma.hpp>
-
-using rocwmma::accumulator;
-using rocwmma::bfloat16_t;
-using rocwmma::col_major;
-using rocwmma::float32_t;
-using rocwmma::matrix_a;
-using rocwmma::matrix_b;
-using rocwmma::row_major;
-
-constexpr int ROCWMMA_M = 16;
-constexpr int ROCWMMA_N = 16;
-constexpr int ROCWMMA_K = 16;
-
-extern "C" __global__ void gemm_rocwmma_d(uint32_t          m,
-                                          uint32_t          n,
-                                          uint32_t          k,
-                                          bfloat16_t const* a,
-                                          bfloat16_t const* b,
-                                          float32_t const*  c,
-                                          float32_t*        d,
-                                          uint32_t          lda,
-                                          uint32_t          ldb,
-                                          uint32_t          ldc,
-                                          uint32_t          ldd,
-                                          float32_t         alpha,
-                                          float32_t         beta)
-{
-    auto fragA = rocwmma::fragment<matrix_a, ROCWMMA_M, ROCWMMA_N, ROCWMMA_K, bfloat16_t, row_major>();
-    auto fragB = rocwmma::fragment<matrix_b, ROCWMMA_M, ROCWMMA_N, ROCWMMA_K, bfloat16_t, col_major>();
-    auto fragC   = rocwmma::fragment<accumulator, ROCWMMA_M, ROCWMMA_N, ROCWMMA_K, float32_t>();
-    auto fragAcc = rocwmma::fragment<accumulator, ROCWMMA_M, ROCWMMA_N, ROCWMMA_K, float32_t>();
-
-    rocwmma::fill_fragment(fragAcc, 0.0f);
-
-    auto majorWarp = (blockIdx.x * blockDim.x + threadIdx.x) / rocwmma::Constants::AMDGCN_WAVE_SIZE;
-    auto minorWarp = (blockIdx.y * blockDim.y + threadIdx.y);
-
-    auto cRow = majorWarp * ROCWMMA_M;
-    auto cCol = minorWarp * ROCWMMA_N;
-
-    if(cRow < m && cCol < n)
-    {
-        for(uint32_t i = 0; i < k; i += ROCWMMA_K)
-        {
-            rocwmma::load_matrix_sync(fragA, a + (cRow * lda + i), lda);
-            rocwmma::load_matrix_sync(fragB, b + (i + cCol * ldb), ldb);
-            rocwmma::mma_sync(fragAcc, fragA, fragB, fragAcc);
-        }
-        rocwmma::load_matrix_sync(fragC, c + (cRow * ldc + cCol), ldc, rocwmma::mem_row_major);
-        for(int i = 0; i < fragC.num_elements; ++i)
-        {
-            fragC.x[i] = alpha * fragAcc.x[i] + beta * fragC.x[i];
-        }
-        rocwmma::store_matrix_sync(d + (cRow * ldd + cCol), fragC, ldd, rocwmma::mem_row_major);
-    }
-}
-"""
-
-
 def _nvrtc():
     try:
         from cuda.bindings import nvrtc

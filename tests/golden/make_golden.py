@@ -1,5 +1,6 @@
-"""Regenerates the golden vectors in this directory.  Needs the reference tree
-mounted at /root/reference (it is NOT needed to run the tests).
+"""Regenerates the golden vectors in this directory.  Needs the rocWMMA source tree
+(oracle.reference_dir(): the environment variable ROCWMMA_REFERENCE_DIR or the default
+mount point); the tree is NOT needed to run the tests.
 
     python tests/golden/make_golden.py
 
@@ -25,7 +26,7 @@ import oracle as O  # noqa: E402
 from rocwmma_b200 import synth  # noqa: E402
 from tests.cases import GEMM_GOLDEN_CASES, gemm_inputs, gemv_inputs, dlrm_inputs  # noqa: E402
 
-REF_DATA = "/root/reference/test/dlrm/data"
+REF_DATA = os.path.join(O.reference_dir(), "test", "dlrm", "data")
 M, K, B = 27, 128, 64
 OUT = K + M * (M - 1) // 2
 

@@ -76,7 +76,7 @@ def test_dlrm_matches_reference_host_code(golden_dir):
     assert np.array_equal(grad.view(np.uint16), g["grad"].view(np.uint16))
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference"), reason="reference tree not mounted")
+@pytest.mark.skipif(not os.path.isdir(O.reference_dir()), reason="reference tree not mounted")
 def test_live_reference_build_agrees():
     """Where the reference tree is mounted, its freshly compiled host code must agree too."""
     assert O.ref() is not None
@@ -90,7 +90,7 @@ def test_live_reference_build_agrees():
     assert np.array_equal(got, want)
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference"), reason="reference tree not mounted")
+@pytest.mark.skipif(not os.path.isdir(O.reference_dir()), reason="reference tree not mounted")
 @pytest.mark.parametrize("triple", [(O.F16, O.F16, O.F16), (O.I8, O.I8, O.I32),
                                     (O.E4M3, O.F32, O.F32), (O.E5M2, O.F32, O.F32)])
 def test_live_reference_build_agrees_on_other_type_triples(triple):
@@ -113,7 +113,7 @@ def test_live_reference_build_agrees_on_other_type_triples(triple):
         assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (triple, literal)
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference"), reason="reference tree not mounted")
+@pytest.mark.skipif(not os.path.isdir(O.reference_dir()), reason="reference tree not mounted")
 def test_reference_sample_kernels_compile_unmodified():
     """Source-level drop-in: the kernel text of the reference's perf_*gemm, simple_*gemm,
     simple_*gemv and simple_dlrm samples compiles, unmodified, against include/rocwmma

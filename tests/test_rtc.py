@@ -7,15 +7,19 @@ import os
 import numpy as np
 import pytest
 
+import oracle as O
 from rocwmma_b200 import rtc
+from tests.rtc_kernels import TILE32_BF16_GEMM
+
+REF_RTC_SAMPLE = os.path.join(O.reference_dir(), "samples", "hipRTC_gemm.cpp")
 
 
 def test_headers_compile_under_nvrtc():
-    ptx = rtc.compile_to_ptx(rtc.BF16_SIMPLE_GEMM_SOURCE, "hiprtc_gemm_equivalent.cu")
+    ptx = rtc.compile_to_ptx(TILE32_BF16_GEMM, "tile32_gemm.cu")
     text = ptx.decode(errors="replace")
     assert ".target sm_100a" in text
     assert "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32" in text
-    assert "gemm_rocwmma_d" in text
+    assert "tile32_gemm" in text
 
 
 def test_all_api_headers_compile_under_nvrtc():
@@ -37,13 +41,12 @@ def test_all_api_headers_compile_under_nvrtc():
     assert b"sm_100a" in rtc.compile_to_ptx(src)
 
 
-@pytest.mark.skipif(not os.path.isfile("/root/reference/samples/hipRTC_gemm.cpp"),
-                    reason="reference tree not mounted")
+@pytest.mark.skipif(not os.path.isfile(REF_RTC_SAMPLE), reason="reference tree not mounted")
 def test_reference_rtc_kernel_source_compiles_unmodified():
     """The kernel source string of the reference's own run-time compilation sample
     (samples/hipRTC_gemm.cpp:73-173, a raw string literal handed to hipRTC) goes through NVRTC
     against these headers as it is: read from the mounted tree, never stored here."""
-    text = open("/root/reference/samples/hipRTC_gemm.cpp").read()
+    text = open(REF_RTC_SAMPLE).read()
     start = text.index('R"(') + 3
     source = text[start:text.index(')";', start)]
     assert "#include <rocwmma/rocwmma.hpp>" in source and "gemm_rocwmma_d" in source
@@ -61,7 +64,6 @@ def test_compile_errors_are_reported():
 def test_runtime_compiled_gemm_matches_the_oracle():
     import torch
 
-    import oracle as O
     from rocwmma_b200 import synth
     torch.cuda.init()
     torch.zeros(1, device="cuda")          # make the primary context current
@@ -74,12 +76,12 @@ def test_runtime_compiled_gemm_matches_the_oracle():
     tb = torch.from_numpy(bt.view(np.int16)).cuda()
     tc = torch.from_numpy(c).cuda()
     td = torch.full((m * n,), float("nan"), device="cuda")
-    mod = rtc.RtcModule(rtc.BF16_SIMPLE_GEMM_SOURCE, "gemm_rocwmma_d")
+    mod = rtc.RtcModule(TILE32_BF16_GEMM, "tile32_gemm")
     u32, f32, ptr = C.c_uint32, C.c_float, C.c_void_p
     args = [u32(m), u32(n), u32(k), ptr(ta.data_ptr()), ptr(tb.data_ptr()), ptr(tc.data_ptr()),
-            ptr(td.data_ptr()), u32(k), u32(k), u32(n), u32(n), f32(2.1), f32(2.1)]
-    # 4 x 4 warps per block as in the sample: 64 x 64 outputs per block
-    mod.launch((m // 64, n // 64, 1), (128, 4, 1), args,
+            ptr(td.data_ptr()), f32(2.1), f32(2.1)]
+    # 2 x 2 warps per block: 64 x 64 outputs per block
+    mod.launch((m // 64, n // 64, 1), (64, 2, 1), args,
                stream=torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     err = O.max_rel_err(O.F32, td.cpu().numpy(), want)
