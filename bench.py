@@ -9,15 +9,27 @@ A step is one pass of the block-cooperative GEMM over the whole problem.  With N
 rows of A and D are split evenly over the ranks (B replicated, no collective in the timed
 region), so the total work is fixed: strong scaling.  Prints ONE JSON line on rank 0.
 
-`value`    device-resident throughput: 2*M*N*K*steps / time of the K launches (CUDA events
-           on the launching stream, max over ranks).
-`e2e`      the same metric through the C ABI's host-buffer entry point
-           (b200wmma_gemm_host): pinned host A, B -> device, kernel, D -> host, every step.
+`value`    device-resident throughput: 2*M*N*K*K_steps / time of the K launches (CUDA events
+           on the launching stream, max over ranks).  The K-step region is timed REGIONS
+           times, each bracketed by a barrier and a device synchronisation; the line
+           reports the median region (all of them are listed under `regions_ms_per_step`):
+           at N = 8 a region lasts 2 ms, too short to stand alone.
+`e2e`      the same metric with HOST buffers: at N = 1 through the C ABI's host-buffer entry
+           point (b200wmma_gemm_host: pinned A, B -> device, kernel, D -> host); at N > 1
+           through rocwmma_b200.shard.ShardedHostGemm: every rank uploads its rows of A and
+           1/N of B, the B slabs are exchanged GPU to GPU (one NCCL all-gather over NVLink,
+           inside this timed region, never inside the `value` region), kernel, rows of D ->
+           host.
 `roofline` tensor-bound: achieved TFLOP/s of the kernel against the measured dense bf16/fp16
            peak of this pool (MEASURED_PEAKS.json, burst figure: the kernel is timed alone).
-`cpu_baseline`  the reference's own OpenMP host GEMM (oracle/_ref, else the oracle port) on
-           a bounded sample of rows of the same problem, on the host cores; the same rows
-           of the GPU result are checked against it.
+`parity`   after timing, every rank recomputes a sample of ITS OWN rows of D on the CPU with
+           the reference's host GEMM (oracle/_ref, else the oracle port) and compares; the
+           line carries the worst relative error over the ranks, at every N.  A result out
+           of tolerance makes the benchmark exit non-zero.
+`cpu_baseline`  (N = 1) that host GEMM timed on a bounded sample of rows of the same
+           problem, on all host cores (count stated).
+`extras`   every other benchmark configuration (bench_configs.py): throughput, roofline
+           fraction and parity per kernel, sharded the same way at N > 1.
 
 --impl reference times only that CPU implementation, on the same config and metric.
 """
@@ -40,9 +52,12 @@ WORKLOAD = ("perf_hgemm 8192^3: fp16 A row-major, fp16 B col-major, fp32 accumul
             "alpha=1, beta=0")
 METRIC = "hgemm 8192^3 TFLOP/s"
 FALLBACK_PEAK_TFLOPS = 1590.0
-# dram bytes per launch of the GEMM kernel from the ncu capture summarised under profiles/
-# (None until a capture exists for the current kernel)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.234e9  # 8192-row launch: 1.104 GB read + 0.130 GB written
+REGIONS = 5          # timed regions of K steps each; the median one is reported
+TOLERANCE = 2e-3     # fp16 inputs, fp32 accumulate: max |a-b| / (|a|+|b|+1)
+# DRAM bytes per launch of the GEMM kernel (dram__bytes_read.sum + dram__bytes_write.sum of one
+# profiler capture of an 8192-row launch), quoted -- not measured by this run -- in
+# roofline.traffic together with where it came from.  None = no capture of the current kernel.
+PROFILED_TRAFFIC = None
 
 
 def measured_peaks():
@@ -129,14 +144,26 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
+def make_config(world: int) -> dict:
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": WORKLOAD, "seed": SEED,
+            "partition": f"M-split x{world}, B replicated", "rows_per_gpu": M // world,
+            "l2": "per-GPU inputs (A rows + all of B >= 144 MiB) exceed the 126 MB L2; no flush",
+            "timing": f"median of {REGIONS} regions of K steps, each between barrier + "
+                      "synchronize; CUDA events on the launching stream, max over ranks"}
+
+
 def cpu_reference_sample(rows_budget_s: float, a_rows_fn, bt, want_rows=None):
-    """Times the reference's host GEMM on a sample of rows of the 8192^3 problem.
-    Returns (tflops, info, rows_idx, d_rows)."""
+    """Times the reference's host GEMM on a sample of rows of the 8192^3 problem, on all
+    host cores.  Returns (tflops, info, rows_idx, d_rows)."""
     import numpy as np
 
     import oracle as O
     use_ref = O.ref() is not None
     kind = "reference" if use_ref else "port"
+    # all host cores, whatever OMP_NUM_THREADS this process inherited (torch.distributed.run
+    # exports 1 to its workers)
+    O.set_num_threads(O.host_cores())
 
     def run(a_rows):
         nrows = a_rows.shape[0]
@@ -194,11 +221,35 @@ def run_reference_arm(args, rank, world):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
-            "data": "synthetic", "config": {"workload": WORKLOAD, "seed": SEED},
+            "data": "synthetic", "config": make_config(max(1, args.gpus)),
             "cpu_baseline": info,
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def shard_parity(a_host, b_host, d_dev, d_host, m_local, world, rows_budget=24):
+    """This rank recomputes a sample of its own rows of D with the reference's host GEMM and
+    compares the device-resident result and the end-to-end (host-buffer) result with it.
+    Returns (err_device, err_e2e, rows)."""
+    import numpy as np
+
+    import oracle as O
+    O.set_num_threads(max(1, O.host_cores() // world))
+    rng = np.random.default_rng(SEED * 100 + int(os.environ.get("RANK", "0")))
+    pick = np.unique(np.concatenate([[0, 127, 128, m_local - 1],
+                                     rng.integers(0, m_local, rows_budget)]))
+    a_np = a_host.numpy()[pick]
+    c0 = np.zeros(pick.size * N, dtype=np.float16)
+    fn = O.ref_gemm if O.ref() is not None else O.gemm
+    want = fn(O.F16, O.F16, pick.size, N, K, np.ascontiguousarray(a_np).reshape(-1),
+              b_host.numpy().reshape(-1), c0, 1.0, 0.0)
+    import torch
+    sel = torch.from_numpy(pick).cuda()
+    got = d_dev.view(m_local, N)[sel].cpu().numpy().reshape(-1)
+    err_dev = O.max_rel_err(O.F16, got, want)
+    err_e2e = O.max_rel_err(O.F16, np.ascontiguousarray(d_host.numpy()[pick]).reshape(-1), want)
+    return err_dev, err_e2e, int(pick.size)
 
 
 def main():
@@ -210,6 +261,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=None,
                     help="steps of the host-buffer measurement (default: min(steps, 10))")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the other configurations (bench_configs.py)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -232,15 +285,21 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
-    assert M % (world * synth.CHUNK_ROWS) == 0
+    assert M % (world * synth.CHUNK_ROWS) == 0 and N % world == 0
 
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
     row0, m_local = shard.gemm_shard(M, world, rank)
+    try:
+        gen_threads = max(1, min(16, len(os.sched_getaffinity(0)) // world))
+    except AttributeError:
+        gen_threads = 1
 
     # ---- synthetic inputs (seeded; every rank regenerates its own rows of A, all of B) ----
-    a_host = torch.from_numpy(synth.rows(SEED, 1, synth.F16, row0, m_local, K)).pin_memory()
-    b_host = torch.from_numpy(synth.rows(SEED, 2, synth.F16, 0, N, K)).pin_memory()
+    a_host = torch.from_numpy(synth.rows(SEED, 1, synth.F16, row0, m_local, K,
+                                         threads=gen_threads)).pin_memory()
+    b_host = torch.from_numpy(synth.rows(SEED, 2, synth.F16, 0, N, K,
+                                         threads=gen_threads)).pin_memory()
     d_host = torch.empty((m_local, N), dtype=torch.float16).pin_memory()
     a_dev = a_host.cuda(non_blocking=True)
     b_dev = b_host.cuda(non_blocking=True)
@@ -257,38 +316,48 @@ def main():
 
     stream = torch.cuda.current_stream()
 
-    # ---- device-resident measurement ----
+    # ---- device-resident measurement: REGIONS regions of exactly `steps` launches ----
     for _ in range(warmup):
         step()
     api.check_device()
     sampler = ClockSampler(physical_gpu_index(local_rank))
-    barrier()
+    region_ms = []
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(steps):
-        step()
-    e1.record(stream)
-    barrier()
+    for _ in range(REGIONS):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            step()
+        e1.record(stream)
+        barrier()
+        region_ms.append(shard.max_over_ranks(e0.elapsed_time(e1), device="cuda"))
     clocks = sampler.stop()
     api.check_device()
-    ms_total = e0.elapsed_time(e1)
+    ms_total = sorted(region_ms)[len(region_ms) // 2]
 
-    # ---- end to end through the host-buffer C entry point ----
+    # ---- end to end with host buffers ----
     e2e_steps = args.e2e_steps if args.e2e_steps is not None else min(steps, 10)
+    host_gemm = shard.ShardedHostGemm(api.F16, api.F16, M, N, K)
+    if world == 1:
+        b_part = b_host
+    else:
+        slab = N // world
+        b_part = b_host[rank * slab:(rank + 1) * slab]      # a view of the pinned buffer
+
+    def e2e_step():
+        host_gemm(a_host, b_part, None, d_host, 1.0, 0.0)
+
     for _ in range(2):
-        api.gemm_host(api.F16, api.F16, m_local, N, K, a_host, b_host, None, d_host, 1.0, 0.0)
+        e2e_step()
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record(stream)
     for _ in range(e2e_steps):
-        api.gemm_host(api.F16, api.F16, m_local, N, K, a_host, b_host, None, d_host, 1.0, 0.0)
+        e2e_step()
     f1.record(stream)
     barrier()
-    e2e_ms_total = f0.elapsed_time(f1)
-
-    ms_total = shard.max_over_ranks(ms_total, device="cuda")
-    e2e_ms_total = shard.max_over_ranks(e2e_ms_total, device="cuda")
+    e2e_ms_total = shard.max_over_ranks(f0.elapsed_time(f1), device="cuda")
 
     flops = 2.0 * M * N * K
     ms_per_step = ms_total / steps
@@ -312,46 +381,79 @@ def main():
                 "frac_of_sustained_peak": (kernel_tflops / sustained_peak
                                            if sustained_peak else None),
                 "timed_region_ms": ms_total,
-                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
+                "traffic": (PROFILED_TRAFFIC["bytes_per_launch"]
+                            if PROFILED_TRAFFIC and world == 1 else None),
+                "traffic_source": (PROFILED_TRAFFIC["source"] if PROFILED_TRAFFIC and world == 1
+                                   else "not captured for this launch shape"),
                 "peak_source": peak_src, "kernel": "gemm_tcgen05_pair_kernel<half,half,float>",
                 "algorithmic_flops_per_launch": 2.0 * m_local * N * K}
 
-    # ---- CPU baseline (rank 0, N = 1 only) + parity of the same rows ----
+    # ---- parity of every rank's shard (both results), worst over the ranks ----
+    err_dev, err_e2e, rows_checked = shard_parity(a_host, b_host, d_dev, d_host, m_local, world)
+    bad = 1e30
+    worst_dev = shard.max_over_ranks(err_dev if err_dev >= 0 else bad, device="cuda")
+    worst_e2e = shard.max_over_ranks(err_e2e if err_e2e >= 0 else bad, device="cuda")
+    parity_ok = worst_dev <= TOLERANCE and worst_e2e <= TOLERANCE
+    parity = {"max_rel_err": worst_dev, "e2e_max_rel_err": worst_e2e, "tolerance": TOLERANCE,
+              "within_tolerance": bool(parity_ok), "rows_checked_per_rank": rows_checked,
+              "ranks": world,
+              "checker": "rocWMMA gemm_CPU on each rank's own rows (per-shard validation)"}
+
+    # ---- CPU baseline (rank 0, N = 1 only) ----
     cpu_info = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        import oracle as O
         a_np, b_np = a_host.numpy(), b_host.numpy().reshape(-1)
         _, cpu_info, nrows, d_cpu = cpu_reference_sample(10.0, lambda n: a_np[:n], b_np)
+        import oracle as O
         d_gpu = d_dev.view(m_local, N)[:nrows].cpu().numpy().reshape(-1)
         err = O.max_rel_err(O.F16, d_gpu, d_cpu)
         cpu_info["gpu_rows_checked"] = nrows
         cpu_info["gpu_max_rel_err"] = err
-        cpu_info["gpu_within_tolerance_2e-3"] = bool(0 <= err <= 2e-3)
-        d_h = d_host[:nrows].numpy().reshape(-1)
-        cpu_info["e2e_rows_max_rel_err"] = O.max_rel_err(O.F16, d_h, d_cpu)
+        cpu_info["gpu_within_tolerance_2e-3"] = bool(0 <= err <= TOLERANCE)
+        cpu_info["e2e_rows_max_rel_err"] = O.max_rel_err(
+            O.F16, d_host[:nrows].numpy().reshape(-1), d_cpu)
+        parity_ok = parity_ok and 0 <= err <= TOLERANCE
+
+    # ---- every other configuration ----
+    extras = None
+    if not args.no_extras:
+        torch.cuda.empty_cache()
+        import bench_configs
+        extras = bench_configs.run_all()
+        parity_ok = parity_ok and all(e.get("parity", True) for e in extras)
 
     if rank == 0:
+        h2d = (a_host.numel() * 2 + b_part.numel() * 2)
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "seed": SEED, "partition": f"M-split x{world}, B replicated",
-                       "rows_per_gpu": m_local,
-                       "l2": "inputs (A+B = 256 MiB at N=1) exceed the 126 MB L2; no flush"},
+            "config": make_config(world),
+            "regions_ms_per_step": [r / steps for r in region_ms],
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "steps": e2e_steps,
-                    "h2d_bytes_per_step": int(a_host.numel() * 2 + b_host.numel() * 2),
+                    "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d_host.numel() * 2),
-                    "call": "b200wmma_gemm_host (pinned host buffers)"},
+                    "bytes_are": "per rank",
+                    "call": ("b200wmma_gemm_host (pinned host buffers)" if world == 1 else
+                             "rocwmma_b200.shard.ShardedHostGemm: rows of A + 1/N of B per rank "
+                             "over PCIe, NCCL all-gather of the B slabs over NVLink inside this "
+                             "region (not inside the `value` region), b200wmma_gemm, rows of D "
+                             "back")},
             "gpu_launches": steps,
             "roofline": roofline,
+            "parity": parity,
         }
         if cpu_info is not None:
             line["cpu_baseline"] = cpu_info
+        if extras is not None:
+            line["extras"] = extras
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if not parity_ok:
+        raise SystemExit("bench.py: a result is out of tolerance against the CPU reference")
 
 
 if __name__ == "__main__":

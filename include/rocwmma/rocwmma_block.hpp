@@ -142,6 +142,15 @@ namespace rocwmma
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensorMap))
                          : "memory");
         }
+        // Asks for the box at (x, y) of `tensorMap` to be brought into L2 (no shared-memory
+        // destination, no completion to wait for).  Same alignment rule for x as a load.
+        ROCWMMA_DEVICE inline void tma_prefetch_l2_2d(void const* tensorMap, int32_t x, int32_t y)
+        {
+            asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(
+                             reinterpret_cast<uint64_t>(tensorMap)),
+                         "r"(x), "r"(y)
+                         : "memory");
+        }
         // Loads the box of `tensorMap` whose innermost coordinate is x (elements;
         // x * element size must be a multiple of 16 bytes) and outer coordinate y
         // into shared memory at dst, signalling `bar` with the byte count.

@@ -108,6 +108,8 @@ def lib():
             getattr(L, name).restype = None
             getattr(L, name).argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
         L.oracle_num_threads.restype = C.c_int
+        L.oracle_set_num_threads.restype = None
+        L.oracle_set_num_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -176,6 +178,23 @@ def ref_kernels():
 
 def num_threads() -> int:
     return lib().oracle_num_threads()
+
+
+def host_cores() -> int:
+    """Host cores this process may run on."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def set_num_threads(n: int) -> int:
+    """OpenMP threads for the CPU routines of this module (restatement and reference build)
+    from now on; returns the count in effect.  Needed where a launcher exported
+    OMP_NUM_THREADS=1 (torch.distributed.run does): the CPU baseline states its core count
+    and must really use it."""
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
 
 
 def _check(a, code, name):

@@ -668,4 +668,14 @@ int oracle_num_threads()
 {
     return omp_get_max_threads();
 }
+
+// Sets the number of OpenMP threads later parallel regions of this process use (this
+// library's and the reference build's: they share one OpenMP runtime).  A launcher may have
+// exported OMP_NUM_THREADS=1 for every worker it starts; the timed CPU baseline must not
+// inherit that.
+void oracle_set_num_threads(int n)
+{
+    if(n >= 1)
+        omp_set_num_threads(n);
+}
 } // extern "C"

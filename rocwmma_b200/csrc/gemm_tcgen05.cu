@@ -29,6 +29,7 @@
 #include <cuda_bf16.h>
 #include <cstdlib>
 #include <cuda_fp16.h>
+#include <atomic>
 #include <mutex>
 #include <rocwmma/rocwmma_block.hpp>
 
@@ -83,6 +84,8 @@ namespace
         uint32_t    sumInTmem; // 1: chunked accumulation keeps its running sum in tensor memory
         uint32_t    wideCols; // pair kernel: tile columns of width bn ...
         uint32_t    tailCols, bnTail; // ... followed by tailCols columns of width bnTail (0: none)
+        uint32_t    snake, mirror; // pair kernel: tile order (TileSchedule)
+        uint32_t    prefetch; // pair kernel: k-blocks of the first tile to request into L2 early
     };
 
     // One operand tile for one K block.  K-major: one TMA box of `rows` rows x 128 bytes of
@@ -1006,7 +1009,8 @@ namespace
         const uint32_t numKB    = (p.k + BK - 1) / BK;
         const uint32_t chunkKB  = p.chunkKB != 0u ? p.chunkKB : numKB; // K blocks per chain
         const uint32_t numChunks = (numKB + chunkKB - 1) / chunkKB;
-        const TileSchedule sched{tilesM, p.wideCols, p.tailCols, bn, p.bnTail, p.band, nPairs};
+        const TileSchedule sched{tilesM, p.wideCols, p.tailCols, bn,      p.bnTail,
+                                 p.band, nPairs,     p.snake,    p.mirror};
 
         if(threadIdx.x == 0)
         {
@@ -1027,6 +1031,30 @@ namespace
             tma_prefetch_descriptor(&tmapB);
             tma_prefetch_descriptor(&tmapBTail);
             tma_prefetch_descriptor(&tmapD);
+        }
+        if(threadIdx.x == 64u && p.prefetch != 0u)
+        {
+            // The operands of this block's first ring slots are requested into L2 while the
+            // set-up below (and, under programmatic dependent launch, the previous kernel's
+            // tail) is still running.  An L2 prefetch reads nothing into the SM, and L2 is
+            // where a later write by the previous kernel lands too, so this is safe before
+            // griddepcontrol.wait even when A or B is that kernel's output.
+            uint32_t tm, col0, width;
+            if(sched.get(pairId, 0, tm, col0, width))
+            {
+                const void*    mapB = width == bn ? static_cast<void const*>(&tmapB)
+                                                  : static_cast<void const*>(&tmapBTail);
+                const int32_t  rowA = int32_t(tm * P_TILE_M + rank * 128u);
+                const int32_t  rowB = int32_t(col0 + rank * (width / 2u));
+                const uint32_t nkb  = p.prefetch < numKB ? p.prefetch : numKB;
+                for(uint32_t kb = 0; kb < nkb; ++kb)
+                {
+                    if(p.aMN == 0u)
+                        tma_prefetch_l2_2d(&tmapA, int32_t(kb * BK), rowA);
+                    if(p.bMN == 0u)
+                        tma_prefetch_l2_2d(mapB, int32_t(kb * BK), rowB);
+                }
+            }
         }
         if(warp == 1)
         {
@@ -1416,7 +1444,7 @@ namespace
         GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
                      status, chunkKB, wide, BN, bandEnv ? bandEnv : bandRows(k, sizeof(InT)),
                      useTma ? 1u : 0u,
-                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u};
+                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
         CUtensorMap mapA, mapB, mapD;
         {
             int rcD = makeOutputMap(&mapD, outputMapType<OutT>(), sizeof(OutT), d, m, n, ldd);
@@ -1482,7 +1510,7 @@ namespace
             auto makespan = [&](uint32_t bnW, uint32_t wideCols, uint32_t tailCols, uint32_t bnT) {
                 const uint32_t total = tilesM * (wideCols + tailCols);
                 const uint32_t pairs = total < pairsMax ? total : pairsMax;
-                TileSchedule   sc{tilesM, wideCols, tailCols, bnW, bnT, GROUP_M, pairs};
+                TileSchedule   sc{tilesM, wideCols, tailCols, bnW, bnT, GROUP_M, pairs, 0u, 0u};
                 uint32_t       worst = 0;
                 for(uint32_t pr = 0; pr < pairs; ++pr)
                 {
@@ -1536,6 +1564,31 @@ namespace
             p.wideCols = wideCols;
             p.tailCols = tailCols;
             p.bnTail   = bnTail;
+            // Tile order (TileSchedule).  B200WMMA_GEMM_ORDER = digits "smp" (snake, mirror on
+            // alternate launches, k-blocks prefetched into L2), e.g. "000" for the plain
+            // order; tuning and comparison only.
+            static const char* orderEnv = getenv("B200WMMA_GEMM_ORDER");
+            const bool snakeOn    = !(orderEnv && orderEnv[0] == '0');
+            const bool mirrorOn   = !(orderEnv && orderEnv[0] && orderEnv[1] == '0');
+            const uint32_t prefKB = (orderEnv && orderEnv[0] && orderEnv[1] && orderEnv[2] >= '0'
+                                     && orderEnv[2] <= '9')
+                                        ? uint32_t(orderEnv[2] - '0')
+                                        : P_STAGES;
+            p.snake    = snakeOn ? 1u : 0u;
+            p.prefetch = prefKB;
+            if(mirrorOn)
+            {
+                // Launches alternate between the forward and the mirrored order, so that each
+                // starts on the operands its predecessor left in L2 (the usual case being the
+                // same B, or the same A and B, launch after launch).  The result does not
+                // depend on the order.
+                static std::atomic<uint32_t> launchParity[64];
+                int                          dev = 0;
+                if(cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64)
+                    p.mirror = launchParity[dev].fetch_add(1u, std::memory_order_relaxed) & 1u;
+                else
+                    (void)cudaGetLastError();
+            }
             int rc = aMN ? makeOperandMapMN(&mapA, dt, sizeof(InT), a, m, k, lda)
                          : makeOperandMap(&mapA, dt, sizeof(InT), a, m, k, lda, 128);
             if(rc != B200WMMA_OK)

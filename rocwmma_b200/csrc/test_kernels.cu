@@ -309,6 +309,29 @@ TEST_API int b200wmma_test_tile_schedule(uint32_t tiles_m, uint32_t wide_cols, u
     return total;
 }
 
+// Order of the wide tiles: seq[tm * wide_cols + c] receives the position p + i * pairs at which
+// the schedule with the given `snake` / `mirror` settings hands out tile (tm, c) (no tail
+// columns).  Returns the number of tiles, or -1 when a tile lies outside the grid.
+TEST_API int b200wmma_test_tile_order(uint32_t tiles_m, uint32_t wide_cols, uint32_t bn,
+                                      uint32_t band, uint32_t pairs, uint32_t snake,
+                                      uint32_t mirror, uint32_t* seq)
+{
+    b200wmma::TileSchedule sc{tiles_m, wide_cols, 0u, bn, 0u, band, pairs, snake, mirror};
+    int                    total = 0;
+    for(uint32_t p = 0; p < pairs; ++p)
+    {
+        uint32_t tm, col0, width;
+        for(uint32_t i = 0; sc.get(p, i, tm, col0, width); ++i)
+        {
+            if(width != bn || col0 % bn != 0 || tm >= tiles_m || col0 / bn >= wide_cols)
+                return -1;
+            seq[tm * wide_cols + col0 / bn] = p + i * pairs;
+            ++total;
+        }
+    }
+    return total;
+}
+
 // Runs the never-satisfied wait with a limit of `limit_cycles` SM cycles (keep it around a
 // millisecond); the kernel always terminates by itself.
 TEST_API int b200wmma_test_bounded_wait(uint32_t* out4, long long limit_cycles, void* stream)

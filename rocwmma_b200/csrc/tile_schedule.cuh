@@ -13,9 +13,18 @@ namespace b200wmma
     // the pairs that are short take two of them each first, the rest is dealt round-robin.
     // All three roles of both blocks of a pair call get() with i = 0, 1, 2, ... and see the
     // same sequence; the host uses the same code to compare schedules.
+    //
+    // Order of the wide tiles: band by band (a band = `band` tile rows whose rows of A stay in
+    // L2), column by column inside a band.  With `snake` set, odd bands walk their columns
+    // right to left, so a band starts on the columns of B the band before it touched last
+    // and finds them in L2 (walking every band left to right streams all of B from DRAM
+    // once per band: B is about as large as the L2).  With `mirror` set the whole sequence
+    // runs backwards: a launch that mirrors its predecessor starts on the tiles -- and the
+    // rows of A and columns of B -- that predecessor finished on.
     struct TileSchedule
     {
         uint32_t tilesM, wideCols, tailCols, bn, bnTail, band, pairs;
+        uint32_t snake = 0, mirror = 0;
 
         __host__ __device__ uint32_t wideTiles() const
         {
@@ -34,15 +43,17 @@ namespace b200wmma
             const uint32_t mine = base + (p < nHi ? 1u : 0u);
             if(i < mine)
             {
-                const uint32_t t        = p + i * pairs;
+                const uint32_t seq      = p + i * pairs;
+                const uint32_t t        = mirror ? W - 1u - seq : seq;
                 const uint32_t perGroup = band * wideCols;
                 const uint32_t group    = t / perGroup;
                 const uint32_t firstM   = group * band;
                 const uint32_t rows     = (tilesM - firstM) < band ? (tilesM - firstM) : band;
                 const uint32_t r        = t % perGroup;
+                const uint32_t col      = r / rows;
                 tm                      = firstM + r % rows;
-                col0                    = (r / rows) * bn;
-                width                   = bn;
+                col0  = ((snake && (group & 1u)) ? wideCols - 1u - col : col) * bn;
+                width = bn;
                 return true;
             }
             i -= mine;

@@ -116,35 +116,47 @@ def _encode(x: np.ndarray, dtype: int) -> np.ndarray:
     raise ValueError(dtype)
 
 
+def _fill_chunk(out, r, n, seed, tensor_id, dtype, row0, ncols, dist, scale):
+    g = _rng(seed, tensor_id, (row0 + r) // CHUNK_ROWS)
+    if dist == "uniform":
+        out[r:r + n] = _encode(g.uniform(-1.0, 1.0, (n, ncols)), dtype)
+    elif dist == "normal":
+        out[r:r + n] = _encode(g.standard_normal((n, ncols)) * scale, dtype)
+    elif dist == "int8":
+        out[r:r + n] = g.integers(-128, 128, (n, ncols), dtype=np.int8)
+    elif dist == "int32":
+        out[r:r + n] = g.integers(-100, 101, (n, ncols)).astype(np.int32)
+    elif dist == "pattern":
+        idx = (np.arange(row0 + r, row0 + r + n)[:, None] * ncols + np.arange(ncols)[None, :])
+        v = (idx % 5).astype(np.float64)
+        v = np.where(idx % 3 != 0, -v, v)
+        out[r:r + n] = v.astype(NP_DTYPE[dtype]) if dtype in (I8, I32) else _encode(v, dtype)
+    else:
+        raise ValueError(dist)
+
+
 def rows(seed: int, tensor_id: int, dtype: int, row0: int, nrows: int, ncols: int,
-         dist: str = "uniform", scale: float = 1.0) -> np.ndarray:
+         dist: str = "uniform", scale: float = 1.0, threads: int = 1) -> np.ndarray:
     """Rows [row0, row0+nrows) of a (?, ncols) tensor stored row by row.
 
     dist: "uniform" in [-1, 1]; "normal" N(0,1) * scale; "int8" uniform integers in
     [-128, 127]; "int32" small integers in [-100, 100]; "pattern" = the reference's
     small-integer fill (rocWMMA test/common.hpp:248-270: (index % 5), negated when
     index % 3 != 0), which makes every GEMM exactly representable.
+    threads > 1 fills the 128-row chunks from a thread pool (every chunk has its own
+    stream, so the values do not depend on the thread count).
     """
     assert row0 % CHUNK_ROWS == 0, "shards start on chunk boundaries"
     out = np.empty((nrows, ncols), dtype=NP_DTYPE[dtype])
-    for r in range(0, nrows, CHUNK_ROWS):
-        n = min(CHUNK_ROWS, nrows - r)
-        g = _rng(seed, tensor_id, (row0 + r) // CHUNK_ROWS)
-        if dist == "uniform":
-            out[r:r + n] = _encode(g.uniform(-1.0, 1.0, (n, ncols)), dtype)
-        elif dist == "normal":
-            out[r:r + n] = _encode(g.standard_normal((n, ncols)) * scale, dtype)
-        elif dist == "int8":
-            out[r:r + n] = g.integers(-128, 128, (n, ncols), dtype=np.int8)
-        elif dist == "int32":
-            out[r:r + n] = g.integers(-100, 101, (n, ncols)).astype(np.int32)
-        elif dist == "pattern":
-            idx = (np.arange(row0 + r, row0 + r + n)[:, None] * ncols + np.arange(ncols)[None, :])
-            v = (idx % 5).astype(np.float64)
-            v = np.where(idx % 3 != 0, -v, v)
-            out[r:r + n] = v.astype(NP_DTYPE[dtype]) if dtype in (I8, I32) else _encode(v, dtype)
-        else:
-            raise ValueError(dist)
+    starts = range(0, nrows, CHUNK_ROWS)
+    args = (seed, tensor_id, dtype, row0, ncols, dist, scale)
+    if threads > 1 and len(starts) > 1:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=threads) as ex:
+            list(ex.map(lambda r: _fill_chunk(out, r, min(CHUNK_ROWS, nrows - r), *args), starts))
+    else:
+        for r in starts:
+            _fill_chunk(out, r, min(CHUNK_ROWS, nrows - r), *args)
     return out
 
 

@@ -28,18 +28,26 @@ def test_distributions_and_encodings():
 
 
 def test_benchmark_table_rows_match_the_reference_header():
-    """bench_all --csv writes rocWMMA's result table: one value per header column."""
-    from rocwmma_b200 import bench_all as B
+    """bench_configs.py --csv writes rocWMMA's result table: one value per header column."""
+    import bench_configs as B
     cols = [c.strip() for c in B.CSV_HEADER.split(",")]
     assert cols[:5] == ["TBlkX", "TBlkY", "BlkM", "BlkN", "BlkK"] and cols[-1] == "Result"
     for simple, in_t, out_t in [(True, B.F16, B.F32), (False, B.E5M2, B.BF16),
                                 (False, B.F64, B.F64), (False, B.I8, B.I32)]:
-        r = {"ms": 0.5, "value": 100.0, "frac": 0.25,
+        r = {"ms": 0.5, "value": 100.0, "roofline": {"frac": 0.25},
              "gemm": {"in_t": in_t, "out_t": out_t, "size": 1024, "alpha": 1.0, "beta": 0.0,
                       "simple": simple}}
         row = [c.strip() for c in B.csv_row(r).split(",")]
         assert len(row) == len(cols)
         assert row[cols.index("Result")] == "BENCH"
         assert row[cols.index("Efficiency(%)")] == "25.00"
-    assert "bf8_bf16_f32" in B.csv_row({"ms": 1, "value": 1, "frac": 1, "gemm": {
+        assert B.csv_row(dict(r, parity=True)).endswith("PASSED")
+        assert B.csv_row(dict(r, parity=False)).endswith("FAILED")
+    assert "bf8_bf16_f32" in B.csv_row({"ms": 1, "value": 1, "roofline": {"frac": 1}, "gemm": {
         "in_t": B.E5M2, "out_t": B.BF16, "size": 64, "alpha": 1, "beta": 0, "simple": False}})
+
+
+def test_threaded_generation_gives_the_same_values():
+    a = synth.rows(7, 1, synth.F16, 256, 1000, 96, threads=1)
+    b = synth.rows(7, 1, synth.F16, 256, 1000, 96, threads=6)
+    assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
