@@ -321,7 +321,7 @@ def main():
         step()
     api.check_device()
     sampler = ClockSampler(physical_gpu_index(local_rank))
-    region_ms = []
+    region_ms, own_ms = [], []
     sampler.start()
     for _ in range(REGIONS):
         barrier()
@@ -331,10 +331,19 @@ def main():
             step()
         e1.record(stream)
         barrier()
-        region_ms.append(shard.max_over_ranks(e0.elapsed_time(e1), device="cuda"))
+        mine = e0.elapsed_time(e1)
+        own_ms.append(mine)
+        region_ms.append(shard.max_over_ranks(mine, device="cuda"))
     clocks = sampler.stop()
     api.check_device()
     ms_total = sorted(region_ms)[len(region_ms) // 2]
+    # every rank's own median region, for the record (the figure above is the slowest rank's)
+    per_rank = [sorted(own_ms)[len(own_ms) // 2] / steps]
+    if world > 1:
+        t = torch.tensor(per_rank, dtype=torch.float64, device="cuda")
+        allr = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(allr, t)
+        per_rank = [float(x.item()) for x in allr]
 
     # ---- end to end with host buffers ----
     e2e_steps = args.e2e_steps if args.e2e_steps is not None else min(steps, 10)
@@ -430,6 +439,7 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": make_config(world),
             "regions_ms_per_step": [r / steps for r in region_ms],
+            "per_rank_ms_per_step": per_rank,
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "steps": e2e_steps,

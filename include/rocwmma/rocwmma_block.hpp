@@ -406,6 +406,18 @@ namespace rocwmma
             asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         }
+        // The two halves of a cluster barrier, to be used as a pair with independent work in
+        // between.  The arrival orders nothing by itself: what the other block must see
+        // (freshly initialised mbarriers) has to be released before it, as mbar_init_fence()
+        // does.  Every thread of the block executes both, warps converged.
+        ROCWMMA_DEVICE inline void cluster_arrive_relaxed()
+        {
+            asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+        }
+        ROCWMMA_DEVICE inline void cluster_wait()
+        {
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
         // Programmatic dependent launch.  A kernel launched with the stream-serialization
         // attribute may start while the previous kernel of its stream still runs;
         // grid_dependency_wait() returns once that kernel has completed and its writes are
@@ -513,6 +525,18 @@ namespace rocwmma
                   "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
                   "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr)
+                : "memory");
+        }
+        // Same for 16 columns.
+        ROCWMMA_DEVICE inline void tmem_load_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
+        {
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+                  "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                  "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                 : "r"(taddr)
                 : "memory");
         }

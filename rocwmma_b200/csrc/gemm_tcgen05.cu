@@ -86,6 +86,7 @@ namespace
         uint32_t    tailCols, bnTail; // ... followed by tailCols columns of width bnTail (0: none)
         uint32_t    snake, mirror; // pair kernel: tile order (TileSchedule)
         uint32_t    prefetch; // pair kernel: k-blocks of the first tile to request into L2 early
+        uint32_t    stagedTail; // pair kernel: a block's last tile leaves through the idle ring
     };
 
     // One operand tile for one K block.  K-major: one TMA box of `rows` rows x 128 bytes of
@@ -718,6 +719,119 @@ namespace
         return true;
     }
 
+    // ---- a block's LAST tile: out through the idle operand ring ---------------------------
+    // Inside a run of tiles the epilogue hides behind the next tile's MMAs; after a block's
+    // last tile nothing is left to hide it, and a two-wave launch (the 1024-row shard of an
+    // 8-GPU run) pays it once per two tiles: 128 rows x 224 columns took 2.6 us through
+    // per-thread row stores, which touch 32 different cache lines per warp instruction.
+    // When the accumulator of the last tile is complete every MMA of the pair has finished
+    // reading shared memory and no load is in flight, so the ring is free: the epilogue
+    // threads lay the whole tile out there -- boxes of 128 rows x 128 bytes in the TMA's
+    // 128-byte swizzle, which also keeps the 16-byte shared stores free of bank conflicts --
+    // with no block-wide barrier between column groups, and one thread hands the boxes to
+    // TMA stores, which write whole 128-byte lines.  2-byte outputs whose tile width is an
+    // odd multiple of 32 columns end in one box of 64-byte rows (the narrow map).
+    // Rows and columns beyond m and n are clipped by the TMA.
+    template <typename OutT, typename CompT>
+    __device__ inline bool drainLastTileStaged(uint64_t* accFullBar, uint32_t accPh,
+                                               AbortState* abort, uint32_t taddrRowBase,
+                                               GemmParams const& p, CUtensorMap const* mapWide,
+                                               CUtensorMap const* mapNarrow, uint8_t* stage,
+                                               CompT alpha, CompT beta, bool useC,
+                                               uint32_t rowInTile, uint32_t tileRow0,
+                                               uint32_t colBase, bool leader, uint32_t bnTile)
+    {
+        // The tile is walked 16 columns at a time (two register sets of 16: the next
+        // tensor-memory load is in flight while the current columns are converted and staged).
+        constexpr uint32_t HALF_B   = 16 * sizeof(OutT); // bytes of 16 columns: 32 or 64
+        constexpr uint32_t PER_BOX  = 128 / HALF_B; // 16-column pieces per 128-byte box row
+        constexpr uint32_t VEC      = 16 / sizeof(OutT);
+        constexpr uint32_t CHUNKS   = HALF_B / 16; // 16-byte chunks per piece: 2 or 4
+        constexpr uint32_t BOX_COLS = 128 / sizeof(OutT);
+        constexpr uint32_t BOX_B    = 128 * 128;
+        const uint32_t     pieces   = bnTile / 16u;
+        const uint32_t     wide     = pieces / PER_BOX; // full 128-byte boxes
+        const uint32_t     row      = tileRow0 + rowInTile;
+        const bool         readC    = useC && row < p.m;
+        OutT const*        cRow     = static_cast<OutT const*>(p.c) + size_t(row) * p.ldc;
+
+        const bool ready = mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL);
+        if(!named_barrier_all(1, EPI_THREADS, ready))
+            return false;
+        tc_fence_after_sync();
+        uint32_t rawA[16], rawB[16];
+        auto     emit = [&](uint32_t const (&raw)[16], uint32_t piece) {
+            const uint32_t col0 = colBase + piece * 16u;
+            const uint32_t box  = piece / PER_BOX;
+            uint8_t*       base = stage + box * BOX_B;
+#pragma unroll
+            for(uint32_t ch = 0; ch < CHUNKS; ++ch)
+            {
+                alignas(16) OutT out[VEC];
+                alignas(16) OutT cin[VEC];
+                const uint32_t   col = col0 + ch * VEC;
+                if(readC)
+                {
+                    if(col + VEC <= p.n)
+                        ldVec<16>(cin, cRow + col);
+                    else
+                        for(uint32_t e = 0; e < VEC; ++e)
+                            cin[e] = (col + e < p.n) ? cRow[col + e] : OutT(0);
+                }
+#pragma unroll
+                for(uint32_t e = 0; e < VEC; ++e)
+                {
+                    CompT acc;
+                    if constexpr(std::is_same<CompT, float>::value)
+                        acc = __uint_as_float(raw[ch * VEC + e]);
+                    else
+                        acc = int32_t(raw[ch * VEC + e]);
+                    CompT r;
+                    if(readC)
+                        r = scaleAdd(alpha, acc, beta, CompT(toCompute(cin[e])));
+                    else if constexpr(std::is_same<CompT, float>::value)
+                        r = CompT(__fmul_rn(float(alpha), float(acc)));
+                    else
+                        r = CompT(alpha * acc);
+                    out[e] = fromCompute<OutT, CompT>(r);
+                }
+                uint32_t off;
+                if(box < wide) // 128-byte rows
+                    off = stagingOffset<128>(rowInTile, (piece % PER_BOX) * CHUNKS + ch);
+                else // the odd last 32 columns of a 2-byte output: 64-byte rows
+                    off = stagingOffset<64>(rowInTile, (piece % PER_BOX) * CHUNKS + ch);
+                *reinterpret_cast<uint4*>(base + off) = *reinterpret_cast<uint4 const*>(out);
+            }
+        };
+        tmem_load_32x32b_x16(taddrRowBase, rawA); // warp-wide
+#pragma unroll 1
+        for(uint32_t piece = 0; piece < pieces; piece += 2) // pieces is even: bnTile % 32 == 0
+        {
+            tmem_load_wait();
+            tmem_load_32x32b_x16(taddrRowBase + (piece + 1) * 16u, rawB);
+            emit(rawA, piece);
+            tmem_load_wait();
+            if(piece + 2 < pieces)
+                tmem_load_32x32b_x16(taddrRowBase + (piece + 2) * 16u, rawA);
+            emit(rawB, piece + 1);
+        }
+        fence_async_shared();
+        named_barrier(1, EPI_THREADS);
+        if(leader && tileRow0 < p.m)
+        {
+            for(uint32_t b = 0; b < wide; ++b)
+                if(colBase + b * BOX_COLS < p.n)
+                    tma_store_2d(mapWide, stage + b * BOX_B, int32_t(colBase + b * BOX_COLS),
+                                 int32_t(tileRow0));
+            if(pieces % PER_BOX != 0u && colBase + wide * BOX_COLS < p.n)
+                tma_store_2d(mapNarrow, stage + wide * BOX_B, int32_t(colBase + wide * BOX_COLS),
+                             int32_t(tileRow0));
+            tma_store_commit();
+        }
+        tc_fence_before_sync();
+        return true;
+    }
+
     template <typename InT, typename OutT, typename CompT>
     __global__ void __launch_bounds__(NUM_THREADS, 1)
         gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmapA,
@@ -976,6 +1090,7 @@ namespace
                                  const __grid_constant__ CUtensorMap tmapB,
                                  const __grid_constant__ CUtensorMap tmapBTail,
                                  const __grid_constant__ CUtensorMap tmapD,
+                                 const __grid_constant__ CUtensorMap tmapDWide,
                                  const GemmParams                    p)
     {
         constexpr uint32_t BK     = ROW_BYTES / sizeof(InT);
@@ -1031,7 +1146,14 @@ namespace
             tma_prefetch_descriptor(&tmapB);
             tma_prefetch_descriptor(&tmapBTail);
             tma_prefetch_descriptor(&tmapD);
+            tma_prefetch_descriptor(&tmapDWide);
         }
+        // First half of the pair's start-up barrier: this block's mbarriers exist (thread 0
+        // released them above, before its own arrival).  The wait comes after the rest of the
+        // set-up, which so overlaps the barrier's latency (measured: a back-to-back
+        // arrive + wait at this point cost 1.8 us of every launch).
+        __syncwarp();
+        cluster_arrive_relaxed();
         if(threadIdx.x == 64u && p.prefetch != 0u)
         {
             // The operands of this block's first ring slots are requested into L2 while the
@@ -1063,7 +1185,7 @@ namespace
         }
         tc_fence_before_sync();
         __syncthreads();
-        cluster_sync(); // both blocks' barriers exist before anything signals them remotely
+        cluster_wait(); // both blocks' barriers exist before anything signals them remotely
         tc_fence_after_sync();
         const uint32_t tmemBase = ctl->tmemBase;
         // Programmatic dependent launch: everything above (barriers, tensor-memory
@@ -1183,6 +1305,9 @@ namespace
                 if(!sched.get(pairId, i, tm, col0, width))
                     break;
                 const uint32_t row = tm * P_TILE_M + rank * 128u + quad * 32u + lane;
+                uint32_t       tmNext, colNext, widthNext;
+                const bool     stagedTail = p.stagedTail != 0u && numChunks == 1u
+                                        && !sched.get(pairId, i + 1u, tmNext, colNext, widthNext);
                 for(uint32_t ch = 0; ch < numChunks; ++ch, ++accIter)
                 {
                     const uint32_t buf   = accIter & 1u;
@@ -1194,8 +1319,16 @@ namespace
                     const uint32_t taddrLane = tmemBase + ((quad * 32u) << 16);
                     const uint32_t taddr     = taddrLane + buf * BN;
                     bool           drained;
-                    if constexpr(std::is_same<OutT, float>::value
-                                 && std::is_same<CompT, float>::value)
+                    if(stagedTail)
+                    {
+                        // this block's last tile: the ring is idle, see drainLastTileStaged
+                        drained = drainLastTileStaged<OutT, CompT>(
+                            &ctl->accFull[buf], accPh, &ctl->abort, taddr, p, &tmapDWide, &tmapD,
+                            tiles, alpha, beta, useC, quad * 32u + lane,
+                            tm * P_TILE_M + rank * 128u, col0, threadIdx.x == 64u, width);
+                    }
+                    else if constexpr(std::is_same<OutT, float>::value
+                                      && std::is_same<CompT, float>::value)
                     {
                         if(p.sumInTmem && numChunks > 1u)
                             drained = drainAccumulatorToTmemSum(&ctl->accFull[buf], accPh,
@@ -1233,13 +1366,23 @@ namespace
                 }
             }
             if(threadIdx.x == 64u)
-                tma_store_wait_all<0>(); // every TMA store of this block has been performed
+            {
+                // Shared memory must outlive the TMA stores' reads of it.  The staged last
+                // tile waits for exactly that (the writes themselves complete with the grid);
+                // the chunked-accumulation path has waited for its stores to be performed.
+                if(p.stagedTail != 0u && numChunks == 1u)
+                    tma_store_wait_read<0>();
+                else
+                    tma_store_wait_all<0>();
+            }
         }
 
         // ---------------- teardown ----------------
         tc_fence_before_sync();
         __syncthreads();
-        cluster_sync(); // neither block leaves while the other may still signal it
+        // neither block leaves while the other may still signal it (nothing to order: relaxed)
+        cluster_arrive_relaxed();
+        cluster_wait();
         if(warp == 1)
         {
             __syncwarp();
@@ -1278,18 +1421,20 @@ namespace
 
     // Tensor map of the row-major output: rows x cols elements, `ld` apart; box = 32 columns
     // (128 or 64 bytes, swizzled accordingly) x 128 rows.
+    // boxCols * elemBytes is 64 or 128 bytes, which is also the swizzle span.
     int makeOutputMap(CUtensorMap* map, CUtensorMapDataType dt, size_t elemBytes, void* base,
-                      uint32_t rows, uint32_t cols, uint32_t ld)
+                      uint32_t rows, uint32_t cols, uint32_t ld, uint32_t boxCols = 32)
     {
         EncodeFn fn = encoder();
         if(!fn)
             return B200WMMA_ERR_CUDA;
         cuuint64_t dims[2]    = {cols, rows};
         cuuint64_t strides[1] = {cuuint64_t(ld) * elemBytes};
-        cuuint32_t box[2]     = {32, 128};
+        cuuint32_t box[2]     = {boxCols, 128};
         cuuint32_t estr[2]    = {1, 1};
         CUresult   r = fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        elemBytes == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                        boxCols * elemBytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                                   : CU_TENSOR_MAP_SWIZZLE_64B,
                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         return r == CUDA_SUCCESS ? B200WMMA_OK : B200WMMA_ERR_CUDA;
     }
@@ -1444,7 +1589,7 @@ namespace
         GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
                      status, chunkKB, wide, BN, bandEnv ? bandEnv : bandRows(k, sizeof(InT)),
                      useTma ? 1u : 0u,
-                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
         CUtensorMap mapA, mapB, mapD;
         {
             int rcD = makeOutputMap(&mapD, outputMapType<OutT>(), sizeof(OutT), d, m, n, ldd);
@@ -1606,6 +1751,26 @@ namespace
                 if(rc != B200WMMA_OK)
                     return rc;
             }
+            // The last tile of every block leaves through the idle operand ring and TMA stores
+            // of 128-byte rows (drainLastTileStaged) when TMA stores are safe for D -- they
+            // write whole 16-byte pieces, so a row of D must end on a 16-byte boundary -- and
+            // K is accumulated in one chain.  B200WMMA_GEMM_STAGED_TAIL=0 switches it off.
+            static const bool stagedEnv = [] {
+                const char* e = getenv("B200WMMA_GEMM_STAGED_TAIL");
+                return !(e && e[0] == '0');
+            }();
+            CUtensorMap mapDWide = mapD;
+            if(stagedEnv && tmaSafe && chunkKB == 0u && epilogueEnv == 0)
+            {
+                p.stagedTail = 1u;
+                if(sizeof(OutT) == 2)
+                {
+                    rc = makeOutputMap(&mapDWide, outputMapType<OutT>(), sizeof(OutT), d, m, n,
+                                       ldd, 64);
+                    if(rc != B200WMMA_OK)
+                        return rc;
+                }
+            }
             auto        kernel = gemm_tcgen05_pair_kernel<InT, OutT, CompT>;
             static bool done[64] = {};
             rc = optInSharedMemory(kernel, P_SMEM_BYTES, done);
@@ -1615,7 +1780,7 @@ namespace
             const uint32_t pairs = tiles < pairsMax ? tiles : pairsMax;
             return b200wmma::cudaToStatus(b200wmma::launchOverlapped(
                 kernel, dim3(2 * pairs), dim3(NUM_THREADS), P_SMEM_BYTES, stream, mapA, mapB,
-                mapBTail, mapD, p));
+                mapBTail, mapD, mapDWide, p));
         }
 
         int rc = aMN ? makeOperandMapMN(&mapA, dt, sizeof(InT), a, m, k, lda)
