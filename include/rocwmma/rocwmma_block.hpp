@@ -164,6 +164,17 @@ namespace rocwmma
                          : "memory");
         }
 
+        // One-dimensional form: the box starting at element x (x * element size a multiple of
+        // 16 bytes).
+        ROCWMMA_DEVICE inline void tma_load_1d(void* dst, void const* tensorMap, uint64_t* bar,
+                                               int32_t x)
+        {
+            asm volatile("cp.async.bulk.tensor.1d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                         " [%0], [%1, {%3}], [%2];" ::"r"(smem_addr(dst)),
+                         "l"(reinterpret_cast<uint64_t>(tensorMap)), "r"(smem_addr(bar)), "r"(x)
+                         : "memory");
+        }
+
         // ---- untiled bulk copies (cp.async.bulk): contiguous bytes, no tensor map ----------
         // Both addresses 16-byte aligned, `bytes` a multiple of 16.
         // Global -> this block's shared memory; `bar` receives complete_tx(bytes).

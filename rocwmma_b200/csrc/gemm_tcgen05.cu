@@ -1397,26 +1397,10 @@ namespace
     }
 
     // ---- host side -----------------------------------------------------------------
-    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-    EncodeFn encoder()
+    using b200wmma::EncodeFn;
+    inline EncodeFn encoder()
     {
-        static EncodeFn       fn = nullptr;
-        static std::once_flag once;
-        std::call_once(once, [] {
-            void*                           sym = nullptr;
-            cudaDriverEntryPointQueryResult q;
-            if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q)
-                   == cudaSuccess
-               && q == cudaDriverEntryPointSuccess)
-                fn = reinterpret_cast<EncodeFn>(sym);
-            else
-                (void)cudaGetLastError();
-        });
-        return fn;
+        return b200wmma::tensorMapEncoder();
     }
 
     // Tensor map of the row-major output: rows x cols elements, `ld` apart; box = 32 columns

@@ -11,62 +11,63 @@
 // whatever the size (a K-split or tree reduction would differ from it by the
 // rounding noise of a 16384-term fp32 sum, which alone exceeds 1e-4 relative).
 //
-//   * a block owns 64 consecutive rows; four loader warps stream 64-row x 32-column
-//     tiles of A through a 10-slot shared-memory ring with 16-byte cp.async copies,
-//     full/empty mbarriers per slot; the 32 values of x that belong to a tile travel in
-//     the same slot, so that no compute thread ever waits on a global load (with x read
-//     straight from global memory the kernel was bound by that latency, 3.8 TB/s);
-//   * 64 compute threads, one per row, read their row's element of each column from
-//     the slot (consecutive threads, consecutive addresses) and x[h] by warp-uniform
-//     vector loads;
+//   * a block owns 64 consecutive rows (32 when the matrix has so few rows that 64-row
+//     blocks would leave most SMs idle: a row shard of a many-GPU run); one producer thread
+//     streams ROWS-row x 32-column tiles of A through a shared-memory ring (12 slots of
+//     8 KiB, or 24 of 4 KiB) with one TMA tile load each, full/empty mbarriers per slot; the
+//     32 values of x that belong to a tile travel in the same slot (a second, one-dimensional
+//     TMA load), so that no compute thread ever waits on a global load (with x read straight
+//     from global memory the kernel was bound by that latency, 3.8 TB/s).  (The first form of
+//     this loader, four warps issuing 16-byte cp.async copies, held a block to ~25 GB/s
+//     whatever the grid: the SM tracks only so many outstanding load sectors, and 80 KiB in
+//     flight needed far more.  One TMA request moves a whole tile.)
+//   * one compute thread per row reads its row's element of each column from the slot
+//     (consecutive threads, consecutive addresses) and x[h] by warp-uniform vector loads;
+//     its loop is software-pipelined three tiles deep (see the compute branch), so that the
+//     only thing on the critical path is the chain of dependent additions the ordered sum
+//     consists of: 4 cycles per column, ~35 us for 16384 columns whatever the row count;
 //   * 2 blocks per SM, 80 KiB of loads in flight per block.
 //
-// When pointer or leading dimension are not 16-byte multiples a plain-load kernel with
-// the same summation order is used.
+// When A, x or the leading dimension are not 16-byte multiples (TMA cannot address them) a
+// plain-load kernel with the same summation order is used.
 #include "common.cuh"
 #include "runtime.cuh"
+#include <cuda.h>
 #include <rocwmma/rocwmma_block.hpp>
 
 using namespace rocwmma::block;
 
 namespace
 {
-    constexpr uint32_t ROWS       = 64; // rows per block, one compute thread per row
-    constexpr uint32_t TILE_BYTES = 8192; // COLS columns x ROWS rows of A
-    constexpr uint32_t XSEG_BYTES = 128; // the COLS values of x that go with them
-    constexpr uint32_t SLOT_BYTES = TILE_BYTES + XSEG_BYTES; // one ring slot
-    constexpr uint32_t STAGES     = 10;
-    constexpr uint32_t CWARPS     = ROWS / 32; // compute warps
-    constexpr uint32_t LWARPS     = 4; // loader warps
-    constexpr uint32_t LTHREADS   = LWARPS * 32;
-    constexpr uint32_t THREADS    = ROWS + LTHREADS;
+    constexpr uint32_t COLS_BYTES = 128; // the columns of a tile: 128 bytes of x (32 fp32, 16 fp64)
+    constexpr uint32_t LTHREADS   = 32; // the producer warp (one elected thread issues)
 
-    struct Control
+    // Geometry of one instantiation: ROWS rows per block (one compute thread per row), STAGES
+    // ring slots of one tile (ROWS rows x 128 bytes' worth of columns) plus its x values.
+    template <typename T, uint32_t ROWS_, uint32_t STAGES_>
+    struct Geometry
     {
-        uint64_t   full[STAGES];
-        uint64_t   empty[STAGES];
-        AbortState abort;
+        static constexpr uint32_t ROWS       = ROWS_;
+        static constexpr uint32_t STAGES     = STAGES_;
+        static constexpr uint32_t COLS       = COLS_BYTES / sizeof(T);
+        static constexpr uint32_t TILE_BYTES = ROWS * COLS * sizeof(T);
+        static constexpr uint32_t XSEG_BYTES = COLS_BYTES;
+        static constexpr uint32_t SLOT_BYTES = TILE_BYTES + XSEG_BYTES;
+        static constexpr uint32_t THREADS    = ROWS + LTHREADS;
+        struct Control
+        {
+            uint64_t   full[STAGES];
+            uint64_t   empty[STAGES];
+            AbortState abort;
+        };
+        static constexpr uint32_t SMEM_BYTES
+            = STAGES * SLOT_BYTES + 128 /*alignment slack*/ + sizeof(Control);
     };
-    constexpr uint32_t SMEM_BYTES = STAGES * SLOT_BYTES + 128 /*alignment slack*/ + sizeof(Control);
 
     __device__ inline float  mulRn(float a, float b) { return __fmul_rn(a, b); }
     __device__ inline double mulRn(double a, double b) { return __dmul_rn(a, b); }
     __device__ inline float  addRn(float a, float b) { return __fadd_rn(a, b); }
     __device__ inline double addRn(double a, double b) { return __dadd_rn(a, b); }
-
-    // 16-byte asynchronous copy global -> shared; bytes beyond srcBytes are zero-filled.
-    __device__ inline void cpAsync16(uint32_t dst, void const* src, uint32_t srcBytes)
-    {
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
-                     "r"(srcBytes)
-                     : "memory");
-    }
-    // One arrival on `bar` once all cp.async issued so far by this thread have landed.
-    __device__ inline void cpAsyncArriveOn(uint64_t* bar)
-    {
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(bar))
-                     : "memory");
-    }
 
     template <typename T, uint32_t N>
     struct alignas(sizeof(T) * N) Vec
@@ -74,37 +75,38 @@ namespace
         T v[N];
     };
 
-    template <typename T>
-    __global__ void __launch_bounds__(THREADS, 2)
-        gemvStreamKernel(uint32_t m, uint32_t k, T const* __restrict__ a, T const* __restrict__ x,
-                         T const* yIn, T* yOut, T alpha, T beta, uint32_t lda, uint32_t* status)
+    template <typename T, uint32_t ROWS, uint32_t STAGES>
+    __global__ void __launch_bounds__(ROWS + LTHREADS, 2)
+        gemvStreamKernel(const __grid_constant__ CUtensorMap tmapA,
+                         const __grid_constant__ CUtensorMap tmapX, uint32_t m, uint32_t k,
+                         T const* yIn, T* yOut, T alpha, T beta, uint32_t* status)
     {
-        constexpr uint32_t COLS   = TILE_BYTES / (ROWS * sizeof(T)); // 32 (fp32) / 16 (fp64)
-        constexpr uint32_t CPC    = ROWS * sizeof(T) / 16; // 16-byte chunks per column
-        constexpr uint32_t CHUNKS = COLS * CPC; // per ring slot (512)
-        constexpr uint32_t XV     = 16 / sizeof(T);
+        using G = Geometry<T, ROWS, STAGES>;
+        using Control = typename G::Control;
+        constexpr uint32_t COLS       = G::COLS; // 32 (fp32) / 16 (fp64)
+        constexpr uint32_t TILE_BYTES = G::TILE_BYTES;
+        constexpr uint32_t SLOT_BYTES = G::SLOT_BYTES;
+        constexpr uint32_t XV         = 16 / sizeof(T);
         extern __shared__ uint8_t smemRaw[];
         const uint32_t            raw   = smem_addr(smemRaw);
         uint8_t*                  tiles = smemRaw + ((128u - (raw & 127u)) & 127u);
         Control* ctl = reinterpret_cast<Control*>(tiles + STAGES * SLOT_BYTES);
 
-        static_assert(COLS * sizeof(T) == XSEG_BYTES, "x segment size");
         const uint32_t row0  = blockIdx.x * ROWS;
         const uint32_t numKB = (k + COLS - 1) / COLS;
-        // x travels through the ring with its columns of A when it can be copied in 16-byte
-        // pieces; otherwise the compute threads read it from global memory themselves
-        const bool xStaged = (reinterpret_cast<uintptr_t>(x) % 16) == 0;
 
         if(threadIdx.x == 0)
         {
             for(uint32_t s = 0; s < STAGES; ++s)
             {
-                mbar_init(&ctl->full[s], LTHREADS);
-                mbar_init(&ctl->empty[s], CWARPS);
+                mbar_init(&ctl->full[s], 1);
+                mbar_init(&ctl->empty[s], ROWS); // every compute thread arrives for itself
             }
             ctl->abort.flag = 0;
             ctl->abort.code = 0;
             mbar_init_fence();
+            tma_prefetch_descriptor(&tmapA);
+            tma_prefetch_descriptor(&tmapX);
         }
         __syncthreads();
         // the barriers are set up while the previous kernel of the stream drains; A, x and y
@@ -114,67 +116,100 @@ namespace
 
         if(threadIdx.x >= ROWS)
         {
-            // ---- loader warps ----
-            const uint32_t t         = threadIdx.x - ROWS;
-            const uint32_t tilesAddr = smem_addr(tiles);
-            const uint32_t rowsValid = (m - row0) < ROWS ? (m - row0) : ROWS;
-            for(uint32_t kb = 0; kb < numKB; ++kb)
+            // ---- producer: one thread, two TMA loads per tile ----
+            // Rows beyond m and columns beyond k are filled with zeros by the TMA (and still
+            // counted in the bytes the barrier expects).
+            if(elect_one())
             {
-                const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
-                if(!mbar_wait(&ctl->empty[s], ph ^ 1u, &ctl->abort, WAIT_STAGE_EMPTY))
-                    break;
-                const uint32_t h0 = kb * COLS;
-#pragma unroll
-                for(uint32_t i = 0; i < CHUNKS / LTHREADS; ++i)
+                uint32_t kb = 0;
+                for(; kb < numKB; ++kb)
                 {
-                    const uint32_t c    = t + i * LTHREADS;
-                    const uint32_t col  = c / CPC, part = c % CPC;
-                    const uint32_t r    = part * XV; // first row of the chunk inside the block
-                    uint32_t       bytes = 0;
-                    if(h0 + col < k && r < rowsValid)
-                        bytes = (rowsValid - r >= XV) ? 16u : uint32_t((rowsValid - r) * sizeof(T));
-                    T const* src = bytes ? a + size_t(h0 + col) * lda + row0 + r : a;
-                    cpAsync16(tilesAddr + s * SLOT_BYTES + c * 16u, src, bytes);
+                    const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
+                    if(!mbar_wait(&ctl->empty[s], ph ^ 1u, &ctl->abort, WAIT_STAGE_EMPTY))
+                        break;
+                    uint8_t* slot = tiles + s * SLOT_BYTES;
+                    mbar_expect_tx(&ctl->full[s], SLOT_BYTES);
+                    tma_load_2d(slot, &tmapA, &ctl->full[s], int32_t(row0), int32_t(kb * COLS));
+                    tma_load_1d(slot + TILE_BYTES, &tmapX, &ctl->full[s], int32_t(kb * COLS));
                 }
-                if(xStaged && t < XSEG_BYTES / 16u)
+                if(kb < numKB)
                 {
-                    const uint32_t j     = t * XV; // first column of this piece
-                    uint32_t       bytes = 0;
-                    if(h0 + j < k)
-                        bytes = (k - h0 - j >= XV) ? 16u : uint32_t((k - h0 - j) * sizeof(T));
-                    cpAsync16(tilesAddr + s * SLOT_BYTES + TILE_BYTES + t * 16u,
-                              bytes ? x + h0 + j : x, bytes);
+                    // Leaving early: give copies already issued a bounded time to land before
+                    // the block's shared memory is released.
+                    const uint32_t pending = kb < STAGES ? kb : STAGES;
+                    for(uint32_t j = 0; j < pending; ++j)
+                    {
+                        const uint32_t prev = kb - 1 - j;
+                        const long long start = clock64();
+                        while(!mbar_try_wait(&ctl->full[prev % STAGES], (prev / STAGES) & 1u)
+                              && clock64() - start < 2000000ll)
+                        {
+                        }
+                    }
                 }
-                cpAsyncArriveOn(&ctl->full[s]);
             }
-            asm volatile("cp.async.wait_all;" ::: "memory"); // nothing in flight when leaving
         }
         else
         {
             // ---- one row per thread, columns in ascending order ----
-            // The ordered sum is a chain of dependent additions (4 cycles each); the loads of
-            // the NEXT tile are issued before the chain of the current one starts, into a
-            // second set of registers, so that their latency and the barrier wait hide
-            // behind the chain.  (With one register set a tile cost ~600 cycles, which held a
-            // block to ~25 GB/s -- just enough for one GPU's bandwidth with 256 blocks.)
             const uint32_t r   = threadIdx.x;
             T              acc = T(0);
-            // copies tile kb's column values of row r, and its x values, into registers
-            auto fetch = [&](uint32_t kb, T (&av)[COLS], T (&xv)[COLS]) -> bool {
-                const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
-                const uint32_t h0 = kb * COLS;
-                if(!xStaged)
-                {
+            // x values of tile kb (from the slot)
+            auto xValues = [&](uint32_t kb, T (&xv)[COLS]) {
+                const uint32_t    s = kb % STAGES;
+                Vec<T, XV> const* xs
+                    = reinterpret_cast<Vec<T, XV> const*>(tiles + s * SLOT_BYTES + TILE_BYTES);
 #pragma unroll
-                    for(uint32_t j = 0; j < COLS; ++j)
-                        xv[j] = (h0 + j < k) ? __ldg(x + h0 + j) : T(0);
-                }
-                if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
-                    return false;
-                if(xStaged)
+                for(uint32_t j = 0; j < COLS; j += XV)
                 {
-                    Vec<T, XV> const* xs
-                        = reinterpret_cast<Vec<T, XV> const*>(tiles + s * SLOT_BYTES + TILE_BYTES);
+                    const Vec<T, XV> q = xs[j / XV]; // same address in every lane: broadcast
+#pragma unroll
+                    for(uint32_t e = 0; e < XV; ++e)
+                        xv[j + e] = q.v[e];
+                }
+            };
+            if constexpr(sizeof(T) == 4)
+            {
+                // The ordered sum is a chain of dependent additions, 4 cycles each: 128 cycles
+                // per tile that nothing can shorten.  Everything else a tile needs -- 32
+                // shared-memory loads of A, 8 of x, 32 multiplications, a barrier poll and a
+                // barrier arrival -- is taken off that chain by working on three tiles at
+                // once: while the products of tile t are added, the values of tile t + 1
+                // (already in registers) are multiplied and tile t + 2 is polled for and
+                // loaded.  A warp issues in order, so what matters is where each result is
+                // first USED: the poll of tile t + 2 is issued before the chain and its outcome
+                // tested after it, the loaded values are first touched one step later.  Written
+                // as one unrolled loop body, additions and multiplications interleave.
+                // (Fetching a whole tile and then adding it cost ~550 cycles per tile, most of
+                // them latency of the barrier poll and its dependent branch, not arithmetic: a
+                // block streamed at 25 GB/s whatever the grid, and a 2048-row shard took as
+                // long as the whole matrix.)
+                // A slot goes back to the producer once its values have been multiplied.
+                // The last tile may be partial: its columns beyond k must not enter the sum
+                // (adding +0 could turn a -0 into +0), so it takes a guarded path of its own.
+                const uint32_t numFull = k / COLS; // tiles made of COLS valid columns
+                bool           ok      = true;
+                // Ring positions are carried along instead of being derived from the tile
+                // number each time (a division by a slot count that is no power of two is a
+                // chain of dependent integer operations, and this warp issues in order).
+                struct RingPos
+                {
+                    uint32_t slot, phase;
+                    __device__ void advance()
+                    {
+                        if(++slot == STAGES)
+                        {
+                            slot = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                };
+                RingPos toLoad{0u, 0u}, toRelease{0u, 0u};
+                // raw values of the tile in slot `s` (A and x) -> registers
+                auto loadTile = [&](uint32_t s, T (&av)[COLS], T (&xv)[COLS]) {
+                    T const*          tile = reinterpret_cast<T const*>(tiles + s * SLOT_BYTES);
+                    Vec<T, XV> const* xs   = reinterpret_cast<Vec<T, XV> const*>(
+                        tiles + s * SLOT_BYTES + TILE_BYTES);
 #pragma unroll
                     for(uint32_t j = 0; j < COLS; j += XV)
                     {
@@ -183,53 +218,178 @@ namespace
                         for(uint32_t e = 0; e < XV; ++e)
                             xv[j + e] = q.v[e];
                     }
-                }
-                T const* tile = reinterpret_cast<T const*>(tiles + s * SLOT_BYTES);
 #pragma unroll
-                for(uint32_t j = 0; j < COLS; ++j)
-                    av[j] = tile[j * ROWS + r];
-                return true;
-            };
-            // the ordered sum over one tile, then the slot goes back to the loaders (its
-            // values have been consumed, so the loads are certainly complete).  Columns
-            // beyond k hold zeros and must not enter the sum (adding +0 could turn a -0
-            // into +0).
-            auto consume = [&](uint32_t kb, T const (&av)[COLS], T const (&xv)[COLS]) {
-                const uint32_t h0    = kb * COLS;
-                const uint32_t valid = (k - h0) < COLS ? (k - h0) : COLS;
+                    for(uint32_t j = 0; j < COLS; ++j)
+                        av[j] = tile[j * ROWS + r];
+                };
+                // Every lane arrives for itself (the barrier counts ROWS arrivals): a lane's
+                // arrival follows its own reads of the slot in program order, so no warp-wide
+                // synchronisation -- another instruction with a branch's latency -- is needed.
+                auto releaseSlot = [&]() {
+                    mbar_arrive(&ctl->empty[toRelease.slot]);
+                    toRelease.advance();
+                };
+                // One steady-state step for tile t: adds the products `pCur` of tile t;
+                // multiplies the raw values of tile t + 1 into `pNext` and releases that tile's
+                // slot; loads tile t + 2 into `aNew`, `xNew`; polls for a tile four further on.
+                // The loads and the poll sit inside the unrolled loop, between additions, so that
+                // their issue slots and latencies fall into the gaps of the 4-cycle chain; what
+                // they return is first used one step (the poll: one trip of four steps) later.
+                // Branches are what a lone warp cannot hide (~40 cycles each, measured), so a
+                // step has none: arrival of the four tiles a trip loads is established once,
+                // before the trip, from the polls of the trip before.
+                RingPos toPoll{0u, 0u};
+                auto    step = [&](T const (&pCur)[COLS], T (&pNext)[COLS], T const (&aNext)[COLS],
+                                T const (&xNext)[COLS], T (&aNew)[COLS], T (&xNew)[COLS],
+                                bool& allArrived) {
+                    T const*          tile = reinterpret_cast<T const*>(tiles + toLoad.slot * SLOT_BYTES);
+                    Vec<T, XV> const* xs   = reinterpret_cast<Vec<T, XV> const*>(
+                        tiles + toLoad.slot * SLOT_BYTES + TILE_BYTES);
+                    toLoad.advance();
 #pragma unroll
-                for(uint32_t j = 0; j < COLS; ++j)
-                    if(j < valid)
-                        acc = addRn(acc, mulRn(av[j], xv[j]));
-                __syncwarp();
-                if((threadIdx.x & 31u) == 0u)
-                    mbar_arrive(&ctl->empty[kb % STAGES]); // one arrival per warp
-            };
-            if constexpr(sizeof(T) == 4)
-            {
-                T    avA[COLS], xvA[COLS], avB[COLS], xvB[COLS];
-                bool ok = numKB == 0u || fetch(0, avA, xvA);
-                for(uint32_t kb = 0; ok && kb < numKB; kb += 2)
+                    for(uint32_t j = 0; j < COLS; ++j)
+                    {
+                        acc      = addRn(acc, pCur[j]);
+                        pNext[j] = mulRn(aNext[j], xNext[j]);
+                        aNew[j]  = tile[j * ROWS + r];
+                        if(j % XV == 0u)
+                        {
+                            const Vec<T, XV> q = xs[j / XV];
+#pragma unroll
+                            for(uint32_t e = 0; e < XV; ++e)
+                                xNew[j + e] = q.v[e];
+                        }
+                        if(j == COLS / 4u)
+                            allArrived
+                                = mbar_try_wait(&ctl->full[toPoll.slot], toPoll.phase) && allArrived;
+                    }
+                    toPoll.advance();
+                    releaseSlot(); // tile t + 1: its values have been multiplied
+                };
+                T pA[COLS], pB[COLS], rA[COLS], rB[COLS], xA[COLS], xB[COLS];
+                if(numFull > 0u)
                 {
-                    const bool has1 = kb + 1 < numKB, has2 = kb + 2 < numKB;
-                    if(has1 && !fetch(kb + 1, avB, xvB))
-                        break;
-                    consume(kb, avA, xvA);
-                    if(has2 && !fetch(kb + 2, avA, xvA))
-                        break;
-                    if(has1)
-                        consume(kb + 1, avB, xvB);
+                    // prologue: tile 0 loaded and multiplied, tile 1 loaded
+                    ok = mbar_wait(&ctl->full[0], 0u, &ctl->abort, WAIT_STAGE_FULL);
+                    if(ok)
+                    {
+                        loadTile(0u, rA, xA);
+                        toLoad.advance();
+#pragma unroll
+                        for(uint32_t j = 0; j < COLS; ++j)
+                            pA[j] = mulRn(rA[j], xA[j]);
+                        releaseSlot();
+                        if(numFull > 1u)
+                        {
+                            ok = mbar_wait(&ctl->full[1], 0u, &ctl->abort, WAIT_STAGE_FULL);
+                            if(ok)
+                            {
+                                loadTile(1u, rB, xB);
+                                toLoad.advance();
+                            }
+                        }
+                    }
+                    // steady state, four tiles per trip (the register sets swap roles).  A trip
+                    // starting at tile t loads tiles t + 2 .. t + 5 and polls t + 6 .. t + 9.
+                    uint32_t t = 0;
+                    toPoll     = toLoad;
+                    for(uint32_t i = 0; i < 4u; ++i)
+                        toPoll.advance();
+                    bool arrivedAll = false;
+                    for(; ok && t + 9 < numFull; t += 4)
+                    {
+                        if(!arrivedAll)
+                        {
+                            // first trip, or a poll came back early: wait for the four tiles
+                            RingPos w = toLoad;
+                            for(uint32_t i = 0; ok && i < 4u; ++i)
+                            {
+                                ok = mbar_wait(&ctl->full[w.slot], w.phase, &ctl->abort,
+                                               WAIT_STAGE_FULL);
+                                w.advance();
+                            }
+                            if(!ok)
+                                break;
+                        }
+                        bool all = true;
+                        step(pA, pB, rB, xB, rA, xA, all);
+                        step(pB, pA, rA, xA, rB, xB, all);
+                        step(pA, pB, rB, xB, rA, xA, all);
+                        step(pB, pA, rA, xA, rB, xB, all);
+                        arrivedAll = all;
+                    }
+                    // The last full tiles, one simple step each: add tile u; multiply tile u + 1
+                    // if there is one; wait for and load tile u + 2 if there is one.  (t is
+                    // even here; toLoad names tile t + 2.)
+                    for(uint32_t u = t; ok && u < numFull; ++u)
+                    {
+                        const bool even = ((u & 1u) == 0u);
+                        T const(&pCur)[COLS]  = even ? pA : pB;
+                        T(&pNext)[COLS]       = even ? pB : pA;
+                        T(&aNext)[COLS]       = even ? rB : rA;
+                        T(&xNext)[COLS]       = even ? xB : xA;
+                        T(&aNew)[COLS]        = even ? rA : rB;
+                        T(&xNew)[COLS]        = even ? xA : xB;
+                        const bool has1 = u + 1 < numFull, has2 = u + 2 < numFull;
+#pragma unroll
+                        for(uint32_t j = 0; j < COLS; ++j)
+                        {
+                            acc = addRn(acc, pCur[j]);
+                            if(has1)
+                                pNext[j] = mulRn(aNext[j], xNext[j]);
+                        }
+                        if(has1)
+                            releaseSlot();
+                        if(has2)
+                        {
+                            ok = mbar_wait(&ctl->full[toLoad.slot], toLoad.phase, &ctl->abort,
+                                           WAIT_STAGE_FULL);
+                            if(ok)
+                            {
+                                loadTile(toLoad.slot, aNew, xNew);
+                                toLoad.advance();
+                            }
+                        }
+                    }
+                }
+                if(ok && numFull < numKB)
+                {
+                    // the partial last tile (toLoad names its slot: it follows the full ones)
+                    const uint32_t valid = k - numFull * COLS;
+                    T              av[COLS], xv[COLS];
+                    if(mbar_wait(&ctl->full[toLoad.slot], toLoad.phase, &ctl->abort,
+                                 WAIT_STAGE_FULL))
+                    {
+                        loadTile(toLoad.slot, av, xv);
+#pragma unroll
+                        for(uint32_t j = 0; j < COLS; ++j)
+                            if(j < valid)
+                                acc = addRn(acc, mulRn(av[j], xv[j]));
+                        releaseSlot();
+                    }
                 }
             }
             else
             {
-                // 64-bit elements: two register sets would not fit; one tile at a time
+                // 64-bit elements: one tile at a time (a second register set would not fit)
                 T av[COLS], xv[COLS];
                 for(uint32_t kb = 0; kb < numKB; ++kb)
                 {
-                    if(!fetch(kb, av, xv))
+                    const uint32_t s = kb % STAGES, ph = (kb / STAGES) & 1u;
+                    if(!mbar_wait(&ctl->full[s], ph, &ctl->abort, WAIT_STAGE_FULL))
                         break;
-                    consume(kb, av, xv);
+                    xValues(kb, xv);
+                    T const* tile = reinterpret_cast<T const*>(tiles + s * SLOT_BYTES);
+#pragma unroll
+                    for(uint32_t j = 0; j < COLS; ++j)
+                        av[j] = tile[j * ROWS + r];
+                    const uint32_t h0    = kb * COLS;
+                    const uint32_t valid = (k - h0) < COLS ? (k - h0) : COLS;
+#pragma unroll
+                    for(uint32_t j = 0; j < COLS; ++j)
+                        if(j < valid)
+                            acc = addRn(acc, mulRn(av[j], xv[j]));
+                    mbar_arrive(&ctl->empty[s]);
                 }
             }
             if(row0 + r < m && ctl->abort.flag == 0u)
@@ -258,12 +418,64 @@ namespace
         yOut[i] = addRn(mulRn(alpha, acc), mulRn(beta, yIn[i]));
     }
 
+    template <typename T, uint32_t ROWS, uint32_t STAGES>
+    int launchStream(uint32_t m, uint32_t k, T const* a, T const* x, T const* yIn, T* yOut, T alpha,
+                     T beta, uint32_t lda, cudaStream_t stream)
+    {
+        using G = Geometry<T, ROWS, STAGES>;
+        b200wmma::EncodeFn encode = b200wmma::tensorMapEncoder();
+        if(!encode)
+            return B200WMMA_ERR_CUDA;
+        const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT64;
+        // A, column-major: m contiguous rows per column, k columns lda apart; a tile is ROWS
+        // rows x COLS columns and lands in shared memory column after column
+        CUtensorMap mapA, mapX;
+        {
+            cuuint64_t dims[2]    = {m, k};
+            cuuint64_t strides[1] = {cuuint64_t(lda) * sizeof(T)};
+            cuuint32_t box[2]     = {ROWS, G::COLS};
+            cuuint32_t estr[2]    = {1, 1};
+            if(encode(&mapA, dt, 2, const_cast<T*>(a), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+               != CUDA_SUCCESS)
+                return B200WMMA_ERR_CUDA;
+        }
+        {
+            cuuint64_t dims[1]    = {k};
+            cuuint64_t strides[1] = {0}; // a one-dimensional map has no strides; never read
+            cuuint32_t box[1]     = {G::COLS};
+            cuuint32_t estr[1]    = {1};
+            if(encode(&mapX, dt, 1, const_cast<T*>(x), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                      CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+               != CUDA_SUCCESS)
+                return B200WMMA_ERR_CUDA;
+        }
+        auto        kernel = gemvStreamKernel<T, ROWS, STAGES>;
+        static bool attrDone[64] = {};
+        int         dev          = 0;
+        B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
+        if(dev < 0 || dev >= 64 || !attrDone[dev])
+        {
+            B200WMMA_CUDA_TRY(cudaFuncSetAttribute(
+                kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(G::SMEM_BYTES)));
+            if(dev >= 0 && dev < 64)
+                attrDone[dev] = true;
+        }
+        return b200wmma::cudaToStatus(b200wmma::launchOverlapped(
+            kernel, dim3((m + ROWS - 1) / ROWS), dim3(G::THREADS), G::SMEM_BYTES, stream, mapA,
+            mapX, m, k, yIn, yOut, alpha, beta, b200wmma::deviceStatusWord()));
+    }
+
     template <typename T>
     int run(uint32_t m, uint32_t k, T const* a, T const* x, T const* yIn, T* yOut, T alpha, T beta,
             uint32_t lda, cudaStream_t stream)
     {
-        // 16-byte asynchronous copies need 16-byte aligned columns
+        // TMA needs 16-byte aligned bases and column stride
         const bool streamOK = (reinterpret_cast<uintptr_t>(a) % 16 == 0)
+                              && (reinterpret_cast<uintptr_t>(x) % 16 == 0)
                               && ((size_t(lda) * sizeof(T)) % 16 == 0);
         if(!streamOK)
         {
@@ -271,20 +483,23 @@ namespace
                                                                   beta, lda);
             return b200wmma::cudaToStatus(cudaGetLastError());
         }
-        static bool attrDone[64] = {};
-        int         dev          = 0;
-        B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
-        if(dev < 0 || dev >= 64 || !attrDone[dev])
-        {
-            B200WMMA_CUDA_TRY(cudaFuncSetAttribute(gemvStreamKernel<T>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   int(SMEM_BYTES)));
-            if(dev >= 0 && dev < 64)
-                attrDone[dev] = true;
-        }
-        return b200wmma::cudaToStatus(b200wmma::launchOverlapped(
-            gemvStreamKernel<T>, dim3((m + ROWS - 1) / ROWS), dim3(THREADS), SMEM_BYTES, stream, m,
-            k, a, x, yIn, yOut, alpha, beta, lda, b200wmma::deviceStatusWord()));
+        // 64 rows per block fill a B200 from 148 x 2 x 64 = 18944 rows up; with fewer rows
+        // than half of that, 32-row blocks put twice as many SMs to work (a row's ordered sum
+        // takes the same time either way, so the launch takes as long as one block does).
+        // B200WMMA_GEMV_ROWS=32|64 forces one form (tuning and comparison only).
+        static const uint32_t rowsEnv = [] {
+            const char* e = getenv("B200WMMA_GEMV_ROWS");
+            return e ? uint32_t(atoi(e)) : 0u;
+        }();
+        const int sms = b200wmma::smCount();
+        if(sms <= 0)
+            return B200WMMA_ERR_CUDA;
+        bool narrow = (m + 63u) / 64u < uint32_t(sms);
+        if(rowsEnv == 32u || rowsEnv == 64u)
+            narrow = rowsEnv == 32u;
+        if(narrow)
+            return launchStream<T, 32, 24>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
+        return launchStream<T, 64, 12>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
     }
 } // namespace
 

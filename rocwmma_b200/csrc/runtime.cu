@@ -41,6 +41,23 @@ namespace b200wmma
         }
     } // namespace
 
+    EncodeFn tensorMapEncoder()
+    {
+        static EncodeFn       fn = nullptr;
+        static std::once_flag once;
+        std::call_once(once, [] {
+            void*                           sym = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q)
+                   == cudaSuccess
+               && q == cudaDriverEntryPointSuccess)
+                fn = reinterpret_cast<EncodeFn>(sym);
+            else
+                (void)cudaGetLastError();
+        });
+        return fn;
+    }
+
     uint32_t* deviceStatusWord()
     {
         std::lock_guard<std::mutex> lock(g_mutex);

@@ -2,11 +2,20 @@
 #ifndef ROCWMMA_B200_CSRC_RUNTIME_CUH
 #define ROCWMMA_B200_CSRC_RUNTIME_CUH
 #include <cstddef>
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <mutex>
 
 namespace b200wmma
 {
+    // cuTensorMapEncodeTiled, looked up once through the runtime (no link-time dependency on
+    // the driver library).  nullptr when the driver does not offer it.
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    EncodeFn tensorMapEncoder();
+
     // A device buffer of at least `bytes`, kept per device and grown on demand
     // (contents are not preserved across growth).  nullptr on failure.
     void* deviceScratch(size_t bytes);
