@@ -8,8 +8,11 @@
 //
 //   * a fragment is cut into "atoms": 16 x KA tiles of A, KA x 8 tiles of B,
 //     16 x 8 tiles of the accumulator, where KA is the K extent of one
-//     mma.sync (4 for 64-bit, 8 for 32-bit, 16 for 16-bit, 32 for 8-bit types;
-//     16 for 8-bit types when BlockK is not a multiple of 32);
+//     mma.sync (4 for 64-bit, 8 for 32-bit, 16 for 16-bit, 32 for 8-bit types),
+//     or of its half-depth form when BlockK is not a multiple of that extent
+//     (4 for 32-bit, 8 for 16-bit, 16 for 8-bit types): rocWMMA's 32 x 32 blocks
+//     go down to BlockK = 8 for 16-bit and 16 for 8-bit inputs
+//     (test/gemm/gemm_predicates_base.hpp:137-209);
 //   * inside an atom a lane (g = lane / 4, t = lane % 4) owns "units" of
 //     consecutive elements: one 32-bit register worth of A or B elements along
 //     K, or two neighbouring accumulator columns;
@@ -52,8 +55,8 @@ namespace rocwmma
         ROCWMMA_HOST_DEVICE constexpr uint32_t kAtom()
         {
             return sizeof(DataT) == 8   ? 4u
-                   : sizeof(DataT) == 4 ? 8u
-                   : sizeof(DataT) == 2 ? 16u
+                   : sizeof(DataT) == 4 ? ((BlockK % 8u == 0u) ? 8u : 4u)
+                   : sizeof(DataT) == 2 ? ((BlockK % 16u == 0u) ? 16u : 8u)
                                         : ((BlockK % 32u == 0u) ? 32u : 16u);
         }
 
@@ -101,8 +104,9 @@ namespace rocwmma
             static_assert(IsB || BlockM % 16u == 0u, "BlockM must be a multiple of 16");
             static_assert(IsA || BlockN % 8u == 0u, "BlockN must be a multiple of 8");
             static_assert(IsAcc || BlockK % KA == 0u,
-                          "BlockK must be a multiple of the K extent of one tensor-core "
-                          "instruction (4 for f64, 8 for f32/xf32, 16 for 16- and 8-bit types)");
+                          "BlockK must be a multiple of the K extent of the shallowest "
+                          "tensor-core instruction (4 for f64, f32 and xf32, 8 for 16-bit, 16 for "
+                          "8-bit types)");
             static_assert(Size * 32u == Height * Width, "fragment does not tile its matrix");
 
             // (row, col) of the first element of unit `u` for lane `lane`.

@@ -110,6 +110,47 @@ namespace rocwmma
                            "r"(c[0]), "r"(c[1]));
         }
 
+        // ---- half-depth forms, for fragments whose BlockK is below the K extent above ----
+        // f16 / bf16, m16n8k8: two A registers (rows g and g + 8), one B register
+        ROCWMMA_DEVICE inline void mma_atom_k8(float (&d)[4], uint32_t const (&a)[2],
+                                               uint32_t const (&b)[1], float const (&c)[4], __half)
+        {
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+                         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[0]), "f"(c[0]), "f"(c[1]), "f"(c[2]),
+                           "f"(c[3]));
+        }
+        ROCWMMA_DEVICE inline void mma_atom_k8(float (&d)[4], uint32_t const (&a)[2],
+                                               uint32_t const (&b)[1], float const (&c)[4],
+                                               __nv_bfloat16)
+        {
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+                         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[0]), "f"(c[0]), "f"(c[1]), "f"(c[2]),
+                           "f"(c[3]));
+        }
+        ROCWMMA_DEVICE inline void mma_atom_f16acc_k8(uint32_t (&d)[2], uint32_t const (&a)[2],
+                                                      uint32_t const (&b)[1],
+                                                      uint32_t const (&c)[2])
+        {
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f16.f16.f16.f16 "
+                         "{%0,%1}, {%2,%3}, {%4}, {%5,%6};"
+                         : "=r"(d[0]), "=r"(d[1])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[0]), "r"(c[0]), "r"(c[1]));
+        }
+        // tf32, m16n8k4: two A registers, one B register
+        ROCWMMA_DEVICE inline void mma_atom_tf32_k4(float (&d)[4], uint32_t const (&a)[2],
+                                                    uint32_t const (&b)[1], float const (&c)[4])
+        {
+            asm volatile("mma.sync.aligned.m16n8k4.row.col.f32.tf32.tf32.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+                         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[0]), "f"(c[0]), "f"(c[1]), "f"(c[2]),
+                           "f"(c[3]));
+        }
+
         // fp32 -> tf32 with round-to-nearest (ties away), as a bit pattern.
         ROCWMMA_DEVICE inline uint32_t to_tf32(float f)
         {

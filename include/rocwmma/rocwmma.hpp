@@ -296,12 +296,21 @@ namespace rocwmma
                     ROCWMMA_UNROLL
                     for(uint32_t kt = 0; kt < KT; ++kt)
                     {
-                        const uint32_t ai    = (mt * KT + kt) * RA;
-                        const uint32_t bi    = (nt * KT + kt) * RB;
-                        const uint32_t ar[4] = {a.mStorage[ai], a.mStorage[ai + 1],
-                                                a.mStorage[ai + 2], a.mStorage[ai + 3]};
-                        const uint32_t br[2] = {b.mStorage[bi], b.mStorage[bi + 1]};
-                        detail::mma_atom_f16acc(acc, ar, br, acc);
+                        const uint32_t ai = (mt * KT + kt) * RA;
+                        const uint32_t bi = (nt * KT + kt) * RB;
+                        if constexpr(GeomA::KA == 16u)
+                        {
+                            const uint32_t ar[4] = {a.mStorage[ai], a.mStorage[ai + 1],
+                                                    a.mStorage[ai + 2], a.mStorage[ai + 3]};
+                            const uint32_t br[2] = {b.mStorage[bi], b.mStorage[bi + 1]};
+                            detail::mma_atom_f16acc(acc, ar, br, acc);
+                        }
+                        else // K extent 8
+                        {
+                            const uint32_t ar[2] = {a.mStorage[ai], a.mStorage[ai + 1]};
+                            const uint32_t br[1] = {b.mStorage[bi]};
+                            detail::mma_atom_f16acc_k8(acc, ar, br, acc);
+                        }
                     }
                     d.mStorage[ci / 2u]      = acc[0];
                     d.mStorage[ci / 2u + 1u] = acc[1];
@@ -317,12 +326,18 @@ namespace rocwmma
                     {
                         const uint32_t ai = (mt * KT + kt) * RA;
                         const uint32_t bi = (nt * KT + kt) * RB;
-                        if constexpr(Is16)
+                        if constexpr(Is16 && GeomA::KA == 16u)
                         {
                             const uint32_t ar[4] = {a.mStorage[ai], a.mStorage[ai + 1],
                                                     a.mStorage[ai + 2], a.mStorage[ai + 3]};
                             const uint32_t br[2] = {b.mStorage[bi], b.mStorage[bi + 1]};
                             detail::mma_atom(acc, ar, br, acc, InT{});
+                        }
+                        else if constexpr(Is16) // K extent 8
+                        {
+                            const uint32_t ar[2] = {a.mStorage[ai], a.mStorage[ai + 1]};
+                            const uint32_t br[1] = {b.mStorage[bi]};
+                            detail::mma_atom_k8(acc, ar, br, acc, InT{});
                         }
                         else if constexpr(IsFp8 && GeomA::KA == 32u)
                         {
@@ -345,6 +360,32 @@ namespace rocwmma
                             const uint32_t br[2] = {detail::fp8x2_to_half2<InT>(b.mStorage[bi], 0),
                                                     detail::fp8x2_to_half2<InT>(b.mStorage[bi], 1)};
                             detail::mma_atom(acc, ar, br, acc, __half{});
+                        }
+                        else if constexpr(IsXF32 && GeomA::KA == 4u)
+                        {
+                            const uint32_t ar[2]
+                                = {detail::f2u(a.x[ai].data), detail::f2u(a.x[ai + 1].data)};
+                            const uint32_t br[1] = {detail::f2u(b.x[bi].data)};
+                            detail::mma_atom_tf32_k4(acc, ar, br, acc);
+                        }
+                        else if constexpr(IsF32 && GeomA::KA == 4u)
+                        {
+                            uint32_t ah[2], al[2], bh[1], bl[1];
+                            ROCWMMA_UNROLL
+                            for(uint32_t r = 0; r < 2; ++r)
+                            {
+                                const float v = a.x[ai + r];
+                                ah[r]         = detail::to_tf32(v);
+                                al[r]         = detail::to_tf32(v - __uint_as_float(ah[r]));
+                            }
+                            {
+                                const float v = b.x[bi];
+                                bh[0]         = detail::to_tf32(v);
+                                bl[0]         = detail::to_tf32(v - __uint_as_float(bh[0]));
+                            }
+                            detail::mma_atom_tf32_k4(acc, al, bh, acc);
+                            detail::mma_atom_tf32_k4(acc, ah, bl, acc);
+                            detail::mma_atom_tf32_k4(acc, ah, bh, acc);
                         }
                         else if constexpr(IsXF32)
                         {

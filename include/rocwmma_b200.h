@@ -95,8 +95,11 @@ B200WMMA_API int b200wmma_gemm_simple(int in_dtype, int out_dtype, uint32_t m, u
  * (accumulator fragment rounded to bf16 after every BlockK step, as rocWMMA does for
  * 16-bit compute types, internal/mfma_impl.hpp:101-156), I8/I8/I32, E5M2/F32/F32.
  * block_k is the K extent of the A and B fragments: 0 for the usual one (16; 32 for 8-bit
- * types in 32 x 32 tiles), else 16, 32 or 64 for 8- and 16-bit types (128 too with
- * 16 x 16 tiles), 8 or 32 for F32 / XF32, 4 or 8 for F64; k must be a multiple of it.
+ * types in 32 x 32 tiles), else 8 (16-bit types only: the reference's minimum for 32 x 32
+ * blocks, test/gemm/gemm_predicates_base.hpp:137-209), 16, 32 or 64 for 8- and 16-bit types
+ * (128 too with 16 x 16 tiles), 4, 8 or 32 for F32 / XF32, 4 or 8 for F64; k must be a
+ * multiple of it.  Fragments whose BlockK is below the K extent of the full-depth tensor-core
+ * instruction run on its half-depth form (m16n8k8 for 16-bit, m16n8k4 for tf32).
  */
 B200WMMA_API int b200wmma_gemm_simple_ex(int in_dtype, int out_dtype, int compute_dtype, uint32_t m,
                             uint32_t n, uint32_t k, const void* a, const void* b, const void* c,

@@ -1,9 +1,9 @@
 // The one-tile-per-warp GEMM with fragment K extents other than each type's usual one
 // (the reference runs BlockK from the per-type minimum up to 128,
 // test/gemm/gemm_common_test_params.hpp:51-121 and
-// docs/api-reference/api-reference-guide.rst:80-153).  Built here: 32 and 64 for 8- and
-// 16-bit types (8-bit 32x32 tiles: 16 and 64), 128 as well for their 16x16 tiles, 8 and 32
-// for float32_t / xfloat32_t, 4 and 8 for float64_t.  A translation unit of its own only to keep compile times apart.
+// docs/api-reference/api-reference-guide.rst:80-153).  Built here: 8 (16-bit types: the
+// reference's minimum for 32x32 blocks), 16, 32 and 64 for 8- and 16-bit types, 128 as well
+// for their 16x16 tiles, 4, 8 and 32 for float32_t / xfloat32_t, 4 and 8 for float64_t.  A translation unit of its own only to keep compile times apart.
 #include "simple_gemm.cuh"
 
 namespace b200wmma
@@ -27,6 +27,8 @@ namespace simple
             }
             else if constexpr(sizeof(InT) == 4)
             {
+                if(block_k == 4)
+                    return launchTile<InT, OutT, CompT, BLOCK, BLOCK, 4>(g);
                 if(block_k == 8)
                     return launchTile<InT, OutT, CompT, BLOCK, BLOCK, 8>(g);
                 if(block_k == 32)
@@ -34,6 +36,11 @@ namespace simple
             }
             else
             {
+                if constexpr(sizeof(InT) == 2)
+                {
+                    if(block_k == 8)
+                        return launchTile<InT, OutT, CompT, BLOCK, BLOCK, 8>(g);
+                }
                 if(block_k == 16)
                     return launchTile<InT, OutT, CompT, BLOCK, BLOCK, 16>(g);
                 if(block_k == 32)

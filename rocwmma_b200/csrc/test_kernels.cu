@@ -45,8 +45,11 @@ namespace
         using Frag = fragment<MatrixT, BM, BN, BK, DataT, Layout>;
         Frag           frag;
         const uint32_t h = Frag::height(), w = Frag::width();
-        const uint32_t warpInBlock = threadIdx.x / Constants::AMDGCN_WAVE_SIZE;
-        const uint32_t warpsPerBlk = blockDim.x / Constants::AMDGCN_WAVE_SIZE;
+        // thread blocks are (warps_x * 32, warps_y) as in the reference's unit tests
+        // (test/unit/unit_test_params.hpp:159-172); warps are numbered x first
+        const uint32_t warpInBlock
+            = (threadIdx.y * blockDim.x + threadIdx.x) / Constants::AMDGCN_WAVE_SIZE;
+        const uint32_t warpsPerBlk = blockDim.x * blockDim.y / Constants::AMDGCN_WAVE_SIZE;
         if(mode > 0)
         {
             const uint32_t tile = blockIdx.x;
@@ -93,9 +96,12 @@ namespace
     int launchRT(void const* in, void* out, uint32_t ld, uint32_t tilesR, uint32_t tilesC, int mode,
                  int warps, cudaStream_t s)
     {
-        const uint32_t tiles  = tilesR * tilesC;
-        const uint32_t blocks = mode > 0 ? tiles : (tiles + warps - 1) / warps;
-        roundTrip<MatrixT, BM, BN, BK, DataT, Layout><<<blocks, warps * 32, 0, s>>>(
+        // `warps` packs the thread block: warps_x + 16 * warps_y (warps_y = 0 means 1)
+        const uint32_t wx = uint32_t(warps) & 15u, wy = (uint32_t(warps) >> 4) ? (uint32_t(warps) >> 4) : 1u;
+        const uint32_t perBlock = wx * wy;
+        const uint32_t tiles    = tilesR * tilesC;
+        const uint32_t blocks   = mode > 0 ? tiles : (tiles + perBlock - 1) / perBlock;
+        roundTrip<MatrixT, BM, BN, BK, DataT, Layout><<<blocks, dim3(wx * 32, wy), 0, s>>>(
             static_cast<DataT const*>(in), static_cast<DataT*>(out), ld, tilesR, tilesC, mode);
         return cudaGetLastError() == cudaSuccess ? 0 : -4;
     }
@@ -130,6 +136,37 @@ namespace
         return -1;
     }
 
+    // The reference's unit tests run over (first, second) block-size pairs
+    // (test/unit/unit_test_params.hpp:85-110): matrix_a is first x second (BlockM x BlockK),
+    // matrix_b second x first (BlockK x BlockN), the accumulator first x second
+    // (BlockM x BlockN).  Pairs a type cannot hold (8-bit operands need BlockK >= 16) return -2.
+    template <uint32_t X, uint32_t Y, typename DataT>
+    int byPair(int matrix, int layout, void const* in, void* out, uint32_t ld, uint32_t tr,
+               uint32_t tc, int mode, int warps, cudaStream_t s)
+    {
+        if(matrix == 2)
+        {
+            if constexpr(Y % 8u == 0u)
+                return byLayout<accumulator, X, Y, 16, DataT>(layout, in, out, ld, tr, tc, mode,
+                                                              warps, s);
+            else
+                return -2;
+        }
+        constexpr uint32_t minK = sizeof(DataT) == 1 ? 16u : sizeof(DataT) == 2 ? 8u : 4u;
+        if constexpr(Y % minK == 0u)
+        {
+            if(matrix == 0)
+                return byLayout<matrix_a, X, 16, Y, DataT>(layout, in, out, ld, tr, tc, mode, warps,
+                                                           s);
+            if(matrix == 1)
+                return byLayout<matrix_b, 16, X, Y, DataT>(layout, in, out, ld, tr, tc, mode, warps,
+                                                           s);
+            return -1;
+        }
+        else
+            return -2;
+    }
+
     template <typename DataT>
     int byShape(int shape, int matrix, int layout, void const* in, void* out, uint32_t ld,
                 uint32_t tr, uint32_t tc, int mode, int warps, cudaStream_t s)
@@ -142,6 +179,25 @@ namespace
             return byMatrix<32, 32, 32, DataT>(matrix, layout, in, out, ld, tr, tc, mode, warps, s);
         case 2:
             return byMatrix<64, 16, 32, DataT>(matrix, layout, in, out, ld, tr, tc, mode, warps, s);
+            // 100 + i: the i-th (first, second) pair of the reference's unit-test grid
+#define B200WMMA_PAIR(ID, X, Y) \
+    case 100 + ID:              \
+        return byPair<X, Y, DataT>(matrix, layout, in, out, ld, tr, tc, mode, warps, s);
+            B200WMMA_PAIR(0, 16, 16)
+            B200WMMA_PAIR(1, 16, 32)
+            B200WMMA_PAIR(2, 16, 64)
+            B200WMMA_PAIR(3, 32, 8)
+            B200WMMA_PAIR(4, 32, 16)
+            B200WMMA_PAIR(5, 32, 32)
+            B200WMMA_PAIR(6, 32, 64)
+            B200WMMA_PAIR(7, 64, 8)
+            B200WMMA_PAIR(8, 64, 16)
+            B200WMMA_PAIR(9, 64, 32)
+            B200WMMA_PAIR(10, 64, 64)
+            B200WMMA_PAIR(11, 128, 8)
+            B200WMMA_PAIR(12, 128, 16)
+            B200WMMA_PAIR(13, 256, 8)
+#undef B200WMMA_PAIR
         }
         return -1;
     }
@@ -343,14 +399,19 @@ TEST_API int b200wmma_test_bounded_wait(uint32_t* out4, long long limit_cycles, 
 }
 
 // elem_bytes 1/2/4/8 -> int8_t / float16_t / float32_t / float64_t; matrix 0/1/2 = a/b/acc;
-// layout 0 row, 1 col; shape 0 = 16x16x16, 1 = 32x32x32, 2 = 64x16x32; mode see roundTrip.
+// layout 0 row, 1 col; shape 0 = 16x16x16, 1 = 32x32x32, 2 = 64x16x32, 100 + i = the i-th block-size
+// pair of the reference's unit-test grid (see byPair); mode see roundTrip; warps = warps_x +
+// 16 * warps_y of the (warps_x * 32, warps_y) thread block.  -2: the type cannot hold the pair.
 TEST_API int b200wmma_test_round_trip(int elem_bytes, int matrix, int layout, int shape,
                                       const void* in, void* out, uint32_t ld, uint32_t tiles_r,
                                       uint32_t tiles_c, int mode, int warps, void* stream)
 {
     auto s = static_cast<cudaStream_t>(stream);
-    if(warps < 1 || warps > 8)
-        return -1;
+    {
+        const int wx = warps & 15, wy = (warps >> 4) ? (warps >> 4) : 1;
+        if(wx < 1 || wx * wy > 8)
+            return -1;
+    }
     switch(elem_bytes)
     {
     case 1:

@@ -14,6 +14,14 @@ import torch
 from rocwmma_b200 import _lib as L
 
 SHAPES = {0: (16, 16, 16), 1: (32, 32, 32), 2: (64, 16, 32)}
+# The reference's unit-test grid of (first, second) block sizes (test/unit/unit_test_params.hpp:
+# 85-110; 128 and 256 are its extended sizes, kept here where a lane's share still fits the
+# register file): matrix_a is first x second (BlockM x BlockK), matrix_b second x first
+# (BlockK x BlockN), the accumulator first x second (BlockM x BlockN).  Shape ids 100 + i.
+PAIRS = [(16, 16), (16, 32), (16, 64), (32, 8), (32, 16), (32, 32), (32, 64), (64, 8), (64, 16),
+         (64, 32), (64, 64), (128, 8), (128, 16), (256, 8)]
+# its thread blocks (unit_test_params.hpp:159-172): (warps_x, warps_y) of a (warps_x*32, warps_y) block
+THREAD_BLOCKS = [(1, 1), (1, 2), (2, 1), (1, 4), (2, 2), (4, 1)]
 NP = {1: np.int8, 2: np.float16, 4: np.float32, 8: np.float64}
 MATRIX = {0: "a", 1: "b", 2: "acc"}
 
@@ -38,8 +46,16 @@ def tlib():
 
 
 def tile_hw(matrix, shape):
+    if shape >= 100:
+        first, second = PAIRS[shape - 100]
+        return {0: (first, second), 1: (second, first), 2: (first, second)}[matrix]
     bm, bn, bk = SHAPES[shape]
     return {0: (bm, bk), 1: (bk, bn), 2: (bm, bn)}[matrix]
+
+
+def pair_fits(eb, matrix, pair):
+    """8-bit operand fragments need BlockK >= 16 (the reference's own minimum)."""
+    return matrix == 2 or eb != 1 or pair[1] >= 16
 
 
 def test_fragment_geometry_matches_the_reference_rules():
@@ -77,10 +93,12 @@ def _run_round_trip(eb, matrix, layout, shape, mode, warps, tiles_r=3, tiles_c=2
     sentinel = np.full_like(src, 77)
     t_in = torch.from_numpy(src).cuda()
     t_out = torch.from_numpy(sentinel).cuda()
+    if isinstance(warps, tuple):                 # (warps_x, warps_y) thread block
+        warps = warps[0] + 16 * warps[1]
     rc = tlib().b200wmma_test_round_trip(eb, matrix, layout, shape, t_in.data_ptr(),
                                          t_out.data_ptr(), ld, tiles_r, tiles_c, mode, warps,
                                          torch.cuda.current_stream().cuda_stream)
-    assert rc == 0
+    assert rc == 0, rc
     torch.cuda.synchronize()
     return (src.reshape(major + 2, ld), t_out.cpu().numpy().reshape(major + 2, ld), major, minor)
 
@@ -92,6 +110,40 @@ def _run_round_trip(eb, matrix, layout, shape, mode, warps, tiles_r=3, tiles_c=2
 @pytest.mark.parametrize("shape", [0, 1, 2])
 def test_load_store_round_trip_and_contamination(eb, matrix, layout, shape):
     src, out, major, minor = _run_round_trip(eb, matrix, layout, shape, mode=0, warps=4)
+    assert np.array_equal(out[:major, :minor], src[:major, :minor])
+    assert (out[:major, minor:] == 77).all() and (out[major:] == 77).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("eb", [1, 2, 4, 8])
+@pytest.mark.parametrize("matrix", [0, 1, 2])
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("pair", range(len(PAIRS)), ids=[f"{a}x{b}" for a, b in PAIRS])
+def test_round_trip_over_the_reference_block_grid(eb, matrix, layout, pair):
+    """load_matrix_sync / store_matrix_sync round trip and contamination check for every block
+    size of the reference's unit-test grid, from 32 x 8 up to 256 x 8, four element sizes."""
+    if not pair_fits(eb, matrix, PAIRS[pair]):
+        pytest.skip("8-bit operand fragments start at BlockK = 16, as in the reference")
+    src, out, major, minor = _run_round_trip(eb, matrix, layout, 100 + pair, mode=0, warps=(2, 2),
+                                             tiles_r=2, tiles_c=3, pad=3)
+    assert np.array_equal(out[:major, :minor], src[:major, :minor])
+    assert (out[:major, minor:] == 77).all() and (out[major:] == 77).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("block", THREAD_BLOCKS, ids=[f"{x * 32}x{y}" for x, y in THREAD_BLOCKS])
+@pytest.mark.parametrize("eb,matrix,layout,pair", [(2, 0, 0, 3), (2, 1, 1, 4), (4, 2, 0, 6),
+                                                   (1, 0, 1, 9), (8, 1, 0, 0), (2, 0, 1, 12),
+                                                   (4, 1, 1, 7), (2, 2, 1, 13)])
+def test_thread_block_arrangements(block, eb, matrix, layout, pair):
+    """The reference's thread blocks -- (32,1), (32,2), (64,1), (32,4), (64,2), (128,1) -- each
+    warp moving its own tile, and all warps of the block moving one tile cooperatively."""
+    src, out, major, minor = _run_round_trip(eb, matrix, layout, 100 + pair, mode=0, warps=block)
+    assert np.array_equal(out[:major, :minor], src[:major, :minor])
+    assert (out[:major, minor:] == 77).all() and (out[major:] == 77).all()
+    nwarps = block[0] * block[1]
+    src, out, major, minor = _run_round_trip(eb, matrix, layout, 100 + pair, mode=nwarps,
+                                             warps=block)
     assert np.array_equal(out[:major, :minor], src[:major, :minor])
     assert (out[:major, minor:] == 77).all() and (out[major:] == 77).all()
 

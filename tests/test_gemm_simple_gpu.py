@@ -97,7 +97,12 @@ BLOCK_K_CASES = [(O.F16, O.F32, 16, 32), (O.F16, O.F32, 16, 64), (O.F16, O.F32, 
                  (O.F32, O.F32, 16, 8), (O.F32, O.F32, 32, 32), (O.XF32, O.F32, 16, 8),
                  (O.XF32, O.F32, 32, 8), (O.XF32, O.F32, 32, 32), (O.F64, O.F64, 16, 4),
                  (O.F64, O.F64, 16, 8), (O.F16, O.F32, 16, 128), (O.BF16, O.F32, 16, 128),
-                 (O.E4M3, O.F32, 16, 128), (O.I8, O.I32, 16, 128)]
+                 (O.E4M3, O.F32, 16, 128), (O.I8, O.I32, 16, 128),
+                 # below the K extent of the full-depth tensor-core instruction: the reference's
+                 # minima for 32 x 32 blocks (test/gemm/gemm_predicates_base.hpp:137-209)
+                 (O.F16, O.F32, 32, 8), (O.F16, O.F16, 32, 8), (O.BF16, O.F32, 32, 8),
+                 (O.BF16, O.BF16, 32, 8), (O.F16, O.F32, 16, 8), (O.XF32, O.F32, 32, 4),
+                 (O.XF32, O.F32, 16, 4), (O.F32, O.F32, 32, 4)]
 
 
 @pytest.mark.parametrize("in_t,out_t,block,block_k", BLOCK_K_CASES)
@@ -110,6 +115,22 @@ def test_simple_gemm_other_fragment_k_extents(in_t, out_t, block, block_k):
     got, want = _run_simple(case, ROW, block, block_k=block_k)
     err = O.max_rel_err(out_t, got, want)
     assert 0 <= err <= tolerance(in_t, out_t), err
+
+
+def test_half_depth_fragments_with_16_bit_accumulation():
+    """f16 / f16 / f16 with BlockK = 8 (m16n8k8 with fp16 accumulators) on the reference's
+    small-integer fill, where every product and sum is exact in any order; bf16 / bf16 / bf16
+    (rounded to bf16 per BlockK step) within the reference's pass mark for that type."""
+    case = dict(in_t=O.F16, out_t=O.F16, m=64, n=64, k=64, la=ROW, lb=COL, alpha=1.0, beta=1.0,
+                seed=77, dist="pattern")
+    got, want = _run_simple(case, ROW, 32, compute=O.F16, block_k=8)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    case = dict(in_t=O.BF16, out_t=O.BF16, m=64, n=64, k=64, la=ROW, lb=COL, alpha=1.0, beta=1.0,
+                seed=78)
+    got, want = _run_simple(case, ROW, 32, compute=O.BF16, block_k=8)
+    err = O.max_rel_err(O.BF16, got, want)
+    assert 0 <= err <= triple_tolerance(O.BF16, O.BF16, O.BF16) + _host_rounding_noise(
+        case, O.BF16, want), err
 
 
 def test_unbuilt_fragment_k_extent_is_refused():
