@@ -50,6 +50,10 @@ from rocwmma_b200._lib import (BF16, COL_MAJOR, E4M3, E5M2, F16, F32, F64, I8, I
 
 WORLD = int(os.environ.get("WORLD_SIZE", "1"))
 RANK = int(os.environ.get("RANK", "0"))
+# How many ranks the problem is cut for.  Normally the process group's size; --as-shard-of N
+# makes a single process run (and time) rank 0's share of an N-rank job, which is how the
+# profiler captures of shard-sized launches are taken on one GPU.
+SHARD_WORLD = WORLD
 
 # north_star tolerances on max |a-b| / (|a|+|b|+1), per input type
 TOLERANCE = {F16: 2e-3, BF16: 2e-3, E4M3: 1e-2, E5M2: 1e-2, I8: 0.0, F32: 1e-4, XF32: 1e-4,
@@ -210,7 +214,7 @@ def gemm_case(name, in_t, out_t, size, alpha, beta, seed, peak_scale, simple=Fal
               check=True, check_rows=16):
     """One GEMM configuration: this rank's rows of A / C / D, all of B."""
     n = k = size
-    row0, m = shard.gemm_shard(size, WORLD, RANK)
+    row0, m = shard.gemm_shard(size, SHARD_WORLD, RANK)
     th = gen_threads()
     if in_t in (E4M3, E5M2):
         a = _fp8_matrix(seed, 1, in_t, row0, m, k, size)
@@ -234,7 +238,8 @@ def gemm_case(name, in_t, out_t, size, alpha, beta, seed, peak_scale, simple=Fal
         fn = lambda: api.gemm(in_t, out_t, m, n, k, da, db, dc, alpha, beta, out=dd)  # noqa: E731
     ws = (m * k + k * n) * _ELEM_BYTES[in_t] + m * n * _ELEM_BYTES[out_t] * (2 if c is not None else 1)
     ms, flushed = timed(fn, iters, ws)
-    tf = 2.0 * size * n * k / ms / 1e9
+    work_rows = size if SHARD_WORLD == WORLD else m     # a lone shard counts its own rows only
+    tf = 2.0 * work_rows * n * k / ms / 1e9
     peak_bf16, _, src = peaks()
     peak = (peak_bf16 * peak_scale if peak_scale else 40.0) * WORLD
     res = {"config": name, "n_gpus": WORLD, "ms": ms, "value": tf, "unit": "TFLOP/s",
@@ -286,7 +291,7 @@ def gemm_case(name, in_t, out_t, size, alpha, beta, seed, peak_scale, simple=Fal
 
 def gemv_case(size, seed=4, iters=50, check=True):
     k = size
-    row0, m = shard.gemv_shard(size, WORLD, RANK)   # this rank's rows: its own column-major block
+    row0, m = shard.gemv_shard(size, SHARD_WORLD, RANK)   # this rank's rows: its own column-major block
     th = gen_threads()
     # column-major m x k with lda = m: k rows of m values; every row shard is its own tensor
     a = synth.rows(seed, 16 + row0 // 64, F32, 0, k, m, threads=th)
@@ -325,7 +330,7 @@ def gemv_case(size, seed=4, iters=50, check=True):
 def dlrm_cases(total_batch, seed=4, iters=20, check=True, which=("fwd", "bwd")):
     m, k = 27, 128
     out_len = k + m * (m - 1) // 2
-    first, batch = shard.dlrm_shard(total_batch, WORLD, RANK)   # this rank's samples
+    first, batch = shard.dlrm_shard(total_batch, SHARD_WORLD, RANK)   # this rank's samples
     assert first % synth.CHUNK_ROWS == 0
     th = gen_threads()
     x = synth.rows(seed, 1, F16, first, batch, m * k, dist="normal", threads=th)
@@ -448,10 +453,17 @@ def main():
     ap.add_argument("--iters", type=int, default=0)
     ap.add_argument("--csv", default="", help="also write the GEMM results as a rocWMMA-style table")
     ap.add_argument("--no-check", action="store_true", help="timing only (no CPU parity check)")
+    ap.add_argument("--as-shard-of", type=int, default=0,
+                    help="run rank 0's share of an N-rank job in this single process (GEMM "
+                         "figures then count the shard's rows only)")
     ap.add_argument("--small", action="store_true",
                     help="reduced sizes (for profiler captures): GEMMs 2048^3, DLRM b=8192, "
                          "GEMV 8192^2")
     args = ap.parse_args()
+    if args.as_shard_of > 1:
+        assert WORLD == 1, "--as-shard-of is for single-process runs"
+        global SHARD_WORLD
+        SHARD_WORLD = args.as_shard_of
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     if WORLD > 1:
         torch.distributed.init_process_group("nccl")
