@@ -87,6 +87,9 @@ namespace
         uint32_t    snake, mirror; // pair kernel: tile order (TileSchedule)
         uint32_t    prefetch; // pair kernel: k-blocks of the first tile to request into L2 early
         uint32_t    stagedTail; // pair kernel: a block's last tile leaves through the idle ring
+        uint32_t    splitTiles; // pair kernel: tiles of the last wave cut in two along K
+        float*      splitWs; // ... their partial accumulators (raw 32-bit values)
+        uint32_t*   splitCtr; // ... and one arrival counter per split tile and block of the pair
     };
 
     // One operand tile for one K block.  K-major: one TMA box of `rows` rows x 128 bytes of
@@ -719,6 +722,97 @@ namespace
         return true;
     }
 
+    // ---- half of a tile that was split along K ---------------------------------------------
+    // Two pairs each accumulate half of K for the same tile (TileSchedule::splitTiles).  Each
+    // block writes its raw 32-bit accumulator to the workspace, makes it visible and takes a
+    // ticket from the tile's counter; whoever draws the second ticket adds the other half
+    // (read from the workspace past L1) to its own (still in tensor memory) and does the
+    // ordinary row epilogue; the first one is done after its write.  Nobody waits for anybody,
+    // so nothing can hang, and a two-term fp32 (or int32) sum does not depend on who came
+    // last.  The counter is put back to zero by the second arrival.
+    // Workspace: [split tile][part][block of the pair][128 rows][256 columns] of 32-bit values.
+    template <typename OutT, typename CompT>
+    __device__ inline bool drainSplitPart(uint64_t* accFullBar, uint32_t accPh, AbortState* abort,
+                                          uint32_t taddrRowBase, GemmParams const& p,
+                                          uint32_t* lastFlag, uint32_t splitIndex, uint32_t part,
+                                          uint32_t rank, CompT alpha, CompT beta, bool useC,
+                                          uint32_t rowInTile, uint32_t row, uint32_t colBase,
+                                          bool leader, uint32_t bnTile)
+    {
+        constexpr uint32_t PLANE  = 128u * 256u; // values of one block's half-accumulator
+        const uint32_t     groups = bnTile / 32u;
+        uint32_t* mine  = reinterpret_cast<uint32_t*>(p.splitWs)
+                         + size_t((splitIndex * 2u + part) * 2u + rank) * PLANE + rowInTile * 256u;
+        uint32_t const* theirs = reinterpret_cast<uint32_t const*>(p.splitWs)
+                                 + size_t((splitIndex * 2u + (part ^ 1u)) * 2u + rank) * PLANE
+                                 + rowInTile * 256u;
+        const bool ready = mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL);
+        if(!named_barrier_all(1, EPI_THREADS, ready))
+            return false;
+        tc_fence_after_sync();
+#pragma unroll 1
+        for(uint32_t h = 0; h < 2u * groups; ++h) // 16 columns at a time
+        {
+            uint32_t raw[16];
+            tmem_load_32x32b_x16(taddrRowBase + h * 16u, raw);
+            tmem_load_wait();
+#pragma unroll
+            for(uint32_t v = 0; v < 2; ++v)
+                stVec<32>(mine + h * 16u + v * 8u, &raw[v * 8u]);
+        }
+        __threadfence(); // this thread's part is visible device-wide before the ticket is drawn
+        named_barrier(1, EPI_THREADS);
+        if(leader)
+        {
+            uint32_t* ctr    = p.splitCtr + splitIndex * 2u + rank;
+            const uint32_t t = atomicAdd(ctr, 1u);
+            if(t == 1u)
+                atomicExch(ctr, 0u); // both halves are in: ready for the next launch
+            *lastFlag = t;
+        }
+        named_barrier(1, EPI_THREADS);
+        const bool last = (*reinterpret_cast<volatile uint32_t*>(lastFlag) == 1u);
+        named_barrier(1, EPI_THREADS); // everybody has read the flag before it is written again
+        if(last)
+        {
+            __threadfence();
+#pragma unroll 1
+            for(uint32_t g = 0; g < groups; ++g)
+            {
+                uint32_t raw[32];
+                __syncwarp();
+                tmem_load_32x32b_x32(taddrRowBase + g * 32u, raw);
+                tmem_load_wait();
+#pragma unroll
+                for(uint32_t h = 0; h < 4; ++h) // the other half, 8 values at a time
+                {
+                    uint32_t other[8];
+#pragma unroll
+                    for(uint32_t v = 0; v < 2; ++v)
+                        asm volatile("ld.global.cg.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(other[v * 4u]), "=r"(other[v * 4u + 1u]),
+                                       "=r"(other[v * 4u + 2u]), "=r"(other[v * 4u + 3u])
+                                     : "l"(theirs + g * 32u + h * 8u + v * 4u));
+#pragma unroll
+                    for(uint32_t e = 0; e < 8; ++e)
+                    {
+                        uint32_t& r = raw[h * 8u + e];
+                        if constexpr(std::is_same<CompT, float>::value)
+                            r = __float_as_uint(
+                                __fadd_rn(__uint_as_float(r), __uint_as_float(other[e])));
+                        else
+                            r = uint32_t(int32_t(r) + int32_t(other[e]));
+                    }
+                }
+                const uint32_t col0 = colBase + g * 32u;
+                if(row < p.m && col0 < p.n)
+                    epilogueRow<OutT, CompT>(raw, p, alpha, beta, useC, row, col0, EPI_WHOLE);
+            }
+        }
+        tc_fence_before_sync();
+        return true;
+    }
+
     // ---- a block's LAST tile: out through the idle operand ring ---------------------------
     // Inside a run of tiles the epilogue hides behind the next tile's MMAs; after a block's
     // last tile nothing is left to hide it, and a two-wave launch (the 1024-row shard of an
@@ -1079,6 +1173,7 @@ namespace
         uint64_t   accFull[ACC_BUFS];
         uint64_t   accEmpty[ACC_BUFS];
         uint32_t   tmemBase;
+        uint32_t   splitLast; // epilogue: this block arrived last at a split tile
         AbortState abort;
     };
     constexpr uint32_t P_SMEM_BYTES
@@ -1124,8 +1219,8 @@ namespace
         const uint32_t numKB    = (p.k + BK - 1) / BK;
         const uint32_t chunkKB  = p.chunkKB != 0u ? p.chunkKB : numKB; // K blocks per chain
         const uint32_t numChunks = (numKB + chunkKB - 1) / chunkKB;
-        const TileSchedule sched{tilesM, p.wideCols, p.tailCols, bn,      p.bnTail,
-                                 p.band, nPairs,     p.snake,    p.mirror};
+        const TileSchedule sched{tilesM, p.wideCols, p.tailCols, bn,       p.bnTail,
+                                 p.band, nPairs,     p.snake,    p.mirror, p.splitTiles};
 
         if(threadIdx.x == 0)
         {
@@ -1161,15 +1256,16 @@ namespace
             // tail) is still running.  An L2 prefetch reads nothing into the SM, and L2 is
             // where a later write by the previous kernel lands too, so this is safe before
             // griddepcontrol.wait even when A or B is that kernel's output.
-            uint32_t tm, col0, width;
-            if(sched.get(pairId, 0, tm, col0, width))
+            uint32_t tm, col0, width, part, ways, splitIndex;
+            if(sched.getItem(pairId, 0, tm, col0, width, part, ways, splitIndex))
             {
                 const void*    mapB = width == bn ? static_cast<void const*>(&tmapB)
                                                   : static_cast<void const*>(&tmapBTail);
                 const int32_t  rowA = int32_t(tm * P_TILE_M + rank * 128u);
                 const int32_t  rowB = int32_t(col0 + rank * (width / 2u));
-                const uint32_t nkb  = p.prefetch < numKB ? p.prefetch : numKB;
-                for(uint32_t kb = 0; kb < nkb; ++kb)
+                const uint32_t kb0  = part * numKB / ways;
+                const uint32_t nkb  = kb0 + (p.prefetch < numKB ? p.prefetch : numKB);
+                for(uint32_t kb = kb0; kb < nkb && kb < numKB; ++kb)
                 {
                     if(p.aMN == 0u)
                         tma_prefetch_l2_2d(&tmapA, int32_t(kb * BK), rowA);
@@ -1205,8 +1301,8 @@ namespace
                 bool     ok = true;
                 for(uint32_t i = 0; ok; ++i)
                 {
-                    uint32_t tm, col0, width;
-                    if(!sched.get(pairId, i, tm, col0, width))
+                    uint32_t tm, col0, width, part, ways, splitIndex;
+                    if(!sched.getItem(pairId, i, tm, col0, width, part, ways, splitIndex))
                         break;
                     const int32_t  rowA = int32_t(tm * P_TILE_M + rank * 128u);
                     const int32_t  rowB = int32_t(col0 + rank * (width / 2u));
@@ -1214,7 +1310,9 @@ namespace
                                                       : static_cast<void const*>(&tmapBTail);
                     const uint32_t pairSlotBytes
                         = aSlotBytes + operandTileBytes<InT>(p.bMN != 0u, width / 2u);
-                    for(uint32_t kb = 0; kb < numKB; ++kb, ++it)
+                    // this item's k-blocks: all of them, or its half of a split tile
+                    const uint32_t kbBegin = part * numKB / ways, kbEnd = (part + 1u) * numKB / ways;
+                    for(uint32_t kb = kbBegin; kb < kbEnd; ++kb, ++it)
                     {
                         const uint32_t s  = it % P_STAGES;
                         const uint32_t ph = (it / P_STAGES) & 1u;
@@ -1245,11 +1343,12 @@ namespace
                 bool     ok = true;
                 for(uint32_t i = 0; ok; ++i)
                 {
-                    uint32_t tm, col0, width;
-                    if(!sched.get(pairId, i, tm, col0, width))
+                    uint32_t tm, col0, width, part, ways, splitIndex;
+                    if(!sched.getItem(pairId, i, tm, col0, width, part, ways, splitIndex))
                         break;
-                    const uint32_t idesc = width == bn ? IDESC : IDESC_TAIL;
-                    for(uint32_t kb0 = 0; ok && kb0 < numKB; kb0 += chunkKB, ++accIter)
+                    const uint32_t idesc   = width == bn ? IDESC : IDESC_TAIL;
+                    const uint32_t kbBegin = part * numKB / ways, kbEnd = (part + 1u) * numKB / ways;
+                    for(uint32_t kb0 = kbBegin; ok && kb0 < kbEnd; kb0 += chunkKB, ++accIter)
                     {
                         const uint32_t buf   = accIter & 1u;
                         const uint32_t accPh = (accIter >> 1) & 1u;
@@ -1261,7 +1360,7 @@ namespace
                         }
                         tc_fence_after_sync();
                         const uint32_t dTmem = tmemBase + buf * BN;
-                        const uint32_t kb1   = min(numKB, kb0 + chunkKB);
+                        const uint32_t kb1   = min(kbEnd, kb0 + chunkKB);
                         for(uint32_t kb = kb0; kb < kb1; ++kb, ++it)
                         {
                             const uint32_t s  = it % P_STAGES;
@@ -1301,13 +1400,15 @@ namespace
             bool           ok      = true;
             for(uint32_t i = 0; ok; ++i)
             {
-                uint32_t tm, col0, width;
-                if(!sched.get(pairId, i, tm, col0, width))
+                uint32_t tm, col0, width, part, ways, splitIndex;
+                if(!sched.getItem(pairId, i, tm, col0, width, part, ways, splitIndex))
                     break;
                 const uint32_t row = tm * P_TILE_M + rank * 128u + quad * 32u + lane;
-                uint32_t       tmNext, colNext, widthNext;
-                const bool     stagedTail = p.stagedTail != 0u && numChunks == 1u
-                                        && !sched.get(pairId, i + 1u, tmNext, colNext, widthNext);
+                uint32_t       tmNext, colNext, widthNext, partNext, waysNext, splitNext;
+                const bool     stagedTail
+                    = p.stagedTail != 0u && numChunks == 1u && ways == 1u
+                      && !sched.getItem(pairId, i + 1u, tmNext, colNext, widthNext, partNext,
+                                        waysNext, splitNext);
                 for(uint32_t ch = 0; ch < numChunks; ++ch, ++accIter)
                 {
                     const uint32_t buf   = accIter & 1u;
@@ -1319,7 +1420,15 @@ namespace
                     const uint32_t taddrLane = tmemBase + ((quad * 32u) << 16);
                     const uint32_t taddr     = taddrLane + buf * BN;
                     bool           drained;
-                    if(stagedTail)
+                    if(ways > 1u)
+                    {
+                        // half of a split tile: see drainSplitPart
+                        drained = drainSplitPart<OutT, CompT>(
+                            &ctl->accFull[buf], accPh, &ctl->abort, taddr, p, &ctl->splitLast,
+                            splitIndex, part, rank, alpha, beta, useC, quad * 32u + lane, row, col0,
+                            threadIdx.x == 64u, width);
+                    }
+                    else if(stagedTail)
                     {
                         // this block's last tile: the ring is idle, see drainLastTileStaged
                         drained = drainLastTileStaged<OutT, CompT>(
@@ -1573,7 +1682,7 @@ namespace
         GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
                      status, chunkKB, wide, BN, bandEnv ? bandEnv : bandRows(k, sizeof(InT)),
                      useTma ? 1u : 0u,
-                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, nullptr, nullptr};
         CUtensorMap mapA, mapB, mapD;
         {
             int rcD = makeOutputMap(&mapD, outputMapType<OutT>(), sizeof(OutT), d, m, n, ldd);
@@ -1636,9 +1745,32 @@ namespace
             const uint32_t widest   = tmemSum ? 160u : 256u;
             const bool     subWave  = tilesM * ((n + widest - 1) / widest) < pairsMax;
             const uint32_t narrowest = (tmemSum || subWave) ? 128u : 192u;
+            // Tiles of a last wave that is less than half full can be cut in two along K
+            // (TileSchedule::splitTiles, drainSplitPart): 256 tiles on 74 pairs then take 3.5
+            // waves instead of 4.  Only with one accumulation chain per tile, a workspace to
+            // meet in (the allocation-free entry point has none) and K deep enough to halve.
+            // OFF unless B200WMMA_GEMM_SPLIT=1: it measured SLOWER on this part -- 4096^3
+            // bf16 -> f32 112.8 -> 119.0 us, fp16 96.0 -> 103.0, int8 50.1 -> 65.6 (same box,
+            // alternating runs).  Under the 1 kW cap a half-empty last wave is not idle time
+            // to be filled: the SMs that have run out let the others clock higher, so wave
+            // quantisation costs 4096^3 about 5 %, not the 13.5 % its tile count suggests, and
+            // the trip through the workspace costs more than that.
+            const char* splitEnv   = getenv("B200WMMA_GEMM_SPLIT");
+            const bool  splitAllowed = (splitEnv && splitEnv[0] == '1') && chunkKB == 0u
+                                      && status != nullptr
+                                      && (k + ROW_BYTES / sizeof(InT) - 1) / (ROW_BYTES / sizeof(InT)) >= 8u;
+            auto splitCount = [&](uint32_t tiles) -> uint32_t {
+                if(!splitAllowed || tiles <= pairsMax)
+                    return 0u;
+                const uint32_t rem = tiles % pairsMax;
+                return (rem != 0u && 2u * rem <= pairsMax) ? rem : 0u;
+            };
             auto makespan = [&](uint32_t bnW, uint32_t wideCols, uint32_t tailCols, uint32_t bnT) {
                 const uint32_t total = tilesM * (wideCols + tailCols);
                 const uint32_t pairs = total < pairsMax ? total : pairsMax;
+                if(tailCols == 0u && splitCount(total) != 0u)
+                    // whole waves, then half a tile plus the fix-up through the workspace
+                    return (total / pairsMax) * (bnW + 64u) + (bnW + 64u) / 2u + 24u;
                 TileSchedule   sc{tilesM, wideCols, tailCols, bnW, bnT, GROUP_M, pairs, 0u, 0u};
                 uint32_t       worst = 0;
                 for(uint32_t pr = 0; pr < pairs; ++pr)
@@ -1693,6 +1825,22 @@ namespace
             p.wideCols = wideCols;
             p.tailCols = tailCols;
             p.bnTail   = bnTail;
+            if(tailCols == 0u)
+            {
+                const uint32_t split = splitCount(tilesM * wideCols);
+                if(split != 0u && split * 2u <= 256u)
+                {
+                    // per split tile: 2 halves x 2 blocks x 128 rows x 256 columns x 4 bytes
+                    uint32_t* ctr = nullptr;
+                    void*     ws  = b200wmma::splitWorkspace(size_t(split) * 4u * 128u * 256u * 4u, &ctr);
+                    if(ws != nullptr)
+                    {
+                        p.splitTiles = split;
+                        p.splitWs    = static_cast<float*>(ws);
+                        p.splitCtr   = ctr;
+                    }
+                }
+            }
             // Tile order (TileSchedule).  B200WMMA_GEMM_ORDER = digits "smp" (snake, mirror on
             // alternate launches, k-blocks prefetched into L2), e.g. "000" for the plain
             // order; tuning and comparison only.
@@ -1760,7 +1908,7 @@ namespace
             rc = optInSharedMemory(kernel, P_SMEM_BYTES, done);
             if(rc != B200WMMA_OK)
                 return rc;
-            const uint32_t tiles = tilesM * (wideCols + tailCols);
+            const uint32_t tiles = tilesM * (wideCols + tailCols) + p.splitTiles; // work items
             const uint32_t pairs = tiles < pairsMax ? tiles : pairsMax;
             return b200wmma::cudaToStatus(b200wmma::launchOverlapped(
                 kernel, dim3(2 * pairs), dim3(NUM_THREADS), P_SMEM_BYTES, stream, mapA, mapB,

@@ -17,6 +17,9 @@ namespace b200wmma
             int       smCount = 0;
             void*     scratch = nullptr; // general scratch (GEMV partial sums ...)
             size_t    scratchBytes = 0;
+            void*     splitWs      = nullptr; // partial accumulators of split GEMM tiles
+            size_t    splitWsBytes = 0;
+            uint32_t* splitCtr     = nullptr; // 256 arrival counters
             void*     stage[4]      = {nullptr, nullptr, nullptr, nullptr}; // A, B, C, D staging
             size_t    stageBytes[4] = {0, 0, 0, 0};
             HostPipe  pipe;
@@ -114,6 +117,42 @@ namespace b200wmma
             st->scratchBytes = bytes;
         }
         return st->scratch;
+    }
+
+    void* splitWorkspace(size_t bytes, uint32_t** counters)
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        DeviceState*                st = current();
+        if(!st || !counters)
+            return nullptr;
+        if(!st->splitCtr)
+        {
+            if(cudaMalloc(&st->splitCtr, 256 * sizeof(uint32_t)) != cudaSuccess
+               || cudaMemset(st->splitCtr, 0, 256 * sizeof(uint32_t)) != cudaSuccess
+               || cudaDeviceSynchronize() != cudaSuccess)
+            {
+                (void)cudaGetLastError();
+                if(st->splitCtr)
+                    (void)cudaFree(st->splitCtr);
+                st->splitCtr = nullptr;
+                return nullptr;
+            }
+        }
+        if(st->splitWsBytes < bytes)
+        {
+            if(st->splitWs)
+                (void)cudaFree(st->splitWs);
+            st->splitWs      = nullptr;
+            st->splitWsBytes = 0;
+            if(cudaMalloc(&st->splitWs, bytes) != cudaSuccess)
+            {
+                (void)cudaGetLastError();
+                return nullptr;
+            }
+            st->splitWsBytes = bytes;
+        }
+        *counters = st->splitCtr;
+        return st->splitWs;
     }
 
     void* stagingBuffer(int slot, size_t bytes)
@@ -274,6 +313,13 @@ int b200wmma_check_device(void* stream, uint32_t* detail)
         // idle here, so put all of them back to zero
         B200WMMA_CUDA_TRY(cudaDeviceSynchronize());
         resetLaunchCounters();
+        {
+            std::lock_guard<std::mutex> lock(g_mutex);
+            DeviceState*                st = current();
+            if(st && st->splitCtr
+               && cudaMemset(st->splitCtr, 0, 256 * sizeof(uint32_t)) != cudaSuccess)
+                (void)cudaGetLastError();
+        }
         return B200WMMA_ERR_DEVICE_WAIT;
     }
     return B200WMMA_OK;
@@ -288,7 +334,7 @@ int b200wmma_shutdown(void)
     {
         DeviceState& st = g_dev[d];
         bool any = st.status || st.scratch || st.stage[0] || st.stage[1] || st.stage[2]
-                   || st.stage[3] || st.pipe.ok || st.counters;
+                   || st.stage[3] || st.pipe.ok || st.counters || st.splitWs || st.splitCtr;
         if(!any)
             continue;
         if(cudaSetDevice(d) != cudaSuccess)
@@ -302,6 +348,13 @@ int b200wmma_shutdown(void)
             (void)cudaFree(st.scratch);
         if(st.counters)
             (void)cudaFree(st.counters);
+        if(st.splitWs)
+            (void)cudaFree(st.splitWs);
+        if(st.splitCtr)
+            (void)cudaFree(st.splitCtr);
+        st.splitWs      = nullptr;
+        st.splitWsBytes = 0;
+        st.splitCtr     = nullptr;
         for(void*& p : st.stage)
             if(p)
                 (void)cudaFree(p);

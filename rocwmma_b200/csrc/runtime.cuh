@@ -19,6 +19,11 @@ namespace b200wmma
     // A device buffer of at least `bytes`, kept per device and grown on demand
     // (contents are not preserved across growth).  nullptr on failure.
     void* deviceScratch(size_t bytes);
+    // Workspace of the GEMM's split tiles: at least `bytes` of device memory (grown on demand)
+    // and, through *counters, 256 zero-initialised 32-bit arrival counters that the kernels
+    // leave at zero.  One per device: GEMM launches that split tiles must not overlap on one
+    // device (different streams).  nullptr on failure.
+    void* splitWorkspace(size_t bytes, uint32_t** counters);
     // Staging buffers for the host-buffer GEMM entry point; slot 0..3 = A, B, C, D.
     void* stagingBuffer(int slot, size_t bytes);
 

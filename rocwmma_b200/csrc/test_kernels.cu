@@ -388,6 +388,42 @@ TEST_API int b200wmma_test_tile_order(uint32_t tiles_m, uint32_t wide_cols, uint
     return total;
 }
 
+// Work items of a launch whose last `split_tiles` tiles are cut in two along K:
+// parts[tm * wide_cols + c] receives a bit mask of the K parts handed out for tile (tm, c)
+// -- bit 0 set alone (with ways == 1) for a whole tile, bits 0 and 1 for the two halves of a
+// split tile -- and whole[...] how often the tile was handed out as a whole.  Returns the
+// number of work items, or -1 on an inconsistent item.
+TEST_API int b200wmma_test_tile_split(uint32_t tiles_m, uint32_t wide_cols, uint32_t bn,
+                                      uint32_t band, uint32_t pairs, uint32_t snake,
+                                      uint32_t mirror, uint32_t split_tiles, uint32_t* parts,
+                                      uint32_t* whole, uint32_t* per_pair)
+{
+    b200wmma::TileSchedule sc{tiles_m, wide_cols, 0u, bn, 0u, band, pairs, snake, mirror, split_tiles};
+    int                    total = 0;
+    for(uint32_t p = 0; p < pairs; ++p)
+    {
+        uint32_t tm, col0, width, part, ways, splitIndex;
+        for(uint32_t i = 0; sc.getItem(p, i, tm, col0, width, part, ways, splitIndex); ++i)
+        {
+            if(width != bn || col0 % bn != 0 || tm >= tiles_m || col0 / bn >= wide_cols
+               || part >= ways || (ways != 1u && ways != 2u) || (ways == 2u && splitIndex >= split_tiles))
+                return -1;
+            const uint32_t idx = tm * wide_cols + col0 / bn;
+            if(ways == 1u)
+                whole[idx] += 1;
+            else
+            {
+                if(parts[idx] & (1u << part))
+                    return -1; // the same half twice
+                parts[idx] |= 1u << part;
+            }
+            per_pair[p] += ways == 1u ? 2u : 1u; // in half-tiles
+            ++total;
+        }
+    }
+    return total;
+}
+
 // Runs the never-satisfied wait with a limit of `limit_cycles` SM cycles (keep it around a
 // millisecond); the kernel always terminates by itself.
 TEST_API int b200wmma_test_bounded_wait(uint32_t* out4, long long limit_cycles, void* stream)

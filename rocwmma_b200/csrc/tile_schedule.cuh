@@ -21,10 +21,17 @@ namespace b200wmma
     // once per band: B is about as large as the L2).  With `mirror` set the whole sequence
     // runs backwards: a launch that mirrors its predecessor starts on the tiles -- and the
     // rows of A and columns of B -- that predecessor finished on.
+    //
+    // Split tiles.  When the last wave of a launch is less than half full, its `splitTiles`
+    // tiles (the last ones in band order; wide tiles only, no tail columns) are each cut in
+    // two along K and handed to two pairs: work item q < wideTiles - splitTiles is a whole
+    // tile, the items after it come in twos, the halves of one tile.  getItem() reports the
+    // half (`part`) and how many there are (`ways`: 1 or 2); the two halves meet in a
+    // workspace (see the kernel).
     struct TileSchedule
     {
         uint32_t tilesM, wideCols, tailCols, bn, bnTail, band, pairs;
-        uint32_t snake = 0, mirror = 0;
+        uint32_t snake = 0, mirror = 0, splitTiles = 0;
 
         __host__ __device__ uint32_t wideTiles() const
         {
@@ -33,6 +40,47 @@ namespace b200wmma
         __host__ __device__ uint32_t tailTiles() const
         {
             return tilesM * tailCols;
+        }
+        // wide tile t (band order, snake applied) -> tile row and first column
+        __host__ __device__ void wideCoord(uint32_t t, uint32_t& tm, uint32_t& col0) const
+        {
+            const uint32_t perGroup = band * wideCols;
+            const uint32_t group    = t / perGroup;
+            const uint32_t firstM   = group * band;
+            const uint32_t rows     = (tilesM - firstM) < band ? (tilesM - firstM) : band;
+            const uint32_t r        = t % perGroup;
+            const uint32_t col      = r / rows;
+            tm                      = firstM + r % rows;
+            col0 = ((snake && (group & 1u)) ? wideCols - 1u - col : col) * bn;
+        }
+        // i-th work item of pair p: tile row, first column, width, and which part of how many
+        // along K (ways == 1: the whole tile).  `splitIndex` numbers the split tiles from 0.
+        // false when the pair is done.
+        __host__ __device__ bool getItem(uint32_t p, uint32_t i, uint32_t& tm, uint32_t& col0,
+                                         uint32_t& width, uint32_t& part, uint32_t& ways,
+                                         uint32_t& splitIndex) const
+        {
+            part       = 0u;
+            ways       = 1u;
+            splitIndex = 0u;
+            if(splitTiles == 0u)
+                return get(p, i, tm, col0, width);
+            // split launches have no tail columns
+            const uint32_t whole = wideTiles() - splitTiles;
+            const uint32_t q     = p + i * pairs;
+            if(q >= whole + 2u * splitTiles)
+                return false;
+            width = bn;
+            if(q < whole)
+            {
+                wideCoord(mirror ? whole - 1u - q : q, tm, col0);
+                return true;
+            }
+            splitIndex = (q - whole) / 2u;
+            part       = (q - whole) % 2u;
+            ways       = 2u;
+            wideCoord(whole + splitIndex, tm, col0);
+            return true;
         }
         // i-th tile of pair p: tile row, first column, width.  false when the pair is done.
         __host__ __device__ bool get(uint32_t p, uint32_t i, uint32_t& tm, uint32_t& col0,
@@ -43,16 +91,8 @@ namespace b200wmma
             const uint32_t mine = base + (p < nHi ? 1u : 0u);
             if(i < mine)
             {
-                const uint32_t seq      = p + i * pairs;
-                const uint32_t t        = mirror ? W - 1u - seq : seq;
-                const uint32_t perGroup = band * wideCols;
-                const uint32_t group    = t / perGroup;
-                const uint32_t firstM   = group * band;
-                const uint32_t rows     = (tilesM - firstM) < band ? (tilesM - firstM) : band;
-                const uint32_t r        = t % perGroup;
-                const uint32_t col      = r / rows;
-                tm                      = firstM + r % rows;
-                col0  = ((snake && (group & 1u)) ? wideCols - 1u - col : col) * bn;
+                const uint32_t seq = p + i * pairs;
+                wideCoord(mirror ? W - 1u - seq : seq, tm, col0);
                 width = bn;
                 return true;
             }

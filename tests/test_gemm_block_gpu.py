@@ -336,3 +336,41 @@ def test_dependent_launches_keep_stream_order(m):
         assert np.array_equal(chain(False), want)
     api.check_device()
     assert np.isfinite(want.view(np.float16).astype(np.float32)).all()
+
+
+@pytest.mark.parametrize("in_t,out_t,alpha,beta", [(O.F16, O.F16, 1.0, 0.0), (O.BF16, O.F32, 2.0, -1.0),
+                                                   (O.I8, O.I32, 1, 1), (O.E4M3, O.BF16, 2.0 ** -8, 0.0)])
+def test_split_last_wave(in_t, out_t, alpha, beta, monkeypatch):
+    """A 4096 x 4096 output is 256 tiles on 74 CTA pairs: the 34 tiles of the last wave are cut
+    in two along K and meet in a workspace (drainSplitPart).  The result must agree with the
+    unsplit launch (bit for bit for int8, whose sums are exact in any order) and with the CPU
+    oracle on a sample of rows; two launches in a row leave the arrival counters at zero."""
+    m = n = 4096
+    k = 1024
+    seed = 9
+    dist = "int8" if in_t == O.I8 else "uniform"
+    a = synth.rows(seed, 1, in_t, 0, m, k, dist=dist)
+    bt = synth.rows(seed, 2, in_t, 0, n, k, dist=dist)
+    c = synth.rows(seed, 3, out_t, 0, m, n, dist="int32" if out_t == O.I32 else "uniform")
+    da, db, dc = to_device(a.reshape(-1), in_t), to_device(bt.reshape(-1), in_t), \
+        to_device(c.reshape(-1), out_t)
+    cc = dc if beta != 0 else None
+    monkeypatch.setenv("B200WMMA_GEMM_SPLIT", "0")
+    whole = api.gemm(in_t, out_t, m, n, k, da, db, cc, alpha, beta)
+    monkeypatch.setenv("B200WMMA_GEMM_SPLIT", "1")
+    split1 = api.gemm(in_t, out_t, m, n, k, da, db, cc, alpha, beta)
+    split2 = api.gemm(in_t, out_t, m, n, k, da, db, cc, alpha, beta)
+    api.check_device()
+    assert torch.equal(split1.view(torch.uint8), split2.view(torch.uint8))
+    got = to_host(split1, out_t).reshape(m, n)
+    ref = to_host(whole, out_t).reshape(m, n)
+    if in_t == O.I8:
+        assert np.array_equal(got, ref)
+    pick = np.unique(np.concatenate([[0, 255, 256, m - 257, m - 1],
+                                     np.random.default_rng(seed).integers(0, m, 16)]))
+    c_rows = np.ascontiguousarray(c[pick]).reshape(-1)
+    want = O.gemm(in_t, out_t, pick.size, n, k, np.ascontiguousarray(a[pick]).reshape(-1),
+                  bt.reshape(-1), c_rows, alpha, beta)
+    for res in (got, ref):
+        err = O.max_rel_err(out_t, np.ascontiguousarray(res[pick]).reshape(-1), want)
+        assert 0 <= err <= tolerance(in_t, out_t), err

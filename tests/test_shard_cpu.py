@@ -271,3 +271,45 @@ def test_a_rank_that_leaves_between_steps_is_reported_not_waited_for(tmp_path):
     status, usable = open(tmp_path / "status.txt").read().split("\n")
     assert status.startswith("error"), status
     assert usable == "True"
+
+
+def test_split_tiles_cover_k_exactly_once():
+    """A launch whose last wave is less than half full cuts that wave's tiles in two along K
+    (TileSchedule::splitTiles): every other tile is handed out once as a whole, every split
+    tile as exactly its two halves, to two different pairs, and no pair carries more than one
+    half-tile beyond the whole waves."""
+    import ctypes as C
+    import os
+
+    import numpy as np
+
+    from rocwmma_b200 import _lib
+    lib = C.CDLL(os.path.join(os.path.dirname(_lib.LIB_PATH), "libb200wmma_test.so"))
+    fn = lib.b200wmma_test_tile_split
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_uint32] * 8 + [C.c_void_p] * 3
+    rng = np.random.default_rng(5)
+    cases = [(16, 16, 16, 74), (16, 16, 8, 74), (4, 20, 8, 74), (3, 27, 2, 74), (9, 9, 4, 37)]
+    cases += [(int(rng.integers(1, 40)), int(rng.integers(1, 40)), int(rng.integers(1, 20)),
+               int(rng.integers(2, 80))) for _ in range(100)]
+    checked = 0
+    for tiles_m, cols, band, pairs in cases:
+        tiles = tiles_m * cols
+        rem = tiles % pairs
+        if tiles <= pairs or rem == 0 or 2 * rem > pairs:
+            continue                      # the launcher would not split this one
+        for snake, mirror in ((0, 0), (1, 0), (1, 1)):
+            parts = np.zeros(tiles, np.uint32)
+            whole = np.zeros(tiles, np.uint32)
+            per_pair = np.zeros(pairs, np.uint32)
+            total = fn(tiles_m, cols, 256, band, pairs, snake, mirror, rem, parts.ctypes.data,
+                       whole.ctypes.data, per_pair.ctypes.data)
+            assert total == tiles + rem, (tiles_m, cols, band, pairs, total)
+            assert (whole + (parts == 3)).tolist() == [1] * tiles       # every tile covered once
+            assert int((parts == 3).sum()) == rem and not ((parts != 0) & (parts != 3)).any()
+            assert not ((whole != 0) & (parts != 0)).any()
+            # whole waves for everybody, then at most one half
+            assert per_pair.max() - per_pair.min() <= 1
+            assert per_pair.max() == 2 * (tiles // pairs) + 1
+            checked += 1
+    assert checked >= 30
