@@ -55,9 +55,15 @@ FALLBACK_PEAK_TFLOPS = 1590.0
 REGIONS = 5          # timed regions of K steps each; the median one is reported
 TOLERANCE = 2e-3     # fp16 inputs, fp32 accumulate: max |a-b| / (|a|+|b|+1)
 # DRAM bytes per launch of the GEMM kernel (dram__bytes_read.sum + dram__bytes_write.sum of one
-# profiler capture of an 8192-row launch), quoted -- not measured by this run -- in
-# roofline.traffic together with where it came from.  None = no capture of the current kernel.
-PROFILED_TRAFFIC = None
+# profiler capture of the current kernel at that launch shape), keyed by the rows of A per
+# launch.  Quoted in roofline.traffic -- a benchmark run does not measure it -- together with
+# where it came from; launch shapes without a capture report null.
+PROFILED_TRAFFIC = {
+    8192: 1.219e9,   # 1.092 GB read + 0.127 GB written (algorithmic: 0.403 GB)
+    1024: 0.180e9,   # 168.8 MB read + 11.1 MB written inside the kernel (algorithmic: 0.168 GB)
+}
+TRAFFIC_SOURCE = ("one ncu capture (--set full, --clock-control none) of a launch of this shape, "
+                  "cold L2; quoted from the committed profiler summary, not measured by this run")
 
 
 def measured_peaks():
@@ -390,9 +396,8 @@ def main():
                 "frac_of_sustained_peak": (kernel_tflops / sustained_peak
                                            if sustained_peak else None),
                 "timed_region_ms": ms_total,
-                "traffic": (PROFILED_TRAFFIC["bytes_per_launch"]
-                            if PROFILED_TRAFFIC and world == 1 else None),
-                "traffic_source": (PROFILED_TRAFFIC["source"] if PROFILED_TRAFFIC and world == 1
+                "traffic": PROFILED_TRAFFIC.get(m_local),
+                "traffic_source": (TRAFFIC_SOURCE if m_local in PROFILED_TRAFFIC
                                    else "not captured for this launch shape"),
                 "peak_source": peak_src, "kernel": "gemm_tcgen05_pair_kernel<half,half,float>",
                 "algorithmic_flops_per_launch": 2.0 * m_local * N * K}
