@@ -85,6 +85,23 @@ namespace rocwmma
             return done != 0;
         }
 
+        // Non-blocking form: reports whether the phase has completed and returns at once
+        // (mbarrier.try_wait may suspend the thread for a system-dependent time, microseconds,
+        // when it has not).  For polls whose outcome is only looked at later.
+        ROCWMMA_DEVICE inline bool mbar_test_wait(uint64_t* bar, uint32_t parity)
+        {
+            uint32_t done;
+            asm volatile("{\n\t"
+                         ".reg .pred P;\n\t"
+                         "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+                         "selp.u32 %0, 1, 0, P;\n\t"
+                         "}"
+                         : "=r"(done)
+                         : "r"(smem_addr(bar)), "r"(parity)
+                         : "memory");
+            return done != 0;
+        }
+
         // Codes recorded next to the abort flag: which kind of wait ran out.
         enum WaitCode : uint32_t
         {

@@ -403,6 +403,293 @@ namespace
         }
     }
 
+    // ---- fp32 with the multiplications taken off the adding warp ------------------------------
+    // The floor of a bit-identical row sum is its chain of k dependent additions: 44 us for
+    // k = 16384 measured on the bare chain, 58 us with one shared-memory load per addend
+    // issued between the additions.  Here the work of a 32-row group is spread over five warps:
+    //   * four multiplier warps take the tiles of the ring in turn; a thread reads its row's
+    //     32 values of A and the tile's 32 values of x, multiplies (rounded, as the host
+    //     routine does) and writes the products back IN PLACE, then arrives on the slot's
+    //     `prod` barrier;
+    //   * the chain warp waits for `prod`, reads its row's 32 products and adds them in column
+    //     order -- one shared-memory load and one addition per column, the loads of tile t + 1
+    //     and the poll for tile t + 2 issued between the additions of tile t -- and hands the
+    //     slot back to the producer.
+    // Block = ROWS / 32 chain warps, four times as many multiplier warps, one producer warp.
+    // Measured: 80 us for a 2048- or 4096-row shard (88-93 us with everything on the adding
+    // warp).  What holds it there is no longer the adding warp -- its polls find the ring empty --
+    // but the rate at which one SM's TMA unit delivers tiles: a tile is 32 box rows (one per
+    // column of A, ROWS * 4 bytes each), and it takes ~300 cycles whether those rows are 128
+    // or 256 bytes long, 2 or 4 multiplier warps wait for it, and whichever form adds it up.
+    // (The polls use mbarrier.try_wait on purpose: when a tile has not arrived it suspends the
+    // warp for a while instead of returning at once, and the non-blocking test_wait in its
+    // place made the single-warp form 20 % slower.)
+    template <uint32_t ROWS, uint32_t STAGES>
+    struct ChainGeometry
+    {
+        static constexpr uint32_t COLS       = 32;
+        static constexpr uint32_t TILE_BYTES = ROWS * COLS * 4;
+        static constexpr uint32_t SLOT_BYTES = TILE_BYTES + 128; // + the tile's values of x
+        static constexpr uint32_t GROUPS     = ROWS / 32;
+        static constexpr uint32_t MULT       = 4; // multiplier warps per 32-row group
+        static constexpr uint32_t THREADS    = ((1 + MULT) * GROUPS + 1) * 32;
+        struct Control
+        {
+            uint64_t   full[STAGES]; // TMA data has landed
+            uint64_t   prod[STAGES]; // products are in place
+            uint64_t   empty[STAGES]; // the chain warps have read them
+            AbortState abort;
+        };
+        static constexpr uint32_t SMEM_BYTES = STAGES * SLOT_BYTES + 128 + sizeof(Control);
+    };
+
+    template <uint32_t ROWS, uint32_t STAGES>
+    __global__ void __launch_bounds__(ChainGeometry<ROWS, STAGES>::THREADS, 2)
+        gemvChainKernel(const __grid_constant__ CUtensorMap tmapA,
+                        const __grid_constant__ CUtensorMap tmapX, uint32_t m, uint32_t k,
+                        float const* yIn, float* yOut, float alpha, float beta, uint32_t* status)
+    {
+        using G       = ChainGeometry<ROWS, STAGES>;
+        using Control = typename G::Control;
+        constexpr uint32_t COLS = G::COLS, TILE_BYTES = G::TILE_BYTES, SLOT_BYTES = G::SLOT_BYTES;
+        constexpr uint32_t GROUPS = G::GROUPS, MULT = G::MULT;
+        extern __shared__ uint8_t smemRaw[];
+        const uint32_t            raw   = smem_addr(smemRaw);
+        uint8_t*                  tiles = smemRaw + ((128u - (raw & 127u)) & 127u);
+        Control* ctl = reinterpret_cast<Control*>(tiles + STAGES * SLOT_BYTES);
+
+        const uint32_t warp  = threadIdx.x / 32u, lane = threadIdx.x % 32u;
+        const uint32_t row0  = blockIdx.x * ROWS;
+        const uint32_t numKB = (k + COLS - 1) / COLS;
+
+        if(threadIdx.x == 0)
+        {
+            for(uint32_t s = 0; s < STAGES; ++s)
+            {
+                mbar_init(&ctl->full[s], 1);
+                mbar_init(&ctl->prod[s], ROWS);
+                mbar_init(&ctl->empty[s], ROWS);
+            }
+            ctl->abort.flag = 0;
+            ctl->abort.code = 0;
+            mbar_init_fence();
+            tma_prefetch_descriptor(&tmapA);
+            tma_prefetch_descriptor(&tmapX);
+        }
+        __syncthreads();
+        grid_dependency_wait();
+        grid_launch_dependents();
+
+        struct RingPos
+        {
+            uint32_t slot, phase;
+            __device__ void advance()
+            {
+                if(++slot == STAGES)
+                {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+        };
+
+        if(warp == (1u + MULT) * GROUPS)
+        {
+            // ---- producer: one thread, two TMA loads per tile ----
+            if(elect_one())
+            {
+                RingPos  pos{0u, 0u};
+                uint32_t kb = 0;
+                for(; kb < numKB; ++kb, pos.advance())
+                {
+                    if(!mbar_wait(&ctl->empty[pos.slot], pos.phase ^ 1u, &ctl->abort,
+                                  WAIT_STAGE_EMPTY))
+                        break;
+                    uint8_t* slot = tiles + pos.slot * SLOT_BYTES;
+                    mbar_expect_tx(&ctl->full[pos.slot], SLOT_BYTES);
+                    tma_load_2d(slot, &tmapA, &ctl->full[pos.slot], int32_t(row0),
+                                int32_t(kb * COLS));
+                    tma_load_1d(slot + TILE_BYTES, &tmapX, &ctl->full[pos.slot],
+                                int32_t(kb * COLS));
+                }
+                if(kb < numKB)
+                {
+                    // leaving early: copies already issued get a bounded time to land
+                    const uint32_t pending = kb < STAGES ? kb : STAGES;
+                    for(uint32_t j = 0; j < pending; ++j)
+                    {
+                        const uint32_t  prev  = kb - 1 - j;
+                        const long long start = clock64();
+                        while(!mbar_try_wait(&ctl->full[prev % STAGES], (prev / STAGES) & 1u)
+                              && clock64() - start < 2000000ll)
+                        {
+                        }
+                    }
+                }
+            }
+        }
+        else if(warp >= GROUPS)
+        {
+            // ---- multiplier warps: tiles of one parity, rows of one 32-row group ----
+            const uint32_t mw = warp - GROUPS, group = mw / MULT, turn = mw % MULT;
+            const uint32_t r  = group * 32u + lane;
+            RingPos        pos{0u, 0u};
+            for(uint32_t i = 0; i < turn; ++i)
+                pos.advance();
+            for(uint32_t kb = turn; kb < numKB; kb += MULT)
+            {
+                if(!mbar_wait(&ctl->full[pos.slot], pos.phase, &ctl->abort, WAIT_STAGE_FULL))
+                    break;
+                float*               tile = reinterpret_cast<float*>(tiles + pos.slot * SLOT_BYTES);
+                Vec<float, 4> const* xs   = reinterpret_cast<Vec<float, 4> const*>(
+                    tiles + pos.slot * SLOT_BYTES + TILE_BYTES);
+                float av[COLS], xv[COLS];
+#pragma unroll
+                for(uint32_t j = 0; j < COLS; j += 4u)
+                {
+                    const Vec<float, 4> q = xs[j / 4u]; // same address in every lane: broadcast
+#pragma unroll
+                    for(uint32_t e = 0; e < 4u; ++e)
+                        xv[j + e] = q.v[e];
+                }
+#pragma unroll
+                for(uint32_t j = 0; j < COLS; ++j)
+                    av[j] = tile[j * ROWS + r];
+#pragma unroll
+                for(uint32_t j = 0; j < COLS; ++j)
+                    tile[j * ROWS + r] = mulRn(av[j], xv[j]);
+                // the slot will be overwritten by a TMA load later: order these generic-proxy
+                // writes before that async-proxy write, then release the products to the waiter
+                fence_async_shared();
+                mbar_arrive(&ctl->prod[pos.slot]);
+                for(uint32_t i = 0; i < MULT; ++i)
+                    pos.advance();
+            }
+        }
+        else
+        {
+            // ---- chain warps: one row per thread, columns in ascending order ----
+            const uint32_t r        = warp * 32u + lane;
+            const uint32_t numFull  = k / COLS;
+            float          acc      = 0.0f;
+            RingPos        toLoad{0u, 0u}, toRelease{0u, 0u};
+            bool           ok       = true;
+            auto loadProducts = [&](uint32_t s, float (&pv)[COLS]) {
+                float const* tile = reinterpret_cast<float const*>(tiles + s * SLOT_BYTES);
+#pragma unroll
+                for(uint32_t j = 0; j < COLS; ++j)
+                    pv[j] = tile[j * ROWS + r];
+            };
+            auto waitProd = [&](RingPos const& at) -> bool {
+                return mbar_wait(&ctl->prod[at.slot], at.phase, &ctl->abort, WAIT_STAGE_FULL);
+            };
+            auto releaseSlot = [&]() {
+                mbar_arrive(&ctl->empty[toRelease.slot]);
+                toRelease.advance();
+            };
+            // one step: adds tile t (`cur`, in registers), loads tile t + 1 (whose arrival was
+            // established before the trip) into `next`, polls for a tile four further on
+            RingPos toPoll{0u, 0u};
+            auto    step = [&](float const (&cur)[COLS], float (&next)[COLS], bool& allArrived) {
+                float const* tile
+                    = reinterpret_cast<float const*>(tiles + toLoad.slot * SLOT_BYTES);
+                toLoad.advance();
+#pragma unroll
+                for(uint32_t j = 0; j < COLS; ++j)
+                {
+                    acc     = addRn(acc, cur[j]);
+                    next[j] = tile[j * ROWS + r];
+                    if(j == COLS / 4u)
+                        allArrived
+                            = mbar_try_wait(&ctl->prod[toPoll.slot], toPoll.phase) && allArrived;
+                }
+                toPoll.advance();
+                releaseSlot(); // tile t: its products were consumed by the additions above
+            };
+            float pA[COLS], pB[COLS];
+            if(numFull > 0u)
+            {
+                ok = waitProd(toLoad);
+                if(ok)
+                {
+                    loadProducts(toLoad.slot, pA);
+                    toLoad.advance();
+                }
+                // steady state: a trip of four steps starting at tile t loads tiles
+                // t + 1 .. t + 4 and polls t + 5 .. t + 8
+                uint32_t t = 0;
+                toPoll     = toLoad;
+                for(uint32_t i = 0; i < 4u; ++i)
+                    toPoll.advance();
+                bool arrivedAll = false;
+                for(; ok && t + 8u < numFull; t += 4u)
+                {
+                    if(!arrivedAll)
+                    {
+                        RingPos w = toLoad;
+                        for(uint32_t i = 0; ok && i < 4u; ++i)
+                        {
+                            ok = waitProd(w);
+                            w.advance();
+                        }
+                        if(!ok)
+                            break;
+                    }
+                    bool all = true;
+                    step(pA, pB, all);
+                    step(pB, pA, all);
+                    step(pA, pB, all);
+                    step(pB, pA, all);
+                    arrivedAll = all;
+                }
+                // the last full tiles, one simple step each (t is a multiple of 4: tile t is
+                // in pA)
+                for(uint32_t u = t; ok && u < numFull; ++u)
+                {
+                    const bool even        = ((u & 1u) == 0u);
+                    float const(&cur)[COLS] = even ? pA : pB;
+                    float(&next)[COLS]      = even ? pB : pA;
+                    if(u + 1u < numFull)
+                    {
+                        ok = waitProd(toLoad);
+                        if(!ok)
+                            break;
+                        loadProducts(toLoad.slot, next);
+                        toLoad.advance();
+                    }
+#pragma unroll
+                    for(uint32_t j = 0; j < COLS; ++j)
+                        acc = addRn(acc, cur[j]);
+                    releaseSlot();
+                }
+            }
+            if(ok && numFull < numKB)
+            {
+                // the partial last tile: columns beyond k hold 0 * 0 and must not enter the sum
+                // (adding +0 could turn a -0 into +0)
+                const uint32_t valid = k - numFull * COLS;
+                float          pv[COLS];
+                if(waitProd(toLoad))
+                {
+                    loadProducts(toLoad.slot, pv);
+#pragma unroll
+                    for(uint32_t j = 0; j < COLS; ++j)
+                        if(j < valid)
+                            acc = addRn(acc, pv[j]);
+                    releaseSlot();
+                }
+            }
+            if(row0 + r < m && ctl->abort.flag == 0u)
+                yOut[row0 + r] = addRn(mulRn(alpha, acc), mulRn(beta, yIn[row0 + r]));
+        }
+        __syncthreads();
+        if(threadIdx.x == 0 && ctl->abort.flag != 0u && status != nullptr)
+        {
+            atomicExch(&status[1], ctl->abort.code);
+            atomicExch(&status[0], 1u);
+        }
+    }
+
     // Same arithmetic with plain loads, for operands TMA cannot address.
     template <typename T>
     __global__ void gemvPlainKernel(uint32_t m, uint32_t k, T const* __restrict__ a,
@@ -469,6 +756,53 @@ namespace
             mapX, m, k, yIn, yOut, alpha, beta, b200wmma::deviceStatusWord()));
     }
 
+    template <uint32_t ROWS, uint32_t STAGES>
+    int launchChain(uint32_t m, uint32_t k, float const* a, float const* x, float const* yIn,
+                    float* yOut, float alpha, float beta, uint32_t lda, cudaStream_t stream)
+    {
+        using G = ChainGeometry<ROWS, STAGES>;
+        b200wmma::EncodeFn encode = b200wmma::tensorMapEncoder();
+        if(!encode)
+            return B200WMMA_ERR_CUDA;
+        CUtensorMap mapA, mapX;
+        {
+            cuuint64_t dims[2]    = {m, k};
+            cuuint64_t strides[1] = {cuuint64_t(lda) * 4u};
+            cuuint32_t box[2]     = {ROWS, G::COLS};
+            cuuint32_t estr[2]    = {1, 1};
+            if(encode(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(a), dims,
+                      strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+               != CUDA_SUCCESS)
+                return B200WMMA_ERR_CUDA;
+        }
+        {
+            cuuint64_t dims[1]    = {k};
+            cuuint64_t strides[1] = {0}; // a one-dimensional map has no strides; never read
+            cuuint32_t box[1]     = {G::COLS};
+            cuuint32_t estr[1]    = {1};
+            if(encode(&mapX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 1, const_cast<float*>(x), dims,
+                      strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                      CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+               != CUDA_SUCCESS)
+                return B200WMMA_ERR_CUDA;
+        }
+        auto        kernel = gemvChainKernel<ROWS, STAGES>;
+        static bool attrDone[64] = {};
+        int         dev          = 0;
+        B200WMMA_CUDA_TRY(cudaGetDevice(&dev));
+        if(dev < 0 || dev >= 64 || !attrDone[dev])
+        {
+            B200WMMA_CUDA_TRY(cudaFuncSetAttribute(
+                kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(G::SMEM_BYTES)));
+            if(dev >= 0 && dev < 64)
+                attrDone[dev] = true;
+        }
+        return b200wmma::cudaToStatus(b200wmma::launchOverlapped(
+            kernel, dim3((m + ROWS - 1) / ROWS), dim3(G::THREADS), G::SMEM_BYTES, stream, mapA,
+            mapX, m, k, yIn, yOut, alpha, beta, b200wmma::deviceStatusWord()));
+    }
+
     template <typename T>
     int run(uint32_t m, uint32_t k, T const* a, T const* x, T const* yIn, T* yOut, T alpha, T beta,
             uint32_t lda, cudaStream_t stream)
@@ -497,6 +831,23 @@ namespace
         bool narrow = (m + 63u) / 64u < uint32_t(sms);
         if(rowsEnv == 32u || rowsEnv == 64u)
             narrow = rowsEnv == 32u;
+        if constexpr(sizeof(T) == 4)
+        {
+            // fp32 with at most one 32-row block per SM (a row shard of a many-GPU run): the
+            // launch takes as long as one row's ordered sum, so the multiplications go to
+            // warps of their own (gemvChainKernel: 81 vs 93 us for 2048 and 4096 rows).  With
+            // more rows than that the kernel is bandwidth-bound and the second pass through
+            // shared memory costs more than it saves (8192 rows: 109 vs 95 us; 16384: 181 vs
+            // 165).  B200WMMA_GEMV_FORM=single|chain forces one form (comparison).
+            const char* form = getenv("B200WMMA_GEMV_FORM");
+            const bool forced = form && form[0] == 'c';
+            if(forced || (!(form && form[0] == 's') && (m + 31u) / 32u <= uint32_t(sms)))
+            {
+                if(narrow)
+                    return launchChain<32, 24>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
+                return launchChain<64, 12>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
+            }
+        }
         if(narrow)
             return launchStream<T, 32, 24>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
         return launchStream<T, 64, 12>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
