@@ -22,8 +22,9 @@ host routine where it was built -- and the largest relative error (the reference
 is reported next to the tolerance.  GEMMs report TFLOP/s = 2 M N K / time against the measured
 dense bf16 tensor peak scaled per type; GEMV and DLRM report algorithmic bytes / time against
 the measured copy bandwidth.  Timing: CUDA events over `iters` back-to-back launches after
-3 warm-ups; a working set that fits in the 126 MB L2 is timed launch by launch with an L2
-flush (a 256 MiB read) in between.
+warm-ups; when a configuration's working set fits in the 126 MB L2 (the 1024^3 sample, a
+shard of a many-GPU run) the launches rotate through enough copies of its buffers that every
+launch reads its operands from DRAM.
 
 Under torchrun every configuration is split over the ranks as rocwmma_b200.shard says (GEMM
 by rows of A / C / D with B replicated, DLRM by batch, GEMV by rows; no collective in a
@@ -88,45 +89,50 @@ def gen_threads() -> int:
 
 
 L2_BYTES = 126 << 20
-_flush = None
 
 
-def timed(fn, iters, working_set=None):
-    """Per-launch time in ms, the slowest rank's.  A working set larger than the L2 is timed
-    as `iters` back-to-back launches between two device events; a smaller one (the 1024^3
-    sample, a shard of a many-GPU run) would be served from L2, so every launch is then
-    timed on its own with a 256 MiB buffer read in between."""
-    global _flush
-    for _ in range(3):
-        fn()
+def copies_needed(working_set: int) -> int:
+    """How many copies of a configuration's device buffers a timed loop rotates through so that
+    no launch finds its operands in L2: 1 when the working set exceeds the L2 by itself, else
+    enough copies for 2.5 x the L2 between two uses of the same copy."""
+    if working_set > L2_BYTES:
+        return 1
+    return min(64, max(2, -(-int(2.5 * L2_BYTES) // max(1, working_set))))
+
+
+def replicate(count, *tensors):
+    """`count` sets of the given device tensors (set 0 = the originals; None stays None)."""
+    sets = [tensors]
+    for _ in range(count - 1):
+        sets.append(tuple(None if t is None else t.clone() for t in tensors))
+    return sets
+
+
+def timed(fn, iters, copies=1):
+    """Per-launch time in ms, the slowest rank's: `iters` back-to-back launches between two
+    device events (after 3 warm-ups per copy in use).  fn(i) launches on buffer set
+    i % copies; with a working set smaller than the L2 the sets rotate (copies_needed), so
+    that every launch reads its operands from DRAM like the first one would -- and the
+    launches still run back to back, as they would in a pipeline that feeds the kernel new
+    data each time.  Returns (ms, copies)."""
+    iters = max(iters, copies) if copies > 1 else iters
+    for i in range(max(3, copies)):
+        fn(i)
     _barrier()
-    if working_set is None or working_set > L2_BYTES:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        _barrier()
-        total = e0.elapsed_time(e1)
-        flushed = False
-    else:
-        if _flush is None:
-            _flush = torch.zeros(64 << 20, dtype=torch.int32, device="cuda")   # 256 MiB
-        pairs = []
-        for i in range(iters):
-            # evict by READING twice the L2's size: a written buffer would leave the L2 full
-            # of dirty lines whose write-back the timed kernel then pays for
-            _flush.sum()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            fn()
-            e1.record()
-            pairs.append((e0, e1))
-        _barrier()
-        total = sum(a.elapsed_time(b) for a, b in pairs)
-        flushed = True
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    _barrier()
+    total = e0.elapsed_time(e1)
     api.check_device()
-    return _max_over_ranks(total) / iters, flushed
+    return _max_over_ranks(total) / iters, copies
+
+
+def l2_note(copies):
+    return ("working set exceeds L2" if copies == 1
+            else f"{copies} copies of the buffers in rotation (2.5 x L2 between reuses)")
 
 
 def to_device(a: np.ndarray, code: int) -> torch.Tensor:
@@ -231,20 +237,25 @@ def gemm_case(name, in_t, out_t, size, alpha, beta, seed, peak_scale, simple=Fal
     da, db = to_device(a, in_t), to_device(bt, in_t)
     dc = to_device(c, out_t) if c is not None else None
     dd = torch.empty(m * n, dtype=api.torch_dtype(out_t), device="cuda")
-    if simple:
-        fn = lambda: api.gemm_simple(in_t, out_t, m, n, k, da, db, dc, alpha, beta, ROW_MAJOR,  # noqa
-                                     COL_MAJOR, ROW_MAJOR, 16, out=dd)
-    else:
-        fn = lambda: api.gemm(in_t, out_t, m, n, k, da, db, dc, alpha, beta, out=dd)  # noqa: E731
     ws = (m * k + k * n) * _ELEM_BYTES[in_t] + m * n * _ELEM_BYTES[out_t] * (2 if c is not None else 1)
-    ms, flushed = timed(fn, iters, ws)
+    sets = replicate(copies_needed(ws), da, db, dc, dd)
+    if simple:
+        def fn(i):
+            xa, xb, xc, xd = sets[i % len(sets)]
+            api.gemm_simple(in_t, out_t, m, n, k, xa, xb, xc, alpha, beta, ROW_MAJOR, COL_MAJOR,
+                            ROW_MAJOR, 16, out=xd)
+    else:
+        def fn(i):
+            xa, xb, xc, xd = sets[i % len(sets)]
+            api.gemm(in_t, out_t, m, n, k, xa, xb, xc, alpha, beta, out=xd)
+    ms, copies = timed(fn, iters, len(sets))
     work_rows = size if SHARD_WORLD == WORLD else m     # a lone shard counts its own rows only
     tf = 2.0 * work_rows * n * k / ms / 1e9
     peak_bf16, _, src = peaks()
     peak = (peak_bf16 * peak_scale if peak_scale else 40.0) * WORLD
     res = {"config": name, "n_gpus": WORLD, "ms": ms, "value": tf, "unit": "TFLOP/s",
            "partition": f"M-split x{WORLD}, B replicated", "seed": seed,
-           "l2": "flushed between launches" if flushed else "working set exceeds L2",
+           "l2": l2_note(copies),
            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s",
                         "frac": tf / peak, "algorithmic_flops": 2.0 * size * n * k,
                         "peak_source": (f"{src} bf16 tensor peak x {peak_scale} x {WORLD} GPU(s)"
@@ -300,15 +311,19 @@ def gemv_case(size, seed=4, iters=50, check=True):
     y = np.ascontiguousarray(y)
     da, dx, dy = to_device(a, F32), to_device(x, F32), to_device(y, F32)
     out = torch.empty_like(dy)
-    ms, flushed = timed(lambda: api.gemv(F32, m, k, da, dx, dy, 2.1, 2.1, out=out), iters,
-                        m * k * 4)
+    sets = replicate(copies_needed(m * k * 4), da, dx, dy, out)
+
+    def fn(i):
+        xa, xx, xy, xo = sets[i % len(sets)]
+        api.gemv(F32, m, k, xa, xx, xy, 2.1, 2.1, out=xo)
+    ms, copies = timed(fn, iters, len(sets))
     nbytes = size * k * 4 + WORLD * k * 4 + 2 * size * 4
     _, hbm, src = peaks()
     hbm *= WORLD
     gbs = nbytes / ms / 1e6
     res = {"config": f"sgemv {size}^2 fp32 col-major, alpha=beta=2.1", "n_gpus": WORLD, "ms": ms,
            "value": gbs, "unit": "GB/s", "partition": f"row split x{WORLD}, x replicated",
-           "seed": seed, "l2": "flushed between launches" if flushed else "working set exceeds L2",
+           "seed": seed, "l2": l2_note(copies),
            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s",
                         "frac": gbs / hbm, "algorithmic_bytes": nbytes,
                         "peak_source": f"{src} copy bandwidth x {WORLD} GPU(s)"}}
@@ -345,11 +360,11 @@ def dlrm_cases(total_batch, seed=4, iters=20, check=True, which=("fwd", "bwd")):
     pick = np.unique(np.concatenate([np.arange(min(128, batch)),
                                      np.arange(max(0, batch - 128), batch)]))
 
-    def entry(name, ms, flushed, nb):
+    def entry(name, ms, copies, nb):
         gbs = nb / ms / 1e6
         return {"config": name, "n_gpus": WORLD, "ms": ms, "value": gbs, "unit": "GB/s",
                 "partition": f"batch split x{WORLD}", "seed": seed,
-                "l2": "flushed between launches" if flushed else "working set exceeds L2",
+                "l2": l2_note(copies),
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s",
                              "frac": gbs / hbm, "algorithmic_bytes": nb,
                              "peak_source": f"{src} copy bandwidth x {WORLD} GPU(s)"}}
@@ -360,9 +375,14 @@ def dlrm_cases(total_batch, seed=4, iters=20, check=True, which=("fwd", "bwd")):
         r["parity"] = bool(_max_over_ranks(0.0 if (0 <= err <= 2e-3 and exact_ok) else 1.0) == 0.0)
 
     if "fwd" in which:
-        ms, flushed = timed(lambda: api.dlrm_fwd(dx, m, k, batch, out=out), iters,
-                            batch * (m * k + out_len) * 2)
-        r = entry(f"dlrm fwd b={total_batch} 27x128 fp16", ms, flushed,
+        sets = replicate(copies_needed(batch * (m * k + out_len) * 2), dx, out)
+
+        def fwd(i):
+            xx, xo = sets[i % len(sets)]
+            api.dlrm_fwd(xx, m, k, batch, out=xo)
+        ms, copies = timed(fwd, iters, len(sets))
+        del sets
+        r = entry(f"dlrm fwd b={total_batch} 27x128 fp16", ms, copies,
                   total_batch * (m * k + out_len) * 2)
         if check:
             import oracle as O
@@ -375,9 +395,14 @@ def dlrm_cases(total_batch, seed=4, iters=20, check=True, which=("fwd", "bwd")):
             verdict(r, O.max_rel_err(F16, got, want))
         res.append(r)
     if "bwd" in which:
-        ms, flushed = timed(lambda: api.dlrm_bwd(dx, dup, m, k, batch, grad=grad, mlp_grad=mlp),
-                            iters, batch * (2 * m * k + out_len + k) * 2)
-        r = entry(f"dlrm bwd b={total_batch} 27x128 fp16", ms, flushed,
+        sets = replicate(copies_needed(batch * (2 * m * k + out_len + k) * 2), dx, dup, grad, mlp)
+
+        def bwd(i):
+            xx, xu, xg, xm = sets[i % len(sets)]
+            api.dlrm_bwd(xx, xu, m, k, batch, grad=xg, mlp_grad=xm)
+        ms, copies = timed(bwd, iters, len(sets))
+        del sets
+        r = entry(f"dlrm bwd b={total_batch} 27x128 fp16", ms, copies,
                   total_batch * (m * k + out_len + m * k + k) * 2)
         if check:
             import oracle as O
@@ -467,9 +492,9 @@ def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     if WORLD > 1:
         torch.distributed.init_process_group("nccl")
-    only = list(filter(None, args.only.split(",")))
-    if only == ["dlrm"]:
-        only = ["dlrm_fwd", "dlrm_bwd"]
+    only = []
+    for name in filter(None, args.only.split(",")):
+        only += ["dlrm_fwd", "dlrm_bwd"] if name == "dlrm" else [name]
     names = only or (["hgemm"] + EXTRAS)
     rows = []
     for r in run_all(names, args.small, args.iters, not args.no_check, keep_gemm=True):
