@@ -528,6 +528,33 @@ namespace rocwmma
                              "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
                              : "memory");
         }
+        // L2 eviction policies for loads that carry a cache hint: lines fetched with
+        // `evict_last` are kept in preference to others (an operand many blocks come back to),
+        // lines fetched with `evict_first` are the first to go (an operand that streams past).
+        ROCWMMA_DEVICE inline uint64_t l2_policy_evict_last()
+        {
+            uint64_t p;
+            asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+            return p;
+        }
+        ROCWMMA_DEVICE inline uint64_t l2_policy_evict_first()
+        {
+            uint64_t p;
+            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+            return p;
+        }
+        // tma_load_2d_pair with an L2 cache hint (a policy from the functions above).
+        ROCWMMA_DEVICE inline void tma_load_2d_pair_hint(void* dst, void const* tensorMap,
+                                                         uint32_t barClusterAddr, int32_t x,
+                                                         int32_t y, uint64_t policy)
+        {
+            asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global"
+                         ".mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(
+                             smem_addr(dst)),
+                         "l"(reinterpret_cast<uint64_t>(tensorMap)), "r"(barClusterAddr), "r"(x),
+                         "r"(y), "l"(policy)
+                         : "memory");
+        }
         // Completion of all pair MMAs issued so far arrives (one count) on the barrier at
         // the same shared-memory offset in every block named in ctaMask.
         ROCWMMA_DEVICE inline void mma_commit_pair(uint64_t* bar, uint16_t ctaMask)

@@ -86,6 +86,7 @@ namespace
         uint32_t    tailCols, bnTail; // ... followed by tailCols columns of width bnTail (0: none)
         uint32_t    snake, mirror; // pair kernel: tile order (TileSchedule)
         uint32_t    prefetch; // pair kernel: k-blocks of the first tile to request into L2 early
+        uint32_t    l2Hints; // pair kernel: bit 0 = A evict_last, bit 1 = B evict_first
         uint32_t    stagedTail; // pair kernel: a block's last tile leaves through the idle ring
         uint32_t    splitTiles; // pair kernel: tiles of the last wave cut in two along K
         float*      splitWs; // ... their partial accumulators (raw 32-bit values)
@@ -95,17 +96,25 @@ namespace
     // One operand tile for one K block.  K-major: one TMA box of `rows` rows x 128 bytes of
     // K.  MN-major: boxes of BK K-rows x 128 bytes of M/N, one per 128 bytes of the tile's
     // M/N extent, stacked in shared memory.  Returns the bytes that will arrive.
+    // `policy`: an L2 eviction policy for the pair form (0: none).
     template <typename InT, bool PAIR>
     __device__ inline uint32_t loadOperandTile(uint8_t* dst, void const* tmap, uint64_t* bar,
                                                uint32_t barClusterAddr, bool mnMajor,
-                                               uint32_t mnOrigin, uint32_t rows, uint32_t k0)
+                                               uint32_t mnOrigin, uint32_t rows, uint32_t k0,
+                                               uint64_t policy = 0)
     {
         constexpr uint32_t BK = ROW_BYTES / sizeof(InT); // K elements per ring slot
         constexpr uint32_t W  = ROW_BYTES / sizeof(InT); // M/N elements per 128 bytes
         if(!mnMajor)
         {
             if constexpr(PAIR)
-                tma_load_2d_pair(dst, tmap, barClusterAddr, int32_t(k0), int32_t(mnOrigin));
+            {
+                if(policy != 0)
+                    tma_load_2d_pair_hint(dst, tmap, barClusterAddr, int32_t(k0), int32_t(mnOrigin),
+                                          policy);
+                else
+                    tma_load_2d_pair(dst, tmap, barClusterAddr, int32_t(k0), int32_t(mnOrigin));
+            }
             else
                 tma_load_2d(dst, tmap, bar, int32_t(k0), int32_t(mnOrigin));
             return rows * ROW_BYTES;
@@ -115,7 +124,14 @@ namespace
         {
             uint8_t* d = dst + a * (BK * ROW_BYTES);
             if constexpr(PAIR)
-                tma_load_2d_pair(d, tmap, barClusterAddr, int32_t(mnOrigin + a * W), int32_t(k0));
+            {
+                if(policy != 0)
+                    tma_load_2d_pair_hint(d, tmap, barClusterAddr, int32_t(mnOrigin + a * W),
+                                          int32_t(k0), policy);
+                else
+                    tma_load_2d_pair(d, tmap, barClusterAddr, int32_t(mnOrigin + a * W),
+                                     int32_t(k0));
+            }
             else
                 tma_load_2d(d, tmap, bar, int32_t(mnOrigin + a * W), int32_t(k0));
         }
@@ -1299,6 +1315,16 @@ namespace
             {
                 uint32_t it = 0;
                 bool     ok = true;
+                // A column tile of B is used by the pairs of one wave and then not before the
+                // next raster band (or the next launch): a B too large to stay in L2 anyway is
+                // fetched "evict first", so that its stream does not push the rows of A, which
+                // every wave of a band comes back to, and the freshly written D out of L2.
+                // Measured (20 launches back to back after an idle gap, same box, alternating
+                // runs): 8192^3 751.7 -> 739.2 us, 4096-row shard 374.6 -> 366.5, 2048 rows
+                // 186.9 -> 182.6, 1024 rows 97.1 -> 95.2; 4096^3 unchanged.  Marking A
+                // "evict last" as well changes nothing measurable (bit 0).
+                const uint64_t policyA = (p.l2Hints & 1u) ? l2_policy_evict_last() : 0;
+                const uint64_t policyB = (p.l2Hints & 2u) ? l2_policy_evict_first() : 0;
                 for(uint32_t i = 0; ok; ++i)
                 {
                     uint32_t tm, col0, width, part, ways, splitIndex;
@@ -1326,10 +1352,10 @@ namespace
                             mbar_expect_tx(&ctl->full[s], 2u * pairSlotBytes); // both blocks
                         const uint32_t leaderFull = map_to_cta(smem_addr(&ctl->full[s]), 0);
                         loadOperandTile<InT, true>(slot, &tmapA, nullptr, leaderFull, p.aMN != 0u,
-                                                   uint32_t(rowA), 128u, kb * BK);
+                                                   uint32_t(rowA), 128u, kb * BK, policyA);
                         loadOperandTile<InT, true>(slot + P_A_BYTES, mapB, nullptr, leaderFull,
                                                    p.bMN != 0u, uint32_t(rowB), width / 2u,
-                                                   kb * BK);
+                                                   kb * BK, policyB);
                     }
                 }
             }
@@ -1682,7 +1708,7 @@ namespace
         GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
                      status, chunkKB, wide, BN, bandEnv ? bandEnv : bandRows(k, sizeof(InT)),
                      useTma ? 1u : 0u,
-                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, nullptr, nullptr};
+                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, nullptr, nullptr};
         CUtensorMap mapA, mapB, mapD;
         {
             int rcD = makeOutputMap(&mapD, outputMapType<OutT>(), sizeof(OutT), d, m, n, ldd);
@@ -1853,6 +1879,12 @@ namespace
                                         : P_STAGES;
             p.snake    = snakeOn ? 1u : 0u;
             p.prefetch = prefKB;
+            {
+                // B200WMMA_GEMM_L2HINT=0..3 forces the cache hints (bit 0: A, bit 1: B; comparison)
+                const char* hintEnv = getenv("B200WMMA_GEMM_L2HINT");
+                const bool  streams = size_t(n) * k * sizeof(InT) > (size_t(48) << 20);
+                p.l2Hints = hintEnv ? uint32_t(hintEnv[0] - '0') & 3u : (streams ? 2u : 0u);
+            }
             if(mirrorOn)
             {
                 // Launches alternate between the forward and the mirrored order, so that each
