@@ -409,18 +409,19 @@ namespace
     // issued between the additions.  Here the work of a 32-row group is spread over five warps:
     //   * four multiplier warps take the tiles of the ring in turn; a thread reads its row's
     //     32 values of A and the tile's 32 values of x, multiplies (rounded, as the host
-    //     routine does) and writes the products back IN PLACE, then arrives on the slot's
-    //     `prod` barrier;
-    //   * the chain warp waits for `prod`, reads its row's 32 products and adds them in column
-    //     order -- one shared-memory load and one addition per column, the loads of tile t + 1
-    //     and the poll for tile t + 2 issued between the additions of tile t -- and hands the
-    //     slot back to the producer.
+    //     routine does) and writes the 32 products of its row side by side into the slot's
+    //     product area (rows 144 bytes apart, so that the 16-byte accesses of a warp spread
+    //     over all banks), then arrives on the slot's `prod` barrier;
+    //   * the chain warp waits for `prod`, reads its row's 32 products with eight 16-byte loads
+    //     and adds them in column order -- the loads of tile t + 1 and the poll for a later
+    //     tile issued between the additions of tile t -- and hands the slot back to the
+    //     producer.
     // Block = ROWS / 32 chain warps, four times as many multiplier warps, one producer warp.
-    // Measured: 80 us for a 2048- or 4096-row shard (88-93 us with everything on the adding
-    // warp).  What holds it there is no longer the adding warp -- its polls find the ring empty --
-    // but the rate at which one SM's TMA unit delivers tiles: a tile is 32 box rows (one per
-    // column of A, ROWS * 4 bytes each), and it takes ~300 cycles whether those rows are 128
-    // or 256 bytes long, 2 or 4 multiplier warps wait for it, and whichever form adds it up.
+    // The chain warp's issue slots are what the launch time hangs on: a micro-benchmark of the
+    // bare chain takes 44.5 us for k = 16384, 57.2 us with one 4-byte shared-memory load per
+    // addend between the additions and 50.6 us with one 16-byte load per four addends -- hence
+    // the row-wise product area -- and with one 32-row group per block the chain warp shares
+    // its scheduler with the producer warp, which sleeps, not with a multiplier warp.
     // (The polls use mbarrier.try_wait on purpose: when a tile has not arrived it suspends the
     // warp for a while instead of returning at once, and the non-blocking test_wait in its
     // place made the single-warp form 20 % slower.)
@@ -429,10 +430,22 @@ namespace
     {
         static constexpr uint32_t COLS       = 32;
         static constexpr uint32_t TILE_BYTES = ROWS * COLS * 4;
-        static constexpr uint32_t SLOT_BYTES = TILE_BYTES + 128; // + the tile's values of x
+        static constexpr uint32_t PROD_STRIDE = COLS + 4; // floats between rows of products
+        static constexpr uint32_t PROD_BYTES  = ROWS * PROD_STRIDE * 4;
+        // the tile as TMA delivers it, the tile's values of x, the products row by row
+        static constexpr uint32_t SLOT_BYTES = TILE_BYTES + 128 + PROD_BYTES;
         static constexpr uint32_t GROUPS     = ROWS / 32;
         static constexpr uint32_t MULT       = 4; // multiplier warps per 32-row group
-        static constexpr uint32_t THREADS    = ((1 + MULT) * GROUPS + 1) * 32;
+        static constexpr uint32_t PRODUCERS  = 2; // producer warps, tiles in turn
+        static constexpr uint32_t THREADS    = ((1 + MULT) * GROUPS + PRODUCERS) * 32;
+        // A wait on a barrier's phase parity is only right while the waiter cannot be a whole
+        // phase ahead of the barrier.  The warp that waits for tile t in a slot must therefore
+        // be the one that handled the slot's previous occupant, tile t - STAGES: otherwise a
+        // multiplier warp that has run ahead can find the slot's barrier still in the phase
+        // of the previous occupant (its copy not landed yet), take that for completion of its
+        // own phase and multiply stale data.
+        static_assert(STAGES % MULT == 0 && STAGES % PRODUCERS == 0,
+                      "ring slots must stay with one multiplier warp and one producer warp");
         struct Control
         {
             uint64_t   full[STAGES]; // TMA data has landed
@@ -444,7 +457,7 @@ namespace
     };
 
     template <uint32_t ROWS, uint32_t STAGES>
-    __global__ void __launch_bounds__(ChainGeometry<ROWS, STAGES>::THREADS, 2)
+    __global__ void __launch_bounds__(ChainGeometry<ROWS, STAGES>::THREADS, 1)
         gemvChainKernel(const __grid_constant__ CUtensorMap tmapA,
                         const __grid_constant__ CUtensorMap tmapX, uint32_t m, uint32_t k,
                         float const* yIn, float* yOut, float alpha, float beta, uint32_t* status)
@@ -452,7 +465,8 @@ namespace
         using G       = ChainGeometry<ROWS, STAGES>;
         using Control = typename G::Control;
         constexpr uint32_t COLS = G::COLS, TILE_BYTES = G::TILE_BYTES, SLOT_BYTES = G::SLOT_BYTES;
-        constexpr uint32_t GROUPS = G::GROUPS, MULT = G::MULT;
+        constexpr uint32_t GROUPS = G::GROUPS, MULT = G::MULT, PROD_STRIDE = G::PROD_STRIDE;
+        constexpr uint32_t PROD_OFFSET = TILE_BYTES + 128;
         extern __shared__ uint8_t smemRaw[];
         const uint32_t            raw   = smem_addr(smemRaw);
         uint8_t*                  tiles = smemRaw + ((128u - (raw & 127u)) & 127u);
@@ -493,32 +507,55 @@ namespace
             }
         };
 
-        if(warp == (1u + MULT) * GROUPS)
+        // Roles.  Warp w issues through scheduler w % 4; with one 32-row group the chain warp
+        // is warp 0 and the first producer warp 4, so that the chain shares its scheduler with
+        // a warp that mostly sleeps: multipliers are warps 1, 2, 3 and 5, further producers 6...
+        constexpr uint32_t NPROD = G::PRODUCERS;
+        uint32_t           producer = ~0u; // index among the producer warps, or none
+        if constexpr(GROUPS == 1u)
         {
-            // ---- producer: one thread, two TMA loads per tile ----
+            if(warp == 4u)
+                producer = 0u;
+            else if(warp >= 6u)
+                producer = warp - 5u;
+        }
+        else if(warp >= (1u + MULT) * GROUPS)
+            producer = warp - (1u + MULT) * GROUPS;
+        if(producer != ~0u)
+        {
+            // ---- producers: one thread each, every NPROD-th tile, two TMA loads per tile ----
+            // (one thread gets through a tile -- barrier test, expect_tx, two TMA instructions --
+            // in ~230 cycles, more than the chain warp needs to add the tile up)
             if(elect_one())
             {
-                RingPos  pos{0u, 0u};
-                uint32_t kb = 0;
-                for(; kb < numKB; ++kb, pos.advance())
+                RingPos pos{0u, 0u};
+                for(uint32_t i = 0; i < producer; ++i)
+                    pos.advance();
+                uint32_t kb = producer;
+                for(; kb < numKB; kb += NPROD)
                 {
                     if(!mbar_wait(&ctl->empty[pos.slot], pos.phase ^ 1u, &ctl->abort,
                                   WAIT_STAGE_EMPTY))
                         break;
                     uint8_t* slot = tiles + pos.slot * SLOT_BYTES;
-                    mbar_expect_tx(&ctl->full[pos.slot], SLOT_BYTES);
+                    mbar_expect_tx(&ctl->full[pos.slot], PROD_OFFSET); // the tile and its x
                     tma_load_2d(slot, &tmapA, &ctl->full[pos.slot], int32_t(row0),
                                 int32_t(kb * COLS));
                     tma_load_1d(slot + TILE_BYTES, &tmapX, &ctl->full[pos.slot],
                                 int32_t(kb * COLS));
+                    for(uint32_t i = 0; i < NPROD; ++i)
+                        pos.advance();
                 }
                 if(kb < numKB)
                 {
-                    // leaving early: copies already issued get a bounded time to land
-                    const uint32_t pending = kb < STAGES ? kb : STAGES;
+                    // leaving early: this thread's copies already issued (tiles kb - NPROD,
+                    // kb - 2 NPROD, ... still in the ring) get a bounded time to land
+                    const uint32_t issued  = (kb - producer) / NPROD;
+                    const uint32_t inRing  = (STAGES + NPROD - 1u) / NPROD;
+                    const uint32_t pending = issued < inRing ? issued : inRing;
                     for(uint32_t j = 0; j < pending; ++j)
                     {
-                        const uint32_t  prev  = kb - 1 - j;
+                        const uint32_t  prev  = kb - NPROD * (1u + j);
                         const long long start = clock64();
                         while(!mbar_try_wait(&ctl->full[prev % STAGES], (prev / STAGES) & 1u)
                               && clock64() - start < 2000000ll)
@@ -530,9 +567,10 @@ namespace
         }
         else if(warp >= GROUPS)
         {
-            // ---- multiplier warps: tiles of one parity, rows of one 32-row group ----
-            const uint32_t mw = warp - GROUPS, group = mw / MULT, turn = mw % MULT;
-            const uint32_t r  = group * 32u + lane;
+            // ---- multiplier warps: every MULT-th tile, rows of one 32-row group ----
+            const uint32_t mw = GROUPS == 1u ? (warp < 4u ? warp - 1u : 3u) : warp - GROUPS;
+            const uint32_t group = mw / MULT, turn = mw % MULT;
+            const uint32_t r     = group * 32u + lane;
             RingPos        pos{0u, 0u};
             for(uint32_t i = 0; i < turn; ++i)
                 pos.advance();
@@ -540,9 +578,11 @@ namespace
             {
                 if(!mbar_wait(&ctl->full[pos.slot], pos.phase, &ctl->abort, WAIT_STAGE_FULL))
                     break;
-                float*               tile = reinterpret_cast<float*>(tiles + pos.slot * SLOT_BYTES);
-                Vec<float, 4> const* xs   = reinterpret_cast<Vec<float, 4> const*>(
+                float const* tile = reinterpret_cast<float const*>(tiles + pos.slot * SLOT_BYTES);
+                Vec<float, 4> const* xs = reinterpret_cast<Vec<float, 4> const*>(
                     tiles + pos.slot * SLOT_BYTES + TILE_BYTES);
+                Vec<float, 4>* out = reinterpret_cast<Vec<float, 4>*>(
+                    tiles + pos.slot * SLOT_BYTES + PROD_OFFSET + r * PROD_STRIDE * 4u);
                 float av[COLS], xv[COLS];
 #pragma unroll
                 for(uint32_t j = 0; j < COLS; j += 4u)
@@ -556,11 +596,17 @@ namespace
                 for(uint32_t j = 0; j < COLS; ++j)
                     av[j] = tile[j * ROWS + r];
 #pragma unroll
-                for(uint32_t j = 0; j < COLS; ++j)
-                    tile[j * ROWS + r] = mulRn(av[j], xv[j]);
-                // the slot will be overwritten by a TMA load later: order these generic-proxy
-                // writes before that async-proxy write, then release the products to the waiter
-                fence_async_shared();
+                for(uint32_t j = 0; j < COLS; j += 4u)
+                {
+                    Vec<float, 4> q;
+#pragma unroll
+                    for(uint32_t e = 0; e < 4u; ++e)
+                        q.v[e] = mulRn(av[j + e], xv[j + e]);
+                    out[j / 4u] = q;
+                }
+                // releases the products to the chain warp; the TMA area of the slot has only
+                // been read, and is not written again before the chain warp has handed the
+                // slot back through `empty`
                 mbar_arrive(&ctl->prod[pos.slot]);
                 for(uint32_t i = 0; i < MULT; ++i)
                     pos.advance();
@@ -574,11 +620,20 @@ namespace
             float          acc      = 0.0f;
             RingPos        toLoad{0u, 0u}, toRelease{0u, 0u};
             bool           ok       = true;
+            auto productsOf = [&](uint32_t s) {
+                return reinterpret_cast<Vec<float, 4> const*>(tiles + s * SLOT_BYTES + PROD_OFFSET
+                                                              + r * PROD_STRIDE * 4u);
+            };
             auto loadProducts = [&](uint32_t s, float (&pv)[COLS]) {
-                float const* tile = reinterpret_cast<float const*>(tiles + s * SLOT_BYTES);
+                Vec<float, 4> const* row = productsOf(s);
 #pragma unroll
-                for(uint32_t j = 0; j < COLS; ++j)
-                    pv[j] = tile[j * ROWS + r];
+                for(uint32_t j = 0; j < COLS; j += 4u)
+                {
+                    const Vec<float, 4> q = row[j / 4u];
+#pragma unroll
+                    for(uint32_t e = 0; e < 4u; ++e)
+                        pv[j + e] = q.v[e];
+                }
             };
             auto waitProd = [&](RingPos const& at) -> bool {
                 return mbar_wait(&ctl->prod[at.slot], at.phase, &ctl->abort, WAIT_STAGE_FULL);
@@ -591,15 +646,20 @@ namespace
             // established before the trip) into `next`, polls for a tile four further on
             RingPos toPoll{0u, 0u};
             auto    step = [&](float const (&cur)[COLS], float (&next)[COLS], bool& allArrived) {
-                float const* tile
-                    = reinterpret_cast<float const*>(tiles + toLoad.slot * SLOT_BYTES);
+                Vec<float, 4> const* row = productsOf(toLoad.slot);
                 toLoad.advance();
 #pragma unroll
                 for(uint32_t j = 0; j < COLS; ++j)
                 {
-                    acc     = addRn(acc, cur[j]);
-                    next[j] = tile[j * ROWS + r];
-                    if(j == COLS / 4u)
+                    acc = addRn(acc, cur[j]);
+                    if(j % 4u == 0u)
+                    {
+                        const Vec<float, 4> q = row[j / 4u];
+#pragma unroll
+                        for(uint32_t e = 0; e < 4u; ++e)
+                            next[j + e] = q.v[e];
+                    }
+                    if(j == COLS / 4u + 1u)
                         allArrived
                             = mbar_try_wait(&ctl->prod[toPoll.slot], toPoll.phase) && allArrived;
                 }
@@ -843,9 +903,13 @@ namespace
             const bool forced = form && form[0] == 'c';
             if(forced || (!(form && form[0] == 's') && (m + 31u) / 32u <= uint32_t(sms)))
             {
-                if(narrow)
-                    return launchChain<32, 24>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
-                return launchChain<64, 12>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
+                if(!narrow)
+                    return launchChain<64, 12>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
+                // a ring of 20 slots fills the shared memory of an SM; with more blocks than
+                // SMs two blocks share one, with 12 slots each
+                if((m + 31u) / 32u <= uint32_t(sms))
+                    return launchChain<32, 20>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
+                return launchChain<32, 12>(m, k, a, x, yIn, yOut, alpha, beta, lda, stream);
             }
         }
         if(narrow)
