@@ -159,6 +159,12 @@ namespace rocwmma
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensorMap))
                          : "memory");
         }
+        // Asks for the 128-byte line that holds `addr` to be brought into L2 (no register
+        // result, nothing to wait for).
+        ROCWMMA_DEVICE inline void prefetch_l2(void const* addr)
+        {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(addr) : "memory");
+        }
         // Asks for the box at (x, y) of `tensorMap` to be brought into L2 (no shared-memory
         // destination, no completion to wait for).  Same alignment rule for x as a load.
         ROCWMMA_DEVICE inline void tma_prefetch_l2_2d(void const* tensorMap, int32_t x, int32_t y)
@@ -235,6 +241,15 @@ namespace rocwmma
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::
                              "l"(reinterpret_cast<uint64_t>(tensorMap)),
                          "r"(smem_addr(src)), "r"(x), "r"(y)
+                         : "memory");
+        }
+        // tma_store_2d with an L2 cache hint (a policy from l2_policy_evict_first / _last).
+        ROCWMMA_DEVICE inline void tma_store_2d_hint(void const* tensorMap, void const* src,
+                                                     int32_t x, int32_t y, uint64_t policy)
+        {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint"
+                         " [%0, {%2, %3}], [%1], %4;" ::"l"(reinterpret_cast<uint64_t>(tensorMap)),
+                         "r"(smem_addr(src)), "r"(x), "r"(y), "l"(policy)
                          : "memory");
         }
         // Same, but adds the box to global memory (element type of the tensor map; the adds
@@ -542,6 +557,16 @@ namespace rocwmma
             uint64_t p;
             asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
             return p;
+        }
+        // tma_load_2d with an L2 cache hint (a policy from the functions above).
+        ROCWMMA_DEVICE inline void tma_load_2d_hint(void* dst, void const* tensorMap, uint64_t* bar,
+                                                    int32_t x, int32_t y, uint64_t policy)
+        {
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                         ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(smem_addr(dst)),
+                         "l"(reinterpret_cast<uint64_t>(tensorMap)), "r"(smem_addr(bar)), "r"(x),
+                         "r"(y), "l"(policy)
+                         : "memory");
         }
         // tma_load_2d_pair with an L2 cache hint (a policy from the functions above).
         ROCWMMA_DEVICE inline void tma_load_2d_pair_hint(void* dst, void const* tensorMap,

@@ -86,8 +86,11 @@ namespace
         uint32_t    tailCols, bnTail; // ... followed by tailCols columns of width bnTail (0: none)
         uint32_t    snake, mirror; // pair kernel: tile order (TileSchedule)
         uint32_t    prefetch; // pair kernel: k-blocks of the first tile to request into L2 early
-        uint32_t    l2Hints; // pair kernel: bit 0 = A evict_last, bit 1 = B evict_first
+        uint32_t    l2Hints; // pair kernel: bit 0 = A evict_last, bit 1 = B evict_first, bit 2 = D
+                             // (written once) evict_first
         uint32_t    stagedTail; // pair kernel: a block's last tile leaves through the idle ring
+        uint32_t    cViaTma; // pair kernel, beta != 0: bit 0 = C comes in through shared memory by
+                             // TMA, bit 1 = C and D pass through L2 marked "evict first"
         uint32_t    splitTiles; // pair kernel: tiles of the last wave cut in two along K
         float*      splitWs; // ... their partial accumulators (raw 32-bit values)
         uint32_t*   splitCtr; // ... and one arrival counter per split tile and block of the pair
@@ -274,6 +277,23 @@ namespace
                          : "memory");
     }
 
+    // stVec with an L2 cache hint (a policy made by createpolicy).
+    template <uint32_t BYTES>
+    __device__ inline void stVecHint(void* dst, void const* src, uint64_t policy)
+    {
+        uint32_t const* v = static_cast<uint32_t const*>(src);
+        if constexpr(BYTES == 32)
+            asm volatile("st.global.L2::cache_hint.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8}, %9;" ::"l"(
+                             dst),
+                         "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]),
+                         "r"(v[6]), "r"(v[7]), "l"(policy)
+                         : "memory");
+        else
+            asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1,%2,%3,%4}, %5;" ::"l"(dst),
+                         "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "l"(policy)
+                         : "memory");
+    }
+
     // Stores (and optionally reads C for) 32 consecutive columns of one output row.
     template <typename OutT, typename CompT, uint32_t VBYTES>
     __device__ inline void epilogueRowV(uint32_t const (&raw)[32], GemmParams const& p,
@@ -288,6 +308,10 @@ namespace
         OutT*              dRow = static_cast<OutT*>(p.d) + size_t(row) * p.ldd;
         const bool         readC = useC && (mode == EPI_WHOLE || mode == EPI_LAST);
         const bool         readD = CAN_CHUNK && (mode == EPI_MIDDLE || mode == EPI_LAST);
+        // a large D that is written once (not a running sum) passes through L2 marked
+        // "evict first", so that it does not push out operand tiles other blocks come back to
+        const bool     hintD = (p.l2Hints & 4u) != 0u && (mode == EPI_WHOLE || mode == EPI_LAST);
+        const uint64_t policyD = hintD ? l2_policy_evict_first() : 0;
 #pragma unroll
         for(uint32_t v = 0; v < 32 / VEC; ++v)
         {
@@ -354,7 +378,12 @@ namespace
                 out[e] = fromCompute<OutT, CompT>(r);
             }
             if(whole)
-                stVec<VBYTES>(dRow + col, out);
+            {
+                if(hintD)
+                    stVecHint<VBYTES>(dRow + col, out, policyD);
+                else
+                    stVec<VBYTES>(dRow + col, out);
+            }
             else
                 for(uint32_t e = 0; e < VEC; ++e)
                     if(col + e < p.n)
@@ -738,6 +767,157 @@ namespace
         return true;
     }
 
+    // ---- beta != 0: C comes in through shared memory as well -------------------------------
+    // A row epilogue reads C with one row per thread and can keep one or two 32-column
+    // groups of it in flight (registers), so every group costs a memory round trip: the drain
+    // of a 128 x 256 fp32 tile took about as long as the tile's MMAs (4096^3 bf16 -> fp32:
+    // 3.5 tiles per pair, beta = -1 cost 15 us of 113; 8192^3: 66 us of 776; one tile alone
+    // 9 us).  Here one thread asks the TMA for the 128-row x 32-column box of C two groups
+    // ahead of its use, into the staging buffer that the TMA store of the group before has
+    // just read; the 128 epilogue threads then combine accumulator and C IN PLACE (each
+    // thread reads and overwrites the same 16-byte pieces, in the swizzled order both TMA
+    // directions use) and the box leaves by a TMA store.  Rows and columns beyond m and n
+    // arrive as zeros and are clipped on the way out.  The first two boxes of a tile are
+    // requested before the wait for its accumulator.
+    template <typename OutT, typename CompT>
+    __device__ inline bool drainAccumulatorTmaC(uint64_t* accFullBar, uint32_t accPh,
+                                                AbortState* abort, uint32_t taddrRowBase,
+                                                CUtensorMap const* tmapC,
+                                                CUtensorMap const* tmapD, uint8_t* staging,
+                                                uint64_t* cFull, uint32_t& stagedGroups,
+                                                CompT alpha, CompT beta, uint32_t rowInTile,
+                                                uint32_t tileRow0, uint32_t colBase, bool leader,
+                                                uint32_t bnTile, bool hintCD)
+    {
+        constexpr uint32_t ROW_B     = 32 * sizeof(OutT); // bytes of one staged row (128 or 64)
+        constexpr uint32_t VEC       = 16 / sizeof(OutT); // elements per 16-byte piece
+        constexpr uint32_t CHUNKS    = ROW_B / 16;
+        constexpr uint32_t BOX_BYTES = 128 * ROW_B;
+        const uint32_t     groups    = bnTile / 32u;
+        uint32_t           requested = 0; // leader: boxes of this tile asked for so far
+        // C is read once and D written once: both pass through L2 marked "evict first", so
+        // that they do not push out the operand tiles that other blocks come back to
+        // (B200WMMA_GEMM_CD_HINT=0 leaves them unmarked, for comparison)
+        const uint64_t streamPolicy = (leader && hintCD) ? l2_policy_evict_first() : 0;
+        auto requestBox = [&](uint32_t g, uint32_t count) {
+            const uint32_t b = count & 1u;
+            mbar_expect_tx(&cFull[b], BOX_BYTES);
+            if(hintCD)
+                tma_load_2d_hint(staging + b * STG_BYTES, tmapC, &cFull[b],
+                                 int32_t(colBase + g * 32u), int32_t(tileRow0), streamPolicy);
+            else
+                tma_load_2d(staging + b * STG_BYTES, tmapC, &cFull[b],
+                            int32_t(colBase + g * 32u), int32_t(tileRow0));
+            ++requested;
+        };
+        // leaving early: boxes asked for and not yet consumed get a bounded time to land
+        auto settle = [&](uint32_t firstGroup, uint32_t firstCount) {
+            if(!leader)
+                return;
+            for(uint32_t g = firstGroup; g < requested; ++g)
+            {
+                const uint32_t  count = firstCount + (g - firstGroup);
+                const long long start = clock64();
+                while(!mbar_try_wait(&cFull[count & 1u], (count >> 1) & 1u)
+                      && clock64() - start < 2000000ll)
+                {
+                }
+            }
+        };
+        if(leader)
+        {
+            tma_store_wait_read<0>(); // the previous tile's stores have read both buffers
+            requestBox(0u, stagedGroups);
+            if(groups > 1u)
+                requestBox(1u, stagedGroups + 1u);
+        }
+        // all 128 epilogue threads must take the same way out: the barriers below have no
+        // time limit of their own
+        const bool ready = mbar_wait(accFullBar, accPh, abort, WAIT_ACC_FULL);
+        if(!named_barrier_all(1, EPI_THREADS, ready))
+        {
+            settle(0u, stagedGroups);
+            return false;
+        }
+        tc_fence_after_sync();
+#pragma unroll 1
+        for(uint32_t g = 0; g < groups; ++g, ++stagedGroups)
+        {
+            uint8_t* buf = staging + (stagedGroups & 1u) * STG_BYTES;
+            uint32_t raw[32];
+            tmem_load_32x32b_x32(taddrRowBase + g * 32u, raw);
+            const bool landed = mbar_wait(&cFull[stagedGroups & 1u], (stagedGroups >> 1) & 1u,
+                                          abort, WAIT_STAGE_FULL);
+            tmem_load_wait();
+#pragma unroll
+            for(uint32_t ch = 0; ch < CHUNKS; ++ch)
+            {
+                uint4* piece
+                    = reinterpret_cast<uint4*>(buf + stagingOffset<ROW_B>(rowInTile, ch));
+                alignas(16) OutT cin[VEC];
+                alignas(16) OutT out[VEC];
+                *reinterpret_cast<uint4*>(cin) = *piece;
+#pragma unroll
+                for(uint32_t e = 0; e < VEC; ++e)
+                {
+                    CompT acc;
+                    if constexpr(std::is_same<CompT, float>::value)
+                        acc = __uint_as_float(raw[ch * VEC + e]);
+                    else
+                        acc = int32_t(raw[ch * VEC + e]);
+                    out[e] = fromCompute<OutT, CompT>(
+                        scaleAdd(alpha, acc, beta, CompT(toCompute(cin[e]))));
+                }
+                *piece = *reinterpret_cast<uint4 const*>(out);
+            }
+            fence_async_shared();
+            if(!named_barrier_all(1, EPI_THREADS, landed))
+            {
+                settle(g + 1u, stagedGroups + 1u);
+                return false;
+            }
+            if(leader)
+            {
+                if(hintCD)
+                    tma_store_2d_hint(tmapD, buf, int32_t(colBase + g * 32u), int32_t(tileRow0),
+                                      streamPolicy);
+                else
+                    tma_store_2d(tmapD, buf, int32_t(colBase + g * 32u), int32_t(tileRow0));
+                tma_store_commit();
+                if(g + 2u < groups)
+                {
+                    tma_store_wait_read<0>(); // that store has read the buffer: refill it
+                    requestBox(g + 2u, stagedGroups + 2u);
+                }
+            }
+        }
+        tc_fence_before_sync();
+        return true;
+    }
+
+    // ---- C on its way to L2 ----------------------------------------------------------------
+    // With beta != 0 an epilogue thread reads its row of C once, from DRAM, and a row
+    // epilogue can only keep one or two 32-column groups of it in flight (registers): every
+    // group then costs a DRAM round trip.  Behind the next tile's MMAs that does not show, but
+    // after a block's last tile it does -- 4096^3 bf16 -> fp32 with beta = -1 took 16 us longer
+    // than with beta = 0, and 16-bit outputs 8 us.  So each thread asks for its row of the
+    // NEXT tile (and, at the start, of its first) to be brought into L2 a whole tile ahead of
+    // use; the loads of the epilogue then take an L2 hit each.
+    template <typename OutT>
+    __device__ inline void prefetchRowOfC(GemmParams const& p, uint32_t row, uint32_t col0,
+                                          uint32_t width)
+    {
+        if(row >= p.m || col0 >= p.n)
+            return;
+        const uint32_t cols  = (p.n - col0 < width) ? p.n - col0 : width;
+        const uint32_t bytes = cols * uint32_t(sizeof(OutT));
+        char const*    base
+            = reinterpret_cast<char const*>(static_cast<OutT const*>(p.c) + size_t(row) * p.ldc + col0);
+        for(uint32_t off = 0; off < bytes; off += 128u)
+            prefetch_l2(base + off);
+        prefetch_l2(base + bytes - 1u); // a row that does not start on a line boundary
+    }
+
     // ---- half of a tile that was split along K ---------------------------------------------
     // Two pairs each accumulate half of K for the same tile (TileSchedule::splitTiles).  Each
     // block writes its raw 32-bit accumulator to the workspace, makes it visible and takes a
@@ -929,13 +1109,19 @@ namespace
         named_barrier(1, EPI_THREADS);
         if(leader && tileRow0 < p.m)
         {
+            const bool     hintD   = (p.l2Hints & 4u) != 0u;
+            const uint64_t policyD = hintD ? l2_policy_evict_first() : 0;
+            auto           store   = [&](CUtensorMap const* map, uint8_t* src, uint32_t col) {
+                if(hintD)
+                    tma_store_2d_hint(map, src, int32_t(col), int32_t(tileRow0), policyD);
+                else
+                    tma_store_2d(map, src, int32_t(col), int32_t(tileRow0));
+            };
             for(uint32_t b = 0; b < wide; ++b)
                 if(colBase + b * BOX_COLS < p.n)
-                    tma_store_2d(mapWide, stage + b * BOX_B, int32_t(colBase + b * BOX_COLS),
-                                 int32_t(tileRow0));
+                    store(mapWide, stage + b * BOX_B, colBase + b * BOX_COLS);
             if(pieces % PER_BOX != 0u && colBase + wide * BOX_COLS < p.n)
-                tma_store_2d(mapNarrow, stage + wide * BOX_B, int32_t(colBase + wide * BOX_COLS),
-                             int32_t(tileRow0));
+                store(mapNarrow, stage + wide * BOX_B, colBase + wide * BOX_COLS);
             tma_store_commit();
         }
         tc_fence_before_sync();
@@ -1188,6 +1374,7 @@ namespace
         uint64_t   empty[P_STAGES];
         uint64_t   accFull[ACC_BUFS];
         uint64_t   accEmpty[ACC_BUFS];
+        uint64_t   cFull[2]; // epilogue: a box of C has landed in staging buffer 0 / 1
         uint32_t   tmemBase;
         uint32_t   splitLast; // epilogue: this block arrived last at a split tile
         AbortState abort;
@@ -1202,6 +1389,7 @@ namespace
                                  const __grid_constant__ CUtensorMap tmapBTail,
                                  const __grid_constant__ CUtensorMap tmapD,
                                  const __grid_constant__ CUtensorMap tmapDWide,
+                                 const __grid_constant__ CUtensorMap tmapC,
                                  const GemmParams                    p)
     {
         constexpr uint32_t BK     = ROW_BYTES / sizeof(InT);
@@ -1250,12 +1438,15 @@ namespace
                 mbar_init(&ctl->accFull[b], 1);
                 mbar_init(&ctl->accEmpty[b], 2 * EPI_THREADS);
             }
+            mbar_init(&ctl->cFull[0], 1);
+            mbar_init(&ctl->cFull[1], 1);
             ctl->abort.flag = 0;
             ctl->abort.code = 0;
             mbar_init_fence();
             tma_prefetch_descriptor(&tmapA);
             tma_prefetch_descriptor(&tmapB);
             tma_prefetch_descriptor(&tmapBTail);
+            tma_prefetch_descriptor(&tmapC);
             tma_prefetch_descriptor(&tmapD);
             tma_prefetch_descriptor(&tmapDWide);
         }
@@ -1431,10 +1622,21 @@ namespace
                     break;
                 const uint32_t row = tm * P_TILE_M + rank * 128u + quad * 32u + lane;
                 uint32_t       tmNext, colNext, widthNext, partNext, waysNext, splitNext;
-                const bool     stagedTail
-                    = p.stagedTail != 0u && numChunks == 1u && ways == 1u
-                      && !sched.getItem(pairId, i + 1u, tmNext, colNext, widthNext, partNext,
-                                        waysNext, splitNext);
+                const bool     hasNext = sched.getItem(pairId, i + 1u, tmNext, colNext, widthNext,
+                                                       partNext, waysNext, splitNext);
+                if(useC && p.cViaTma == 0u)
+                {
+                    if(i == 0u)
+                        prefetchRowOfC<OutT>(p, row, col0, width);
+                    if(hasNext)
+                        prefetchRowOfC<OutT>(
+                            p, tmNext * P_TILE_M + rank * 128u + quad * 32u + lane, colNext,
+                            widthNext);
+                }
+                // (with beta != 0 the last tile keeps the row epilogue, whose loads of C run
+                // ahead of their use; the staged form reads C where it needs it)
+                const bool stagedTail = p.stagedTail != 0u && numChunks == 1u && ways == 1u
+                                        && !useC && !hasNext;
                 for(uint32_t ch = 0; ch < numChunks; ++ch, ++accIter)
                 {
                     const uint32_t buf   = accIter & 1u;
@@ -1453,6 +1655,14 @@ namespace
                             &ctl->accFull[buf], accPh, &ctl->abort, taddr, p, &ctl->splitLast,
                             splitIndex, part, rank, alpha, beta, useC, quad * 32u + lane, row, col0,
                             threadIdx.x == 64u, width);
+                    }
+                    else if(p.cViaTma != 0u && useC && numChunks == 1u)
+                    {
+                        drained = drainAccumulatorTmaC<OutT, CompT>(
+                            &ctl->accFull[buf], accPh, &ctl->abort, taddr, &tmapC, &tmapD, staging,
+                            ctl->cFull, stagedGroups, alpha, beta, quad * 32u + lane,
+                            tm * P_TILE_M + rank * 128u, col0, threadIdx.x == 64u, width,
+                            (p.cViaTma & 2u) != 0u);
                     }
                     else if(stagedTail)
                     {
@@ -1708,7 +1918,7 @@ namespace
         GemmParams  p{m,    n,      k,       c,    d,  ldc, ldd, alpha, beta,
                      status, chunkKB, wide, BN, bandEnv ? bandEnv : bandRows(k, sizeof(InT)),
                      useTma ? 1u : 0u,
-                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, nullptr, nullptr};
+                     aMN ? 1u : 0u,      bMN ? 1u : 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, nullptr, nullptr};
         CUtensorMap mapA, mapB, mapD;
         {
             int rcD = makeOutputMap(&mapD, outputMapType<OutT>(), sizeof(OutT), d, m, n, ldd);
@@ -1880,10 +2090,13 @@ namespace
             p.snake    = snakeOn ? 1u : 0u;
             p.prefetch = prefKB;
             {
-                // B200WMMA_GEMM_L2HINT=0..3 forces the cache hints (bit 0: A, bit 1: B; comparison)
+                // B200WMMA_GEMM_L2HINT=0..7 forces the cache hints (bit 0: A, bit 1: B, bit 2: D;
+                // comparison)
                 const char* hintEnv = getenv("B200WMMA_GEMM_L2HINT");
                 const bool  streams = size_t(n) * k * sizeof(InT) > (size_t(48) << 20);
-                p.l2Hints = hintEnv ? uint32_t(hintEnv[0] - '0') & 3u : (streams ? 2u : 0u);
+                const bool  bigD    = size_t(m) * n * sizeof(OutT) >= (size_t(32) << 20);
+                p.l2Hints = hintEnv ? uint32_t(hintEnv[0] - '0') & 7u
+                                    : (streams ? 2u : 0u) | (bigD ? 4u : 0u);
             }
             if(mirrorOn)
             {
@@ -1917,14 +2130,17 @@ namespace
             }
             // The last tile of every block leaves through the idle operand ring and TMA stores
             // of 128-byte rows (drainLastTileStaged) when TMA stores are safe for D -- they
-            // write whole 16-byte pieces, so a row of D must end on a 16-byte boundary -- and
-            // K is accumulated in one chain.  B200WMMA_GEMM_STAGED_TAIL=0 switches it off.
+            // write whole 16-byte pieces, so a row of D must end on a 16-byte boundary -- K
+            // is accumulated in one chain and the output is a 16-bit type (1024-row shard of
+            // 8192^3 fp16: 92.85 -> 92.6 us; with 128 KB of 32-bit output per block to stage
+            // it is the slower form, int8 -> int32 4096^3 50.7 -> 52.2 us).
+            // B200WMMA_GEMM_STAGED_TAIL=0 switches it off.
             static const bool stagedEnv = [] {
                 const char* e = getenv("B200WMMA_GEMM_STAGED_TAIL");
                 return !(e && e[0] == '0');
             }();
             CUtensorMap mapDWide = mapD;
-            if(stagedEnv && tmaSafe && chunkKB == 0u && epilogueEnv == 0)
+            if(stagedEnv && tmaSafe && chunkKB == 0u && epilogueEnv == 0 && sizeof(OutT) == 2)
             {
                 p.stagedTail = 1u;
                 if(sizeof(OutT) == 2)
@@ -1935,6 +2151,37 @@ namespace
                         return rc;
                 }
             }
+            // beta == 0: every tile but a block's last leaves through the staging buffers and
+            // TMA stores of whole 128-byte (64-byte) rows rather than by per-thread row
+            // stores.  The two measure alike where the MMAs of a tile outlast its drain
+            // (8192^3 fp16); where they do not -- int8 -> int32 at K = 4096 has 8.6 us of MMAs
+            // per tile and 128 KB to write per block -- the row stores are the slower and the
+            // more fragile form (50.7 -> 57.6 us after unrelated changes to the kernel moved
+            // its code around; 50.8 us through TMA before and after).
+            if(tmaSafe && epilogueEnv == 0 && chunkKB == 0u && (beta == 0.0 || c == nullptr))
+                p.tmaStore = 1u;
+            // beta != 0 with K accumulated in one chain: C is fetched by TMA as well
+            // (drainAccumulatorTmaC) when both C and D meet the TMA's alignment rules.
+            // B200WMMA_GEMM_CTMA=0 keeps the row epilogue for C (comparison).
+            static const bool cTmaEnv = [] {
+                const char* e = getenv("B200WMMA_GEMM_CTMA");
+                return !(e && e[0] == '0');
+            }();
+            CUtensorMap mapC = mapD;
+            if(cTmaEnv && beta != 0.0 && c != nullptr && chunkKB == 0u && tmaSafe
+               && epilogueEnv == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0
+               && (size_t(ldc) * sizeof(OutT)) % 16 == 0)
+            {
+                rc = makeOutputMap(&mapC, outputMapType<OutT>(), sizeof(OutT),
+                                   const_cast<void*>(c), m, n, ldc);
+                if(rc != B200WMMA_OK)
+                    return rc;
+                static const bool cdHintEnv = [] {
+                    const char* e = getenv("B200WMMA_GEMM_CD_HINT");
+                    return !(e && e[0] == '0');
+                }();
+                p.cViaTma = cdHintEnv ? 3u : 1u;
+            }
             auto        kernel = gemm_tcgen05_pair_kernel<InT, OutT, CompT>;
             static bool done[64] = {};
             rc = optInSharedMemory(kernel, P_SMEM_BYTES, done);
@@ -1944,7 +2191,7 @@ namespace
             const uint32_t pairs = tiles < pairsMax ? tiles : pairsMax;
             return b200wmma::cudaToStatus(b200wmma::launchOverlapped(
                 kernel, dim3(2 * pairs), dim3(NUM_THREADS), P_SMEM_BYTES, stream, mapA, mapB,
-                mapBTail, mapD, mapDWide, p));
+                mapBTail, mapD, mapDWide, mapC, p));
         }
 
         int rc = aMN ? makeOperandMapMN(&mapA, dt, sizeof(InT), a, m, k, lda)

@@ -158,6 +158,39 @@ def test_padded_leading_dimensions_leave_padding_untouched():
     assert 0 <= O.max_rel_err(O.F16, np.ascontiguousarray(got[:, :n]).reshape(-1), want) <= 2e-3
 
 
+@pytest.mark.parametrize("in_t,out_t", [(O.F16, O.F16), (O.BF16, O.F32), (O.I8, O.I32)])
+def test_beta_with_c_in_place_and_own_leading_dimension(in_t, out_t):
+    """beta != 0 over several tiles per block pair: once with C in a buffer of its own whose
+    leading dimension differs from D's, once in place (C and D the same buffer).  Both must
+    match the host routine; columns of D beyond n keep their fill."""
+    m, n, k = 2100, 2600, 144  # 9 x 11 tiles: some block pairs get two
+    al, be = _ab(in_t)
+    case = dict(in_t=in_t, out_t=out_t, m=m, n=n, k=k, la=ROW, lb=COL, alpha=al, beta=be, seed=91)
+    a, b, c = gemm_inputs(case)
+    want = O.gemm(in_t, out_t, m, n, k, a, b, c, al, be, ROW, COL)
+    ldc, ldd = n + 16, n + 32
+    fill = -7 if out_t == O.I32 else 777.0
+    cbuf = np.zeros((m, ldc), dtype=c.dtype); cbuf[:, :n] = c.reshape(m, n)
+    da, db = to_device(a, in_t), to_device(b, in_t)
+    out = torch.full((m * ldd,), fill, dtype=api.torch_dtype(out_t), device="cuda")
+    api.gemm(in_t, out_t, m, n, k, da, db, to_device(cbuf.reshape(-1), out_t), al, be, ldc=ldc,
+             ldd=ldd, out=out)
+    api.check_device()
+    got = to_host(out, out_t).reshape(m, ldd)
+    assert (out.reshape(m, ldd)[:, n:] == fill).all(), "columns beyond n were overwritten"
+    tol = 0.0 if out_t == O.I32 else 2e-3
+    assert 0 <= O.max_rel_err(out_t, np.ascontiguousarray(got[:, :n]).reshape(-1), want) <= tol
+    # in place
+    dbuf = np.zeros((m, ldd), dtype=c.dtype); dbuf[:, :n] = c.reshape(m, n)
+    inplace = to_device(dbuf.reshape(-1), out_t)
+    api.gemm(in_t, out_t, m, n, k, da, db, inplace, al, be, ldc=ldd, ldd=ldd, out=inplace)
+    api.check_device()
+    got2 = to_host(inplace, out_t).reshape(m, ldd)
+    assert np.array_equal(np.ascontiguousarray(got2[:, :n]).view(np.uint8),
+                          np.ascontiguousarray(got[:, :n]).view(np.uint8))
+    assert (np.ascontiguousarray(got2[:, n:]).view(np.uint8) == 0).all()
+
+
 def test_misaligned_arguments_are_refused():
     t = torch.zeros(1 << 16, dtype=torch.float16, device="cuda")
     with pytest.raises(api.B200WmmaError) as e:
