@@ -787,7 +787,8 @@ namespace
                                                 uint64_t* cFull, uint32_t& stagedGroups,
                                                 CompT alpha, CompT beta, uint32_t rowInTile,
                                                 uint32_t tileRow0, uint32_t colBase, bool leader,
-                                                uint32_t bnTile, bool hintCD)
+                                                uint32_t bnTile, bool hintCD,
+                                                uint32_t taddrLane = 0, bool withSum = false)
     {
         constexpr uint32_t ROW_B     = 32 * sizeof(OutT); // bytes of one staged row (128 or 64)
         constexpr uint32_t VEC       = 16 / sizeof(OutT); // elements per 16-byte piece
@@ -846,6 +847,21 @@ namespace
             uint8_t* buf = staging + (stagedGroups & 1u) * STG_BYTES;
             uint32_t raw[32];
             tmem_load_32x32b_x32(taddrRowBase + g * 32u, raw);
+            if constexpr(std::is_same<CompT, float>::value)
+            {
+                // last chunk of a chunked accumulation: the running sum kept in tensor memory
+                // (drainAccumulatorToTmemSum) is added first, as the row epilogue does
+                if(withSum)
+                {
+                    uint32_t sum[32];
+                    tmem_load_32x32b_x32(taddrLane + sumColumn(g, bnTile), sum);
+                    tmem_load_wait();
+#pragma unroll
+                    for(uint32_t e = 0; e < 32; ++e)
+                        raw[e] = __float_as_uint(
+                            __fadd_rn(__uint_as_float(sum[e]), __uint_as_float(raw[e])));
+                }
+            }
             const bool landed = mbar_wait(&cFull[stagedGroups & 1u], (stagedGroups >> 1) & 1u,
                                           abort, WAIT_STAGE_FULL);
             tmem_load_wait();
@@ -1675,7 +1691,14 @@ namespace
                     else if constexpr(std::is_same<OutT, float>::value
                                       && std::is_same<CompT, float>::value)
                     {
-                        if(p.sumInTmem && numChunks > 1u)
+                        if(p.sumInTmem && numChunks > 1u && mode == EPI_LAST && useC
+                           && p.cViaTma != 0u)
+                            drained = drainAccumulatorTmaC<OutT, CompT>(
+                                &ctl->accFull[buf], accPh, &ctl->abort, taddr, &tmapC, &tmapD,
+                                staging, ctl->cFull, stagedGroups, alpha, beta, quad * 32u + lane,
+                                tm * P_TILE_M + rank * 128u, col0, threadIdx.x == 64u, width,
+                                (p.cViaTma & 2u) != 0u, taddrLane, true);
+                        else if(p.sumInTmem && numChunks > 1u)
                             drained = drainAccumulatorToTmemSum(&ctl->accFull[buf], accPh,
                                                                 &ctl->abort, taddr, taddrLane, p,
                                                                 alpha, beta, useC, row, col0, mode,
@@ -2168,7 +2191,8 @@ namespace
                 return !(e && e[0] == '0');
             }();
             CUtensorMap mapC = mapD;
-            if(cTmaEnv && beta != 0.0 && c != nullptr && chunkKB == 0u && tmaSafe
+            if(cTmaEnv && beta != 0.0 && c != nullptr && (chunkKB == 0u || p.sumInTmem != 0u)
+               && tmaSafe
                && epilogueEnv == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0
                && (size_t(ldc) * sizeof(OutT)) % 16 == 0)
             {
