@@ -369,7 +369,7 @@ def dlrm_cases(total_batch, seed=4, iters=20, check=True, which=("fwd", "bwd")):
                              "frac": gbs / hbm, "algorithmic_bytes": nb,
                              "peak_source": f"{src} copy bandwidth x {WORLD} GPU(s)"}}
 
-    def verdict(r, err, exact_ok=True):
+    def record_parity(r, err, exact_ok=True):
         r["max_rel_err"] = _max_over_ranks(err if err >= 0 else 1e30)
         r["tolerance"] = 2e-3
         r["parity"] = bool(_max_over_ranks(0.0 if (0 <= err <= 2e-3 and exact_ok) else 1.0) == 0.0)
@@ -392,7 +392,7 @@ def dlrm_cases(total_batch, seed=4, iters=20, check=True, which=("fwd", "bwd")):
             got = out.view(batch, out_len)[torch.from_numpy(pick).cuda()].cpu().numpy().reshape(-1)
             r["checker"] = ("rocWMMA dlrm_fwd_CPU" if O.ref() is not None else "oracle port") + \
                 f", {pick.size} samples per rank, {threads} threads"
-            verdict(r, O.max_rel_err(F16, got, want))
+            record_parity(r, O.max_rel_err(F16, got, want))
         res.append(r)
     if "bwd" in which:
         sets = replicate(copies_needed(batch * (2 * m * k + out_len + k) * 2), dx, dup, grad, mlp)
@@ -415,7 +415,7 @@ def dlrm_cases(total_batch, seed=4, iters=20, check=True, which=("fwd", "bwd")):
             gmlp = mlp.view(batch, k)[sel].cpu().numpy().reshape(-1)
             r["checker"] = ("rocWMMA dlrm_bwd_CPU" if O.ref() is not None else "oracle port") + \
                 f", {pick.size} samples per rank, {threads} threads"
-            verdict(r, O.max_rel_err(F16, ggrad, wgrad),
+            record_parity(r, O.max_rel_err(F16, ggrad, wgrad),
                     bool(np.array_equal(gmlp.view(np.uint16), wmlp.view(np.uint16))))
         res.append(r)
     return res
