@@ -54,3 +54,21 @@ def test_config_sgemv_16384():
                    2.1).cpu().numpy()
     api.check_device()
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("form", ["chain", "single"])
+@pytest.mark.parametrize("m,k", [(2048, 4100), (6144, 2048), (9472, 1024), (12000, 515)])
+def test_sgemv_both_forms_at_every_block_count(form, m, k, monkeypatch):
+    """The two fp32 forms (adding warp fed by multiplier warps / one warp doing everything) are
+    picked by the number of 32-row blocks; B200WMMA_GEMV_FORM forces one.  Forced, each must
+    stay bit-identical to the host routine also where the other would run: one block per SM,
+    two blocks per SM (a shallower ring), 64-row blocks -- on the first launch of each shape,
+    when the copies of a ring land least in order."""
+    monkeypatch.setenv("B200WMMA_GEMV_FORM", form)
+    a, x, y = gemv_inputs(m, k, seed=13)
+    want = O.gemv(O.F32, m, k, a, x, y, 2.1, 2.1)
+    da, dx, dy = to_device(a, O.F32), to_device(x, O.F32), to_device(y, O.F32)
+    for _ in range(3):
+        got = api.gemv(O.F32, m, k, da, dx, dy, 2.1, 2.1).cpu().numpy()
+        api.check_device()
+        assert np.array_equal(got, want)
