@@ -59,8 +59,10 @@ TOLERANCE = 2e-3     # fp16 inputs, fp32 accumulate: max |a-b| / (|a|+|b|+1)
 # launch.  Quoted in roofline.traffic -- a benchmark run does not measure it -- together with
 # where it came from; launch shapes without a capture report null.
 PROFILED_TRAFFIC = {
-    8192: 1.219e9,   # 1.092 GB read + 0.127 GB written (algorithmic: 0.403 GB)
-    1024: 0.180e9,   # 168.8 MB read + 11.1 MB written inside the kernel (algorithmic: 0.168 GB)
+    # B's tiles are fetched "evict first": a lone cold launch re-reads them from DRAM (1.22 GB
+    # without the mark) and is slower for it, launches back to back are 1.7 % faster
+    8192: 1.968e9,   # 1.857 GB read + 0.110 GB written (algorithmic: 0.403 GB)
+    1024: 0.160e9,   # 155.2 MB read + 4.7 MB written inside the kernel (algorithmic: 0.168 GB)
 }
 TRAFFIC_SOURCE = ("one ncu capture (--set full, --clock-control none) of a launch of this shape, "
                   "cold L2; quoted from the committed profiler summary, not measured by this run")
